@@ -1,0 +1,145 @@
+/* C ABI of the B200 routed-expert FFN (one MoE layer, one tensor-parallel rank).
+ *
+ * Drop-in surface for the reference's expert-rank seam
+ *   crates/mimo26-spark/kernels/b1_serve.cu:214-574   (extern "C" m26s_b1_*)
+ *   crates/mimo26-spark/src/b1.rs:21-49               (the Rust declarations that bind it)
+ * with the same conventions: opaque heap handles, plain pointers and sizes,
+ * int return codes, a caller-owned NUL-terminated error buffer.
+ *
+ * Return codes (as b1_serve.cu): 0 ok; 1 bad argument / handle / pitch;
+ * 2 CUDA error ("what: cudaGetErrorString"); 3 plan rejected (invalid id,
+ * non-resident expert, weight outside [0, FLT_MAX], an expert twice in one row);
+ * 4 numerical fault (stage name and fault code in the message). Outputs are
+ * undefined on a nonzero return.
+ *
+ * Threading: handles may move between threads but are not shared; one call at
+ * a time per scratch. Every entry point runs on the CUDA device that is
+ * current when it is called; a handle must be used on the device it was made on.
+ */
+#ifndef M26B_EXPERT_H
+#define M26B_EXPERT_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct m26b_layer m26b_layer;
+typedef struct m26b_scratch m26b_scratch;
+
+#define M26B_HIDDEN 4096
+#define M26B_INTERMEDIATE 2048
+#define M26B_EXPERTS 256
+#define M26B_TOPK 8
+
+/* Replaces m26s_b1_layer_new (b1_serve.cu:218-265): prepare one layer from the
+ * reference's canonical-v2 rank image in device memory, 256 experts x 3,342,336
+ * bytes, rank 0..3 of TP4 (crates/mimo26-repack/src/geom.rs:36-50). The image
+ * may be freed after the call returns. */
+int m26b_layer_new(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t rank, m26b_layer** out,
+                   char* err, size_t errlen);
+
+/* Same image layout generalised to tp_size in {1,2,4,8}: per expert
+ * gate payload [I,2048] | gate scales [I,128] | up payload | up scales |
+ * down payload [4096,I/2] | down scales [4096,I/32], I = 2048 / tp_size.
+ * tp_size 4 is exactly m26b_layer_new. */
+int m26b_layer_new_tp(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t tp_rank, uint32_t tp_size,
+                      m26b_layer** out, char* err, size_t errlen);
+
+/* From the checkpoint's own tensors (crates/mimo26-expert/src/mxfp4.rs:13-19),
+ * all in device memory and stacked over the 256 experts: gate_proj / up_proj
+ * weight u8 [256][2048][2048] + weight_scale u8 [256][2048][128], down_proj
+ * weight u8 [256][4096][1024] + weight_scale u8 [256][4096][64]. The rank
+ * keeps gate/up rows [tp_rank*I, (tp_rank+1)*I) and the matching down columns
+ * (the reference's build_slice, crates/mimo26-repack/src/repack.rs:135-163). */
+int m26b_layer_new_from_checkpoint(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w,
+                                   const uint8_t* up_s, const uint8_t* down_w, const uint8_t* down_s,
+                                   uint32_t tp_rank, uint32_t tp_size, m26b_layer** out, char* err, size_t errlen);
+
+/* Replaces m26s_b1_layer_all_normal (b1_serve.cu:267-268): 1 if every weight
+ * scale byte lies in [2, 252]. Informational here: the block-scaled MMA takes
+ * every UE8M0 byte 0..254, and byte 255 is stored as 254 at prepare time. */
+int m26b_layer_all_normal(const m26b_layer* layer);
+/* Local intermediate width of the layer (2048 / tp_size). */
+int m26b_layer_i_local(const m26b_layer* layer);
+/* Replaces m26s_b1_layer_free (b1_serve.cu:270-276). */
+void m26b_layer_free(m26b_layer* layer);
+
+/* Replace m26s_b1_scratch_new / _free (b1_serve.cu:278-302): a non-blocking
+ * stream, events and grow-only device buffers. */
+int m26b_scratch_new(m26b_scratch** out, char* err, size_t errlen);
+void m26b_scratch_free(m26b_scratch* scratch);
+
+/* Replaces m26s_b1_ffn (b1_serve.cu:312-572), same arguments: HOST payload rows
+ * of 4096 E4M3 bytes at payload_pitch, HOST scale rows of 128 UE8M0 bytes at
+ * scales_pitch (4224 for both reads the request frame in place), HOST ids and
+ * weights [rows*8] token-major, HOST bf16_out [rows*4096]. Synchronous.
+ * rows may exceed the reference's 4096 (larger requests run in passes).
+ * ms (or NULL) receives 8 floats: [0] host time to upload and enqueue, [1] GPU
+ * time of the FFN, [2] host tail (download, checks), [3] token tiles (the
+ * reference reports 16-row groups here), [4] plan+permute+FC1 (the
+ * intermediate quantiser is fused into FC1), [5] 0, [6] FC2, [7] combine. */
+int m26b_ffn(const m26b_layer* layer, m26b_scratch* scratch, const uint8_t* payload, size_t payload_pitch,
+             const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
+             uint16_t* bf16_out, float* ms, char* err, size_t errlen);
+
+/* Device-resident variant of the same call (the reference's older device-pointer
+ * ABI shows the convention: crates/mimo26-expert/kernels/include/mimo26_expert_kernels.h:31-69).
+ * x_dtype: 0 = BF16 [rows,4096], 1 = FP32 [rows,4096], 2 = E4M3 payload with x_scales [rows,128].
+ * codec (x_dtype 0/1 only): 0 = the coordinator's wire quantiser
+ * (crates/mimo26-coordinator/src/wire.rs:53-78), 1 = e4m3fn-k32-v1
+ * (crates/mimo26-expert/kernels/b1/quant_v1.cuh).
+ * All pointers are device pointers; work is enqueued on `stream` (a
+ * cudaStream_t; NULL = the scratch's own stream) and the call returns without
+ * synchronising. partial_out (FP32 [rows,4096], the pre-BF16 rank sum) may be
+ * NULL. Faults are reported by m26b_scratch_status. rows <= 16384 per call. */
+int m26b_ffn_dev(const m26b_layer* layer, m26b_scratch* scratch, const void* x, int x_dtype,
+                 const uint8_t* x_scales, int codec, const int32_t* ids, const float* weights, uint32_t rows,
+                 uint16_t* bf16_out, float* partial_out, void* stream, char* err, size_t errlen);
+
+/* Waits for the scratch's last m26b_ffn_dev and returns its code (0, 2, 3 or 4). */
+int m26b_scratch_status(m26b_scratch* scratch, void* stream, char* err, size_t errlen);
+
+/* Stage dumps for parity tests (the reference's primitive cell dumps stages the
+ * same way: crates/mimo26-expert/tests/b1_core/primitive.cu:173-196).
+ * flags bit 0: keep an FP32 copy of silu(gate)*up before quantisation. */
+int m26b_scratch_set_debug(m26b_scratch* scratch, uint32_t flags);
+enum {
+    M26B_PEEK_META = 0,            /* 8 x u32: fault, tiles, fc1 items, fc2 items, active experts, max count */
+    M26B_PEEK_INVERSE = 1,         /* i32 [routes]  original route -> grouped route  (group_plan.cuh:19) */
+    M26B_PEEK_ORIGINAL_ROUTES = 2, /* i32 [routes]  grouped route -> original route  (group_plan.cuh:20) */
+    M26B_PEEK_GROUPED_WEIGHTS = 3, /* f32 [routes] */
+    M26B_PEEK_X_PAYLOAD = 4,       /* u8 [rows,4096] quantised input */
+    M26B_PEEK_X_SCALES = 5,        /* u8 [rows,128] */
+    M26B_PEEK_MID_PAYLOAD = 6,     /* u8 [routes,I_local] grouped order */
+    M26B_PEEK_MID_F32 = 7,         /* f32 [routes,I_local] grouped order (debug flag 1) */
+    M26B_PEEK_Y = 8,               /* f32 [routes,4096] original route order, unweighted */
+    M26B_PEEK_PARTIAL = 9,         /* f32 [rows,4096] */
+    M26B_PEEK_MID_SCALES = 10      /* u8 [routes,I_local/32] grouped order, row-major (gathered from the scale blocks) */
+};
+/* Copies a buffer of the last pass to host memory; returns 0 or 1/2. */
+int m26b_scratch_peek(m26b_scratch* scratch, int what, void* host_dst, uint64_t bytes, char* err, size_t errlen);
+
+/* Stand-alone stages on device pointers, enqueued on `stream`.
+ * Quantise n_elems (a multiple of 32) values: x_dtype 0 BF16 / 1 FP32, codec as
+ * above; fault_dev is one u32 the kernel ORs fault codes into (4 nonfinite,
+ * 5 reconstruction overflow; quant_v1 only). */
+int m26b_quantize_dev(const void* x, int x_dtype, uint64_t n_elems, int codec, uint8_t* payload, uint8_t* scales,
+                      uint32_t* fault_dev, void* stream, char* err, size_t errlen);
+/* Ordered top-8 combine (crates/mimo26-expert/kernels/b1/route_reduce.cu:61-74):
+ * y FP32 [rows,8,4096], weights [rows,8] -> partial FP32 [rows,4096] (or NULL) and bf16. */
+int m26b_route_reduce_dev(const float* y, const float* weights, uint32_t rows, float* partial, uint16_t* bf16,
+                          uint32_t* fault_dev, void* stream, char* err, size_t errlen);
+/* Cross-rank sum in rank order (crates/mimo26-coordinator/kernels/glue.cu:202-213):
+ * planes[r] BF16 [n], r < n_ranks <= 8 -> out FP32 [n]. `planes` is a HOST array of device pointers. */
+int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
+                      size_t errlen);
+
+/* Library identity: "m26b-expert <version> sm_100a". */
+const char* m26b_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

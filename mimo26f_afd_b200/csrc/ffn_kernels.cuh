@@ -1,0 +1,378 @@
+// The bandwidth-bound kernels around the two grouped GEMMs: activation
+// quantisers, the stable route planner, the token-to-expert permutation, the
+// ordered top-k weighted combine, the cross-rank sum and the weight repack.
+// All are plain coalesced/vectorised CUDA; none reshapes its work into a GEMM.
+#pragma once
+#include <cuda_runtime.h>
+#include "layout.cuh"
+#include "codec.cuh"
+
+namespace m26b {
+
+// ---------------------------------------------------------------- quantisers
+// One K32 block = four threads of eight elements (16-byte loads for BF16,
+// 2 x 16 bytes for FP32); the block maximum crosses the four lanes by shuffle.
+// CODEC 0: wire codec (scale byte 0 for a zero block, ties away from zero).
+// CODEC 1: quant_v1 (floor 1e-4, ties to even, faults instead of clipping; a
+// faulting block writes nothing), crates/mimo26-expert/kernels/b1/quant_v1.cu:34-59.
+template <int CODEC, typename IN>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const IN* __restrict__ x, uint64_t n_elems,
+                                                            uint8_t* __restrict__ payload,
+                                                            uint8_t* __restrict__ scales,
+                                                            uint32_t* __restrict__ fault) {
+    const uint64_t n8 = n_elems / 8;
+    uint32_t bad = 0;
+    // the bound is rounded up to a whole warp so every lane reaches the shuffles
+    for (uint64_t g = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < ((n8 + 31) & ~uint64_t(31));
+         g += uint64_t(gridDim.x) * blockDim.x) {
+        uint32_t bits[8];
+        const bool live = g < n8;
+        if (live) {
+            if constexpr (sizeof(IN) == 2) {
+                const uint4 v = reinterpret_cast<const uint4*>(x)[g];
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { bits[2 * i] = w[i] << 16; bits[2 * i + 1] = w[i] & 0xffff0000u; }
+            } else {
+                const uint4 a = reinterpret_cast<const uint4*>(x)[2 * g], b = reinterpret_cast<const uint4*>(x)[2 * g + 1];
+                bits[0] = a.x; bits[1] = a.y; bits[2] = a.z; bits[3] = a.w;
+                bits[4] = b.x; bits[5] = b.y; bits[6] = b.z; bits[7] = b.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bits[i] = 0;
+        }
+        uint32_t amax = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t m = bits[i] & 0x7fffffffu;
+            if (CODEC == 0 && m > 0x7f800000u) m = 0;   // the wire codec's maximum skips NaN
+            amax = m > amax ? m : amax;
+        }
+        uint32_t o = __shfl_xor_sync(0xffffffffu, amax, 1); amax = o > amax ? o : amax;
+        o = __shfl_xor_sync(0xffffffffu, amax, 2); amax = o > amax ? o : amax;
+        uint32_t code[8];
+        uint32_t sbyte;
+        bool write = live;
+        if constexpr (CODEC == 0) {
+            sbyte = wire_scale_byte(amax);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) code[i] = wire_payload(bits[i], sbyte);
+        } else {
+            bool over = false;
+            if (amax >= 0x7f800000u) {
+                if (live) bad |= kFaultQuantNonfinite;
+                write = false;
+                sbyte = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) code[i] = 0;
+            } else {
+                const int k = quant_v1_scale_exp(amax);
+                sbyte = uint32_t(k + 127);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { code[i] = quant_v1_payload(bits[i], k); over |= !quant_v1_finite(code[i], k); }
+            }
+            uint32_t ov = over ? 1u : 0u;
+            ov |= __shfl_xor_sync(0xffffffffu, ov, 1);
+            ov |= __shfl_xor_sync(0xffffffffu, ov, 2);
+            if (ov) { if (live) bad |= kFaultQuantOverflow; write = false; }
+        }
+        if (write) {
+            uint2 out;
+            out.x = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
+            out.y = code[4] | (code[5] << 8) | (code[6] << 16) | (code[7] << 24);
+            reinterpret_cast<uint2*>(payload)[g] = out;
+            if ((g & 3) == 0) scales[g >> 2] = uint8_t(sbyte);
+        }
+    }
+    if (bad) atomicOr(fault, bad);
+}
+
+// ---------------------------------------------------------------- route plan
+struct ExpertPlan {
+    int32_t count, rbase, tile_start, width;
+};
+struct PlanOut {
+    int32_t* inverse;          // original route -> grouped route
+    int32_t* original_routes;  // grouped route -> original route
+    float* grouped_weights;
+    ExpertPlan* experts;       // [256]
+    TokenTile* tiles;
+    WorkItem* items_fc1;
+    WorkItem* items_fc2;
+    PlanMeta* meta;
+};
+
+// One CTA. Validates the routes, counts per expert, then places routes in
+// expert-major order, stable inside an expert (identical to a stable sort by
+// expert id: crates/mimo26-expert/kernels/b1/group_plan.cu:32-79), and cuts
+// each expert's run into token tiles of at most `max_n` rows.
+// Rejection rules as the reference planner (b1_serve.cu:46-59): id in
+// [0,256), expert resident, 0 <= weight <= FLT_MAX, no expert twice in a row.
+__global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
+                                                    uint32_t rows, const uint8_t* __restrict__ resident, int max_n,
+                                                    int mt_fc1, int mt_fc2, PlanOut o) {
+    __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
+    __shared__ uint32_t i1base[kExperts], i2base[kExperts], cursor[kExperts];
+    __shared__ uint32_t wcnt[32][kExperts];
+    __shared__ uint32_t bad;
+    const uint32_t tid = threadIdx.x, nt = blockDim.x, routes = rows * kTopK;
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t e = tid; e < kExperts; e += nt) { cnt[e] = 0; cursor[e] = 0; }
+    if (tid == 0) bad = 0;
+    __syncthreads();
+    for (uint32_t r = tid; r < routes; r += nt) {
+        const int32_t e = ids[r];
+        const float wt = w[r];
+        bool ok = e >= 0 && e < kExperts && resident[e] && wt >= 0.0f && wt <= 3.402823466e+38f;
+        if (ok)
+            for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
+        if (!ok) atomicOr(&bad, 1u); else atomicAdd(&cnt[e], 1u);
+    }
+    __syncthreads();
+    if (bad) {
+        if (tid == 0) { PlanMeta m{}; m.fault = kFaultPlan; *o.meta = m; }
+        return;
+    }
+    if (tid == 0) {
+        uint32_t rb = 0, t = 0, i1 = 0, i2 = 0, active = 0, mx = 0;
+        for (int e = 0; e < kExperts; ++e) {
+            const uint32_t c = cnt[e];
+            const uint32_t n = c ? (c + max_n - 1) / max_n : 0;
+            const uint32_t per = n ? (c + n - 1) / n : 0;
+            rbase[e] = rb; tstart[e] = t; ntl[e] = n; width[e] = (per + 15u) & ~15u;
+            i1base[e] = i1; i2base[e] = i2;
+            rb += c; t += n; i1 += n * mt_fc1; i2 += n * mt_fc2;
+            active += c ? 1 : 0; mx = c > mx ? c : mx;
+        }
+        PlanMeta m{};
+        m.fault = 0; m.n_tiles = t; m.n_items_fc1 = i1; m.n_items_fc2 = i2; m.active_experts = active; m.max_count = mx;
+        *o.meta = m;
+    }
+    __syncthreads();
+    // stable placement, 1024 routes per pass in route order
+    for (uint32_t base = 0; base < routes; base += nt) {
+        for (uint32_t i = tid; i < 32 * kExperts; i += nt) (&wcnt[0][0])[i] = 0;
+        __syncthreads();
+        const uint32_t r = base + tid;
+        const bool valid = r < routes;
+        const int32_t e = valid ? ids[r] : -1 - int32_t(lane);
+        const uint32_t peers = __match_any_sync(0xffffffffu, e);
+        const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+        if (valid && rank == 0) wcnt[warp][e] = __popc(peers);
+        __syncthreads();
+        if (tid < kExperts) {
+            uint32_t run = cursor[tid];
+            for (int wi = 0; wi < 32; ++wi) { const uint32_t t = wcnt[wi][tid]; wcnt[wi][tid] = run; run += t; }
+            cursor[tid] = run;
+        }
+        __syncthreads();
+        if (valid) {
+            const uint32_t g = rbase[e] + wcnt[warp][e] + rank;
+            o.inverse[r] = int32_t(g);
+            o.original_routes[g] = int32_t(r);
+            o.grouped_weights[g] = w[r];
+        }
+        __syncthreads();
+    }
+    // tiles and work items: one warp per expert, lanes over (weight tile, token tile)
+    for (uint32_t e = warp; e < kExperts; e += nt / 32) {
+        const uint32_t c = cnt[e], n = ntl[e], wd = width[e];
+        if (lane == 0) o.experts[e] = ExpertPlan{int32_t(c), int32_t(rbase[e]), int32_t(tstart[e]), int32_t(wd)};
+        for (uint32_t j = lane; j < n; j += 32) {
+            const uint32_t nv = c - j * wd < wd ? c - j * wd : wd;
+            o.tiles[tstart[e] + j] = TokenTile{int32_t(e), int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
+        }
+        for (uint32_t i = lane; i < n * mt_fc1; i += 32)
+            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % n), int32_t(i / n)};
+        for (uint32_t i = lane; i < n * mt_fc2; i += 32)
+            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % n), int32_t(i / n)};
+    }
+}
+
+// ---------------------------------------------------------------- permutation
+// Grouped row p <- token row original_routes[p] / 8: 4096 E4M3 bytes (one
+// 16-byte vector per thread) and 128 scale bytes scattered into the token
+// tile's scale blocks. Also the input gate of the path: a scale byte outside
+// 105..247 or a NaN payload code raises kFaultInputScale, as the reference's
+// activation view poisons them (kernels/b1/grouped.cu:28,36).
+__global__ void __launch_bounds__(256) permute_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs,
+                                                      const int32_t* __restrict__ ids,
+                                                      const int32_t* __restrict__ original_routes,
+                                                      const ExpertPlan* __restrict__ experts,
+                                                      const PlanMeta* __restrict__ meta, uint32_t routes,
+                                                      uint8_t* __restrict__ x_perm, uint8_t* __restrict__ sfb,
+                                                      uint32_t* __restrict__ fault) {
+    if (meta->fault) return;   // a rejected plan leaves no valid route tables
+    uint32_t bad = 0;
+    for (uint32_t p = blockIdx.x; p < routes; p += gridDim.x) {
+        const int32_t route = original_routes[p];
+        const uint32_t token = uint32_t(route) / kTopK;
+        const uint4 v = reinterpret_cast<const uint4*>(xq + size_t(token) * kHidden)[threadIdx.x];
+        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if ((((wv[i] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) != 0u) bad = kFaultInputScale;
+        reinterpret_cast<uint4*>(x_perm + size_t(p) * kHidden)[threadIdx.x] = v;
+        if (threadIdx.x < kHidden / kBlockK) {
+            const ExpertPlan ep = experts[ids[route]];
+            const uint32_t local = p - uint32_t(ep.rbase);
+            const uint32_t tile = uint32_t(ep.tile_start) + local / uint32_t(ep.width), lr = local % uint32_t(ep.width);
+            const uint8_t sb = xs[size_t(token) * (kHidden / kBlockK) + threadIdx.x];
+            if (sb < 105 || sb > 247) bad = kFaultInputScale;
+            const uint32_t chunk = threadIdx.x >> 2, kb = threadIdx.x & 3u;
+            sfb[((size_t(tile) * (kHidden / kChunkK) + chunk) * 2 + (lr >> 7)) * kScaleBlockBytes +
+                scale_block_offset(int(lr & 127u), int(kb))] = sb;
+        }
+    }
+    if (bad) atomicOr(fault, bad);
+}
+
+// ---------------------------------------------------------------- combine
+// Per (token, column): v = 0; v = add(v, mul(w_j, y_j)) for slot j = 0..7 with
+// separate round-to-nearest multiply and add, then BF16 round-to-nearest-even
+// (crates/mimo26-expert/kernels/b1/route_reduce.cu:61-74). Any nonfinite
+// weight, value or partial sum, or a BF16 overflow, raises kFaultReduce.
+__global__ void __launch_bounds__(256) route_reduce_kernel(const float* __restrict__ y, const float* __restrict__ w,
+                                                           uint32_t rows, float* __restrict__ partial,
+                                                           uint16_t* __restrict__ bf16, uint32_t* __restrict__ fault) {
+    const float kMax = 3.402823466e+38f;
+    const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
+    bool failed = false;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint64_t row = i / (kHidden / 4), c4 = i % (kHidden / 4);
+        float4 z[kTopK];
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) z[j] = reinterpret_cast<const float4*>(y)[(row * kTopK + j) * (kHidden / 4) + c4];
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) {
+            const float wt = w[row * kTopK + j];
+            ok = ok && wt >= 0.0f && wt <= kMax;
+            const float zz[4] = {z[j].x, z[j].y, z[j].z, z[j].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                ok = ok && zz[k] >= -kMax && zz[k] <= kMax;
+                v[k] = __fadd_rn(v[k], __fmul_rn(wt, zz[k]));
+                ok = ok && v[k] >= -kMax && v[k] <= kMax;
+            }
+        }
+        uint32_t code[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { code[k] = bf16_rne_bits(v[k]); ok = ok && (code[k] & 0x7f80u) != 0x7f80u; }
+        if (!ok) {
+            failed = true;
+            code[0] = code[1] = code[2] = code[3] = 0;
+            v[0] = v[1] = v[2] = v[3] = __int_as_float(0x7fc00000);
+        }
+        if (partial) reinterpret_cast<float4*>(partial)[i] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<uint2*>(bf16)[i] = make_uint2(code[0] | (code[1] << 16), code[2] | (code[3] << 16));
+    }
+    if (__syncthreads_or(failed) && threadIdx.x == 0) atomicOr(fault, uint32_t(kFaultReduce));
+}
+
+// Cross-rank sum: s = 0; s = add(s, f32(bf16_r)) for r = 0..G-1 in rank order
+// (crates/mimo26-coordinator/kernels/glue.cu:202-213, crates/mimo26-wire/src/l4.rs:169-244).
+struct RankPlanes {
+    const uint16_t* p[8];
+};
+__global__ void __launch_bounds__(256) rank_sum_kernel(RankPlanes planes, int n_ranks, uint64_t n, float* __restrict__ out) {
+    const uint64_t n8 = n / 8;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += uint64_t(gridDim.x) * blockDim.x) {
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < n_ranks; ++r) {
+            const uint4 v = reinterpret_cast<const uint4*>(planes.p[r])[i];
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                s[2 * k] = __fadd_rn(s[2 * k], __uint_as_float(wv[k] << 16));
+                s[2 * k + 1] = __fadd_rn(s[2 * k + 1], __uint_as_float(wv[k] & 0xffff0000u));
+            }
+        }
+        reinterpret_cast<float4*>(out)[2 * i] = make_float4(s[0], s[1], s[2], s[3]);
+        reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(s[4], s[5], s[6], s[7]);
+    }
+    for (uint64_t i = n8 * 8 + uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) {
+        float s = 0.f;
+        for (int r = 0; r < n_ranks; ++r) s = __fadd_rn(s, __uint_as_float(uint32_t(planes.p[r][i]) << 16));
+        out[i] = s;
+    }
+}
+
+// ---------------------------------------------------------------- weight repack
+// Source of one projection: payload u8 [E][rows][in/2] and scales u8
+// [E][rows][in/32] with explicit strides, so the same kernels read the
+// checkpoint tensors (crates/mimo26-expert/src/mxfp4.rs:13-19) and a per-rank
+// canonical slice image (crates/mimo26-repack/src/geom.rs:36-50).
+struct ProjSrc {
+    const uint8_t* payload;
+    const uint8_t* scales;
+    uint64_t expert_stride_p, expert_stride_s;   // bytes between experts
+    uint64_t row_stride_p, row_stride_s;         // bytes between rows
+    uint64_t row0;                               // first row of this rank's slice
+    uint64_t col0_p, col0_s;                     // first payload / scale byte of this rank's K slice
+};
+
+// w13[e][j][r][*]: r < 64 -> gate row 64 j + r, else up row 64 j + r - 64. 16 bytes per thread.
+__global__ void __launch_bounds__(256) prep_w13_kernel(ProjSrc gate, ProjSrc up, int i_local, uint8_t* __restrict__ dst) {
+    const uint64_t vec_per_row = kHidden / 2 / 16;
+    const uint64_t total = uint64_t(kExperts) * (i_local / 64) * 128 * vec_per_row;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint64_t v = i % vec_per_row, row = i / vec_per_row;
+        const uint64_t r = row % 128, j = (row / 128) % (i_local / 64), e = row / 128 / (i_local / 64);
+        const ProjSrc& s = r < 64 ? gate : up;
+        const uint64_t srow = s.row0 + j * 64 + (r & 63);
+        reinterpret_cast<uint4*>(dst)[i] =
+            *reinterpret_cast<const uint4*>(s.payload + e * s.expert_stride_p + srow * s.row_stride_p + s.col0_p + v * 16);
+    }
+}
+// s13[e][j][c][512]. One byte per thread; byte 255 (reserved) is stored as 254:
+// the checkpoint contract clamps it to 2^127 (crates/mimo26-expert/src/mxfp4.rs:24-29).
+__global__ void __launch_bounds__(256) prep_s13_kernel(ProjSrc gate, ProjSrc up, int i_local, uint8_t* __restrict__ dst,
+                                                       uint32_t* __restrict__ abnormal) {
+    const uint64_t chunks = kHidden / kChunkK;
+    const uint64_t total = uint64_t(kExperts) * (i_local / 64) * chunks * kScaleBlockBytes;
+    uint32_t odd = 0;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint32_t o = uint32_t(i % kScaleBlockBytes);
+        const uint64_t c = (i / kScaleBlockBytes) % chunks, j = (i / kScaleBlockBytes / chunks) % (i_local / 64);
+        const uint64_t e = i / kScaleBlockBytes / chunks / (i_local / 64);
+        const uint32_t r = (o >> 4) + 32u * ((o >> 2) & 3u), kb = o & 3u;
+        const ProjSrc& s = r < 64 ? gate : up;
+        const uint64_t srow = s.row0 + j * 64 + (r & 63);
+        uint8_t b = s.scales[e * s.expert_stride_s + srow * s.row_stride_s + s.col0_s + c * 4 + kb];
+        if (b < 2 || b > 252) odd = 1;
+        dst[i] = b == 255 ? 254 : b;
+    }
+    if (odd) atomicOr(abnormal, 1u);
+}
+// w2[e][h][i_local/2]: this rank's K slice of every down_proj row.
+__global__ void __launch_bounds__(256) prep_w2_kernel(ProjSrc down, int i_local, uint8_t* __restrict__ dst) {
+    const uint64_t vec_per_row = uint64_t(i_local) / 2 / 16;
+    const uint64_t total = uint64_t(kExperts) * kHidden * vec_per_row;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint64_t v = i % vec_per_row, h = (i / vec_per_row) % kHidden, e = i / vec_per_row / kHidden;
+        reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(
+            down.payload + e * down.expert_stride_p + (down.row0 + h) * down.row_stride_p + down.col0_p + v * 16);
+    }
+}
+// s2[e][h/128][c][512].
+__global__ void __launch_bounds__(256) prep_s2_kernel(ProjSrc down, int i_local, uint8_t* __restrict__ dst,
+                                                      uint32_t* __restrict__ abnormal) {
+    const uint64_t chunks = uint64_t(i_local) / kChunkK, mts = kHidden / kTileM;
+    const uint64_t total = uint64_t(kExperts) * mts * chunks * kScaleBlockBytes;
+    uint32_t odd = 0;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint32_t o = uint32_t(i % kScaleBlockBytes);
+        const uint64_t c = (i / kScaleBlockBytes) % chunks, mt = (i / kScaleBlockBytes / chunks) % mts;
+        const uint64_t e = i / kScaleBlockBytes / chunks / mts;
+        const uint32_t r = (o >> 4) + 32u * ((o >> 2) & 3u), kb = o & 3u;
+        uint8_t b = down.scales[e * down.expert_stride_s + (down.row0 + mt * 128 + r) * down.row_stride_s + down.col0_s + c * 4 + kb];
+        if (b < 2 || b > 252) odd = 1;
+        dst[i] = b == 255 ? 254 : b;
+    }
+    if (odd) atomicOr(abnormal, 1u);
+}
+
+}  // namespace m26b

@@ -1,0 +1,255 @@
+// Grouped block-scaled GEMM for the expert FFN on tcgen05 (sm_100a).
+//
+// Both projections run the same main loop with the weights as the MMA "A"
+// operand and the routed tokens as "B":
+//     D[weight row, token] = sum_k E2M1(w) 2^sw  *  E4M3(x) 2^sx
+// A work item is (token tile of one expert) x (128 weight rows). Weight rows
+// are the tcgen05 M = 128; the token count of the tile is the MMA N (a multiple
+// of 16, up to 240), so one to two routed rows per expert at decode do not pad
+// to a 128-row tile, and a few hundred rows per expert at prefill fill N.
+//
+//   producer warp : TMA loads per 128-wide K chunk - the 4-bit weight tile
+//                   (unpacked to 8-bit containers by the 16U4_ALIGN16B tensor
+//                   map), the E4M3 token rows, and the two UE8M0 scale blocks.
+//   MMA warp      : copies the scale blocks to tensor memory (tcgen05.cp) and
+//                   issues 4 x tcgen05.mma kind::mxf8f6f4.block_scale per chunk
+//                   into one of two accumulator buffers in tensor memory.
+//   4 epilogue    : drain the other accumulator buffer.
+//     warps         FC1: lanes 0..63 hold gate, 64..127 up of the same 64
+//                   features; the halves meet through shared memory, then
+//                   SiLU(gate)*up and the e4m3fn-k32-v1 quantiser run in
+//                   registers (one warp = one K32 block per token) and the
+//                   quantised intermediate plus its scale bytes are stored in
+//                   the layout FC2's loads want.
+//                   FC2: FP32 rows are stored at their original route index.
+//
+// Reference behaviour: FC1 crates/mimo26-expert/kernels/b1/grouped.cu:71-113,
+// quantiser kernels/b1/quant_v1.cuh:32-100, FC2 grouped.cu:136-154 and
+// kernels/b1/connected.cu:48-79 (unweighted rows in original route order).
+#pragma once
+#include "sm100_ptx.cuh"
+#include "layout.cuh"
+#include "codec.cuh"
+
+namespace m26b {
+
+constexpr int kGemmThreads = 192;
+constexpr int kAccStride = 256;     // tensor-memory columns between the two accumulator buffers
+constexpr int kSfaCol0 = 240, kSfbCol0 = 244;          // scale columns, slot 0 (slot 1 = +256)
+constexpr uint32_t kTmemCols = 512;
+
+enum { kModeFc1 = 1, kModeFc2 = 2 };
+
+struct GemmArgs {
+    const TokenTile* tiles;
+    const WorkItem* items;
+    const uint32_t* n_items;
+    const uint8_t* sfa;         // weight scale blocks [E][m_tiles][k_chunks][512]
+    const uint8_t* sfb;         // token scale blocks  [tile][k_chunks][2][512]
+    int m_tiles;                // 128-row weight tiles per expert
+    int k_chunks;               // K / 128
+    uint32_t* fault;            // one word, OR of fault codes
+    // FC1 epilogue
+    uint8_t* mid_q;             // [grouped rows][i_local] E4M3
+    uint8_t* mid_sf;            // scale blocks for FC2 [tile][i_local/128][2][512]
+    float* mid_f32;             // optional FP32 copy of silu(gate)*up, same indexing as mid_q
+    int i_local;
+    // FC2 epilogue
+    float* y;                   // [routes][4096] FP32, original route order
+    const int32_t* original_routes;
+};
+
+template <int B_ROWS, int STAGES>
+struct GemmSmem {
+    alignas(1024) uint8_t a[STAGES][kTileM * 128];
+    alignas(1024) uint8_t b[STAGES][B_ROWS * 128];
+    alignas(16) uint8_t sfa[STAGES][kScaleBlockBytes];
+    alignas(16) uint8_t sfb[STAGES][2 * kScaleBlockBytes];
+    alignas(16) float xbuf[2][2][16][64];
+    uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+// E-ACT-CR32 activation: no positive exponential is evaluated, ordered FP32 ops.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    const float e = expf(-fabsf(g));
+    const float d = __fadd_rn(1.0f, e);
+    const float s = g >= 0.0f ? __fdiv_rn(g, d) : __fdiv_rn(__fmul_rn(g, e), d);
+    return __fmul_rn(s, u);
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int MODE, int B_ROWS, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const GemmArgs p) {
+    using Smem = GemmSmem<B_ROWS, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 4); }
+        s.abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tb = s.tmem_base;
+    const uint32_t n_items = *p.n_items;
+    volatile uint32_t* abort_flag = &s.abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (elect_one()) {
+            tma_prefetch_desc(&map_w);
+            tma_prefetch_desc(&map_x);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
+                const WorkItem wi = p.items[it];
+                const TokenTile tt = p.tiles[wi.tile];
+                const int w_row = (tt.expert * p.m_tiles + wi.m_tile) * kTileM;
+                const uint8_t* sfa_g = p.sfa + size_t(tt.expert * p.m_tiles + wi.m_tile) * p.k_chunks * kScaleBlockBytes;
+                const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * 2 * kScaleBlockBytes;
+                const int n_blk = tt.n_mma > 128 ? 2 : 1;
+                const uint32_t tx = kTileM * 64 + tt.n_mma * 128 + kScaleBlockBytes * (1 + n_blk);
+                for (int c = 0; c < p.k_chunks; ++c) {
+                    if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(&s.full[stage], tx);
+                    tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
+                    for (int r = 0; r < tt.n_mma; r += 16)
+                        tma_load_2d(s.b[stage] + r * 128, &map_x, c * kChunkK, tt.row_base + r, &s.full[stage]);
+                    bulk_load(s.sfa[stage], sfa_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
+                    bulk_load(s.sfb[stage], sfb_g + size_t(c) * 2 * kScaleBlockBytes, kScaleBlockBytes * n_blk,
+                              &s.full[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issue
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0, local = 0, sf_slot = 0;
+            bool ok = true;
+            for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
+                const TokenTile tt = p.tiles[p.items[it].tile];
+                const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
+                if (!mbar_wait(&s.acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tb + acc * kAccStride;
+                const int n_blk = tt.n_mma > 128 ? 2 : 1;
+                for (int c = 0; c < p.k_chunks; ++c) {
+                    if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    // consecutive chunks alternate between two scale slots in tensor memory
+                    const uint32_t slot = sf_slot * kAccStride;
+                    sf_slot ^= 1u;
+                    const uint32_t t_sfa = tb + slot + kSfaCol0, t_sfb = tb + slot + kSfbCol0;
+                    tc_cp_scales(t_sfa, desc_scale_block(smem_u32(s.sfa[stage])));
+                    tc_cp_scales(t_sfb, desc_scale_block(smem_u32(s.sfb[stage])));
+                    if (n_blk == 2) tc_cp_scales(t_sfb + 4, desc_scale_block(smem_u32(s.sfb[stage]) + kScaleBlockBytes));
+                    const uint32_t a0 = smem_u32(s.a[stage]), b0 = smem_u32(s.b[stage]);
+#pragma unroll
+                    for (uint32_t kb = 0; kb < 4; ++kb)
+                        tc_mma_mx(d_tmem, desc_sw128(a0 + kb * 32), desc_sw128(b0 + kb * 32),
+                                  idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), kb, kb), t_sfa, t_sfb,
+                                  (c | int(kb)) ? 1u : 0u);
+                    tc_commit(&s.empty[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(&s.acc_full[acc]);
+            }
+            if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t q = uint32_t(warp) & 3u;       // tensor-memory lane quadrant this warp may read
+        uint32_t local = 0;
+        bool ok = true;
+        for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
+            const WorkItem wi = p.items[it];
+            const TokenTile tt = p.tiles[wi.tile];
+            const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
+            mbar_wait(&s.acc_full[acc], acc_phase, abort_flag);
+            // The four epilogue warps must agree on leaving: they meet at a named barrier below.
+            epi_bar_sync();
+            if (*abort_flag) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_acc = tb + acc * kAccStride + ((q * 32u) << 16);
+            if constexpr (MODE == kModeFc2) {
+                float* ybase = p.y + size_t(wi.m_tile) * kTileM + q * 32u + lane;
+                for (int c0 = 0; c0 < tt.n_mma; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(t_acc + uint32_t(c0), r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = c0 + j;
+                        if (t < tt.n_valid) {
+                            const int32_t route = p.original_routes[tt.row_base + t];
+                            ybase[size_t(route) * kHidden] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            } else {
+                const bool is_gate = q < 2u;
+                const uint32_t fblk = q & 1u;                    // which 32-feature block of the 64-feature tile
+                const uint32_t f = fblk * 32u + lane;
+                const int feat0 = wi.m_tile * 64 + int(fblk) * 32;   // first feature of this warp's K32 block
+                const int blk = feat0 / 32, cch = blk >> 2, kb = blk & 3;
+                uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + cch) * 2 * kScaleBlockBytes;
+                uint32_t par = 0;
+                uint32_t fault = 0;
+                for (int c0 = 0; c0 < tt.n_mma; c0 += 32, par ^= 1u) {
+                    uint32_t lo[16], hi[16];
+                    tmem_ld16(t_acc + uint32_t(c0), lo);
+                    tmem_ld16(t_acc + uint32_t(c0 + 16), hi);
+                    tmem_wait_ld();
+                    // gate warps keep columns c0..c0+15 and hand the next 16 to the up warps; up warps the reverse
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        s.xbuf[par][is_gate ? 0 : 1][j][f] = __uint_as_float(is_gate ? hi[j] : lo[j]);
+                    epi_bar_sync();
+                    const int t0 = c0 + (is_gate ? 0 : 16);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + j;
+                        if (t >= tt.n_valid) continue;   // warp-uniform
+                        const float other = s.xbuf[par][is_gate ? 1 : 0][j][f];
+                        const float g = is_gate ? __uint_as_float(lo[j]) : other;
+                        const float u = is_gate ? other : __uint_as_float(hi[j]);
+                        const float h = silu_mul(g, u);
+                        const size_t row = size_t(tt.row_base + t);
+                        if (p.mid_f32) p.mid_f32[row * p.i_local + feat0 + lane] = h;
+                        const uint32_t bits = __float_as_uint(h);
+                        const uint32_t amax = __reduce_max_sync(0xffffffffu, bits & 0x7fffffffu);
+                        if (amax >= 0x7f800000u) { fault |= kFaultQuantNonfinite; continue; }
+                        const int k = quant_v1_scale_exp(amax);
+                        const uint32_t code = quant_v1_payload(bits, k);
+                        if (__any_sync(0xffffffffu, !quant_v1_finite(code, k))) { fault |= kFaultQuantOverflow; continue; }
+                        p.mid_q[row * p.i_local + feat0 + lane] = uint8_t(code);
+                        if (lane == 0)
+                            sf_tile[(t >> 7) * kScaleBlockBytes + scale_block_offset(t & 127, kb)] = uint8_t(k + 127);
+                    }
+                }
+                if (fault && lane == 0) atomicOr(p.fault, fault);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.acc_empty[acc]);
+        }
+        if (!ok && lane == 0) atomicOr(p.fault, uint32_t(kFaultPipeline));
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tb, kTmemCols);
+}
+
+}  // namespace m26b

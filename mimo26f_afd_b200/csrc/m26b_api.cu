@@ -1,0 +1,609 @@
+// C ABI and host orchestration of the B200 routed-expert FFN.
+// Declarations and the reference interfaces they replace: include/m26b_expert.h.
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <chrono>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "../../include/m26b_expert.h"
+#include "layout.cuh"
+#include "ffn_kernels.cuh"
+#include "gemm_mx.cuh"
+
+using namespace m26b;
+
+namespace {
+
+constexpr uint32_t kMaxPassRows = 16384;   // token rows per pass of the pipeline (bounds scratch memory)
+
+void set_err(char* err, size_t len, const char* what, cudaError_t e) {
+    if (err && len) std::snprintf(err, len, "%s: %s", what, cudaGetErrorString(e));
+}
+void set_msg(char* err, size_t len, const char* msg) {
+    if (err && len) std::snprintf(err, len, "%s", msg);
+}
+
+// Grow-only device buffer.
+struct Dev {
+    void* p = nullptr;
+    size_t n = 0;
+    cudaError_t ensure(size_t bytes, bool* grew = nullptr) {
+        if (bytes <= n) return cudaSuccess;
+        if (p) cudaFree(p);
+        p = nullptr; n = 0;
+        const size_t want = bytes < 256 ? 256 : bytes;
+        const cudaError_t e = cudaMalloc(&p, want);
+        if (e == cudaSuccess) { n = want; if (grew) *grew = true; }
+        return e;
+    }
+    template <class T> T* as() const { return static_cast<T*>(p); }
+    ~Dev() { if (p) cudaFree(p); }
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+// 2-D K-major operand map: `cols` elements per row, 128-element x `box_rows` boxes, 128-byte swizzle.
+bool make_map(CUtensorMap* m, bool fp4, void* base, uint64_t cols, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    EncodeTiledFn f = encode_fn();
+    if (!f) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t es[2] = {1, 1};
+    return f(m, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box,
+             es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MODE, int B_ROWS, int STAGES>
+cudaError_t launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
+    const int smem = int(sizeof(GemmSmem<B_ROWS, STAGES>)) + 1024;
+    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    gemm_mx_kernel<MODE, B_ROWS, STAGES><<<ctas, kGemmThreads, smem, st>>>(mw, mx, a);
+    return cudaGetLastError();
+}
+template <int MODE>
+cudaError_t launch_gemm_class(uint32_t rows, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int ctas,
+                              cudaStream_t st) {
+    if (rows <= 32) return launch_gemm<MODE, 32, 9>(mw, mx, a, ctas, st);
+    if (rows <= 128) return launch_gemm<MODE, 128, 6>(mw, mx, a, ctas, st);
+    return launch_gemm<MODE, 256, 4>(mw, mx, a, ctas, st);
+}
+
+// Device status block of one pass: PlanMeta then four fault words.
+struct Status {
+    PlanMeta meta;
+    uint32_t fault_input, fault_fc1, fault_fc2, fault_reduce;
+    uint32_t pad[4];
+};
+static_assert(sizeof(Status) == 64, "status block is 64 bytes");
+
+}  // namespace
+
+struct m26b_layer {
+    uint8_t *w13 = nullptr, *s13 = nullptr, *w2 = nullptr, *s2 = nullptr, *resident = nullptr;
+    int i_local = 0;
+    uint32_t tp_rank = 0, tp_size = 1;
+    bool all_normal = false;
+    int device = 0;
+    CUtensorMap map_w13, map_w2;
+};
+
+struct m26b_scratch {
+    cudaStream_t st = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr, ea = nullptr, ec = nullptr;
+    int device = 0, sms = 0;
+    uint32_t debug = 0;
+    Dev xq, xs, iw, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
+        partial, bf16, status, gather;
+    CUtensorMap map_x, map_mid;
+    void* map_x_base = nullptr; void* map_mid_base = nullptr;
+    uint64_t map_x_rows = 0, map_mid_rows = 0; int map_mid_cols = 0;
+    std::vector<uint8_t> hiw;
+    Status* hstatus = nullptr;       // pinned
+    // last pass
+    uint32_t last_rows = 0; int last_i_local = 0; bool pending = false; uint32_t n_status = 0;
+    const int32_t* last_ids = nullptr; const uint8_t* last_xq = nullptr; const uint8_t* last_xs = nullptr;
+};
+
+namespace {
+
+int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, uint32_t tp_rank, uint32_t tp_size,
+                  m26b_layer** out, char* err, size_t errlen) {
+    const int i_local = kInter / int(tp_size);
+    auto* L = new m26b_layer();
+    L->i_local = i_local; L->tp_rank = tp_rank; L->tp_size = tp_size;
+    cudaGetDevice(&L->device);
+    const size_t w13_bytes = size_t(kExperts) * 2 * i_local * (kHidden / 2);
+    const size_t s13_bytes = size_t(kExperts) * 2 * i_local * (kHidden / kBlockK);
+    const size_t w2_bytes = size_t(kExperts) * kHidden * (i_local / 2);
+    const size_t s2_bytes = size_t(kExperts) * kHidden * (i_local / kBlockK);
+    cudaError_t e;
+    uint32_t* flag = nullptr;
+    auto fail = [&](const char* what, cudaError_t ce, int rc) {
+        set_err(err, errlen, what, ce);
+        if (flag) cudaFree(flag);
+        m26b_layer_free(L);
+        return rc;
+    };
+    if ((e = cudaMalloc(&L->w13, w13_bytes)) != cudaSuccess || (e = cudaMalloc(&L->s13, s13_bytes)) != cudaSuccess ||
+        (e = cudaMalloc(&L->w2, w2_bytes)) != cudaSuccess || (e = cudaMalloc(&L->s2, s2_bytes)) != cudaSuccess ||
+        (e = cudaMalloc(&L->resident, kExperts)) != cudaSuccess || (e = cudaMalloc(&flag, 4)) != cudaSuccess)
+        return fail("m26b layer alloc", e, 2);
+    if ((e = cudaMemset(flag, 0, 4)) != cudaSuccess || (e = cudaMemset(L->resident, 1, kExperts)) != cudaSuccess)
+        return fail("m26b layer metadata", e, 2);
+    prep_w13_kernel<<<2048, 256>>>(gate, up, i_local, L->w13);
+    prep_s13_kernel<<<2048, 256>>>(gate, up, i_local, L->s13, flag);
+    prep_w2_kernel<<<2048, 256>>>(down, i_local, L->w2);
+    prep_s2_kernel<<<2048, 256>>>(down, i_local, L->s2, flag);
+    uint32_t h = 1;
+    if ((e = cudaGetLastError()) != cudaSuccess || (e = cudaMemcpy(&h, flag, 4, cudaMemcpyDeviceToHost)) != cudaSuccess ||
+        (e = cudaDeviceSynchronize()) != cudaSuccess)
+        return fail("m26b layer prepare", e, 2);
+    cudaFree(flag); flag = nullptr;
+    L->all_normal = h == 0;
+    if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(kExperts) * 2 * i_local, kHidden / 2, kTileM) ||
+        !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(kExperts) * kHidden, uint64_t(i_local) / 2, kTileM)) {
+        set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight operands");
+        m26b_layer_free(L);
+        return 2;
+    }
+    *out = L;
+    return 0;
+}
+
+ProjSrc canonical_proj(const uint8_t* base, uint64_t image, uint64_t payload_off, uint64_t scale_off, uint64_t in_cols) {
+    ProjSrc s{};
+    s.payload = base + payload_off; s.scales = base + scale_off;
+    s.expert_stride_p = s.expert_stride_s = image;
+    s.row_stride_p = in_cols / 2; s.row_stride_s = in_cols / kBlockK;
+    return s;
+}
+
+#define M26B_CK(expr, what) do { if ((e = (expr)) != cudaSuccess) { set_err(err, errlen, what, e); return 2; } } while (0)
+
+// Buffers of one pass of `rows` tokens on a layer of width i_local.
+int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, char* err, size_t errlen) {
+    cudaError_t e;
+    const size_t routes = size_t(rows) * kTopK;
+    const LaunchClass lc = launch_class(rows);
+    const size_t tiles_max = routes / lc.max_n + kExperts;
+    const size_t rows_cap = routes + 256;
+    if (own_input) {
+        M26B_CK(S->xq.ensure(size_t(rows) * kHidden), "m26b x alloc");
+        M26B_CK(S->xs.ensure(size_t(rows) * (kHidden / kBlockK)), "m26b xs alloc");
+    }
+    M26B_CK(S->inverse.ensure(routes * 4), "m26b inverse alloc");
+    M26B_CK(S->original.ensure(routes * 4), "m26b original alloc");
+    M26B_CK(S->gweights.ensure(routes * 4), "m26b gweights alloc");
+    M26B_CK(S->experts.ensure(kExperts * sizeof(ExpertPlan)), "m26b experts alloc");
+    M26B_CK(S->tiles.ensure(tiles_max * sizeof(TokenTile)), "m26b tiles alloc");
+    M26B_CK(S->items1.ensure(tiles_max * (i_local / 64) * sizeof(WorkItem)), "m26b fc1 items alloc");
+    M26B_CK(S->items2.ensure(tiles_max * (kHidden / kTileM) * sizeof(WorkItem)), "m26b fc2 items alloc");
+    M26B_CK(S->sfb1.ensure(tiles_max * (kHidden / kChunkK) * 2 * kScaleBlockBytes), "m26b sfb alloc");
+    M26B_CK(S->mid_sf.ensure(tiles_max * (i_local / kChunkK) * 2 * kScaleBlockBytes), "m26b mid scale alloc");
+    if (S->debug & 1u) M26B_CK(S->mid_f32.ensure(rows_cap * i_local * 4), "m26b mid f32 alloc");
+    M26B_CK(S->y.ensure(routes * kHidden * 4), "m26b y alloc");
+    M26B_CK(S->partial.ensure(size_t(rows) * kHidden * 4), "m26b partial alloc");
+    M26B_CK(S->bf16.ensure(size_t(rows) * kHidden * 2), "m26b bf16 alloc");
+    M26B_CK(S->status.ensure(sizeof(Status) * 64), "m26b status alloc");
+    M26B_CK(S->x_perm.ensure(rows_cap * kHidden), "m26b x_perm alloc");
+    M26B_CK(S->mid_q.ensure(rows_cap * i_local), "m26b mid alloc");
+    const uint64_t xr = S->x_perm.n / kHidden, mr = S->mid_q.n / i_local;
+    if (S->map_x_base != S->x_perm.p || S->map_x_rows != xr) {
+        if (!make_map(&S->map_x, false, S->x_perm.p, kHidden, xr, kHidden, 16)) {
+            set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the token operand");
+            return 2;
+        }
+        S->map_x_base = S->x_perm.p; S->map_x_rows = xr;
+    }
+    if (S->map_mid_base != S->mid_q.p || S->map_mid_rows != mr || S->map_mid_cols != i_local) {
+        if (!make_map(&S->map_mid, false, S->mid_q.p, uint64_t(i_local), mr, uint64_t(i_local), 16)) {
+            set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the intermediate operand");
+            return 2;
+        }
+        S->map_mid_base = S->mid_q.p; S->map_mid_rows = mr; S->map_mid_cols = i_local;
+    }
+    return 0;
+}
+
+// Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine.
+int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const uint8_t* xs, const int32_t* ids,
+                 const float* w, uint32_t rows, uint16_t* bf16_out, float* partial_out, Status* status,
+                 cudaStream_t st, bool events, char* err, size_t errlen) {
+    cudaError_t e;
+    const uint32_t routes = rows * kTopK;
+    const LaunchClass lc = launch_class(rows);
+    const int mt1 = L->i_local / 64, mt2 = kHidden / kTileM;
+    M26B_CK(cudaMemsetAsync(status, 0, sizeof(Status), st), "m26b status clear");
+    if (events) M26B_CK(cudaEventRecord(S->e0, st), "m26b event 0");
+    PlanOut po{S->inverse.as<int32_t>(), S->original.as<int32_t>(), S->gweights.as<float>(), S->experts.as<ExpertPlan>(),
+               S->tiles.as<TokenTile>(), S->items1.as<WorkItem>(), S->items2.as<WorkItem>(), &status->meta};
+    plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, po);
+    M26B_CK(cudaGetLastError(), "m26b plan launch");
+    permute_kernel<<<routes < 65535u * 8u ? routes : 65535u * 8u, 256, 0, st>>>(
+        xq, xs, ids, S->original.as<int32_t>(), S->experts.as<ExpertPlan>(), &status->meta, routes,
+        S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input);
+    M26B_CK(cudaGetLastError(), "m26b permute launch");
+    GemmArgs a{};
+    a.tiles = S->tiles.as<TokenTile>();
+    a.i_local = L->i_local;
+    a.mid_q = S->mid_q.as<uint8_t>();
+    a.mid_sf = S->mid_sf.as<uint8_t>();
+    a.mid_f32 = (S->debug & 1u) ? S->mid_f32.as<float>() : nullptr;
+    a.y = S->y.as<float>();
+    a.original_routes = S->original.as<int32_t>();
+    // FC1: weights w13 (K = hidden), tokens x_perm
+    a.items = S->items1.as<WorkItem>(); a.n_items = &status->meta.n_items_fc1;
+    a.sfa = L->s13; a.sfb = S->sfb1.as<uint8_t>(); a.m_tiles = mt1; a.k_chunks = kHidden / kChunkK;
+    a.fault = &status->fault_fc1;
+    M26B_CK(launch_gemm_class<kModeFc1>(rows, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
+    if (events) M26B_CK(cudaEventRecord(S->ea, st), "m26b event a");
+    // FC2: weights w2 (K = i_local), tokens mid_q
+    a.items = S->items2.as<WorkItem>(); a.n_items = &status->meta.n_items_fc2;
+    a.sfa = L->s2; a.sfb = S->mid_sf.as<uint8_t>(); a.m_tiles = mt2; a.k_chunks = L->i_local / kChunkK;
+    a.fault = &status->fault_fc2;
+    M26B_CK(launch_gemm_class<kModeFc2>(rows, L->map_w2, S->map_mid, a, S->sms, st), "m26b fc2 launch");
+    if (events) M26B_CK(cudaEventRecord(S->ec, st), "m26b event c");
+    const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
+    const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
+    route_reduce_kernel<<<blocks, 256, 0, st>>>(S->y.as<float>(), w, rows, partial_out, bf16_out, &status->fault_reduce);
+    M26B_CK(cudaGetLastError(), "m26b reduce launch");
+    if (events) M26B_CK(cudaEventRecord(S->e1, st), "m26b event 1");
+    S->last_rows = rows; S->last_i_local = L->i_local; S->last_ids = ids; S->last_xq = xq; S->last_xs = xs;
+    return 0;
+}
+
+int decode_status(const Status* hs, uint32_t n, char* err, size_t errlen) {
+    for (uint32_t i = 0; i < n; ++i) {
+        const Status& s = hs[i];
+        if (s.meta.fault) { set_msg(err, errlen, "m26b plan: invalid routes (id/residency/weight/duplicate)"); return 3; }
+    }
+    for (uint32_t i = 0; i < n; ++i) {
+        const Status& s = hs[i];
+        const uint32_t words[4] = {s.fault_input, s.fault_fc1, s.fault_fc2, s.fault_reduce};
+        const char* names[4] = {"input", "fc1/quantizer", "fc2", "reduce"};
+        for (int k = 0; k < 4; ++k)
+            if (words[k]) {
+                if (err && errlen) std::snprintf(err, errlen, "m26b %s fault %u (pass %u, tiles %u)", names[k], words[k], i, s.meta.n_tiles);
+                return 4;
+            }
+    }
+    return 0;
+}
+
+bool device_ok(int dev_of_handle, char* err, size_t errlen) {
+    int d = -1;
+    if (cudaGetDevice(&d) != cudaSuccess || d != dev_of_handle) {
+        set_msg(err, errlen, "m26b: handle used on a different CUDA device than it was created on");
+        return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* m26b_version(void) { return "m26b-expert 0.1 sm_100a"; }
+
+int m26b_layer_new_tp(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t tp_rank, uint32_t tp_size,
+                      m26b_layer** out, char* err, size_t errlen) {
+    if (!out || !canonical_dev || !(tp_size == 1 || tp_size == 2 || tp_size == 4 || tp_size == 8) || tp_rank >= tp_size) {
+        set_msg(err, errlen, "m26b layer: bad canonical extent/rank");
+        return 1;
+    }
+    const uint64_t il = kInter / tp_size;
+    const uint64_t gp = il * (kHidden / 2), gs = il * (kHidden / kBlockK);
+    const uint64_t dp = uint64_t(kHidden) * (il / 2), ds = uint64_t(kHidden) * (il / kBlockK);
+    const uint64_t image = 2 * (gp + gs) + dp + ds;
+    if (canonical_bytes != image * kExperts) {
+        set_msg(err, errlen, "m26b layer: bad canonical extent/rank");
+        return 1;
+    }
+    const ProjSrc gate = canonical_proj(canonical_dev, image, 0, gp, kHidden);
+    const ProjSrc up = canonical_proj(canonical_dev, image, gp + gs, gp + gs + gp, kHidden);
+    const ProjSrc down = canonical_proj(canonical_dev, image, 2 * (gp + gs), 2 * (gp + gs) + dp, il);
+    return prepare_layer(gate, up, down, tp_rank, tp_size, out, err, errlen);
+}
+
+int m26b_layer_new(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t rank, m26b_layer** out, char* err,
+                   size_t errlen) {
+    return m26b_layer_new_tp(canonical_dev, canonical_bytes, rank, 4, out, err, errlen);
+}
+
+int m26b_layer_new_from_checkpoint(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w,
+                                   const uint8_t* up_s, const uint8_t* down_w, const uint8_t* down_s,
+                                   uint32_t tp_rank, uint32_t tp_size, m26b_layer** out, char* err, size_t errlen) {
+    if (!out || !gate_w || !gate_s || !up_w || !up_s || !down_w || !down_s ||
+        !(tp_size == 1 || tp_size == 2 || tp_size == 4 || tp_size == 8) || tp_rank >= tp_size) {
+        set_msg(err, errlen, "m26b layer: bad checkpoint tensors/rank");
+        return 1;
+    }
+    const uint64_t il = kInter / tp_size;
+    ProjSrc gate{}, up{}, down{};
+    gate.payload = gate_w; gate.scales = gate_s;
+    gate.expert_stride_p = uint64_t(kInter) * (kHidden / 2); gate.expert_stride_s = uint64_t(kInter) * (kHidden / kBlockK);
+    gate.row_stride_p = kHidden / 2; gate.row_stride_s = kHidden / kBlockK;
+    gate.row0 = il * tp_rank;
+    up = gate; up.payload = up_w; up.scales = up_s;
+    down.payload = down_w; down.scales = down_s;
+    down.expert_stride_p = uint64_t(kHidden) * (kInter / 2); down.expert_stride_s = uint64_t(kHidden) * (kInter / kBlockK);
+    down.row_stride_p = kInter / 2; down.row_stride_s = kInter / kBlockK;
+    down.col0_p = il * tp_rank / 2; down.col0_s = il * tp_rank / kBlockK;
+    return prepare_layer(gate, up, down, tp_rank, tp_size, out, err, errlen);
+}
+
+int m26b_layer_all_normal(const m26b_layer* L) { return L && L->all_normal ? 1 : 0; }
+int m26b_layer_i_local(const m26b_layer* L) { return L ? L->i_local : 0; }
+
+void m26b_layer_free(m26b_layer* L) {
+    if (!L) return;
+    cudaFree(L->w13); cudaFree(L->s13); cudaFree(L->w2); cudaFree(L->s2); cudaFree(L->resident);
+    delete L;
+}
+
+int m26b_scratch_new(m26b_scratch** out, char* err, size_t errlen) {
+    if (!out) { set_msg(err, errlen, "m26b scratch: null out"); return 1; }
+    auto* S = new m26b_scratch();
+    cudaError_t e;
+    cudaDeviceProp prop;
+    if ((e = cudaGetDevice(&S->device)) != cudaSuccess || (e = cudaGetDeviceProperties(&prop, S->device)) != cudaSuccess) {
+        set_err(err, errlen, "m26b scratch device", e);
+        delete S;
+        return 2;
+    }
+    if (prop.major != 10) {
+        set_msg(err, errlen, "m26b scratch: this library is built for sm_100a (B200) only; no other device and no CPU path exists");
+        delete S;
+        return 2;
+    }
+    S->sms = prop.multiProcessorCount;
+    if ((e = cudaStreamCreateWithFlags(&S->st, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreate(&S->e0)) != cudaSuccess || (e = cudaEventCreate(&S->e1)) != cudaSuccess ||
+        (e = cudaEventCreate(&S->ea)) != cudaSuccess || (e = cudaEventCreate(&S->ec)) != cudaSuccess ||
+        (e = cudaMallocHost(reinterpret_cast<void**>(&S->hstatus), sizeof(Status) * 64)) != cudaSuccess) {
+        set_err(err, errlen, "m26b scratch stream/events", e);
+        m26b_scratch_free(S);
+        return 2;
+    }
+    *out = S;
+    return 0;
+}
+
+void m26b_scratch_free(m26b_scratch* S) {
+    if (!S) return;
+    if (S->e0) cudaEventDestroy(S->e0);
+    if (S->e1) cudaEventDestroy(S->e1);
+    if (S->ea) cudaEventDestroy(S->ea);
+    if (S->ec) cudaEventDestroy(S->ec);
+    if (S->st) cudaStreamDestroy(S->st);
+    if (S->hstatus) cudaFreeHost(S->hstatus);
+    delete S;
+}
+
+int m26b_scratch_set_debug(m26b_scratch* S, uint32_t flags) {
+    if (!S) return 1;
+    S->debug = flags;
+    return 0;
+}
+
+int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_t payload_pitch, const uint8_t* scales,
+             size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows, uint16_t* bf16_out, float* ms,
+             char* err, size_t errlen) {
+    if (!L || !S || !rows || rows > (1u << 20) || payload_pitch < kHidden || scales_pitch < kHidden / kBlockK || !payload ||
+        !scales || !ids || !weights || !bf16_out) {
+        set_msg(err, errlen, "m26b ffn: bad rows/handles/pitch");
+        return 1;
+    }
+    if (!device_ok(L->device, err, errlen) || !device_ok(S->device, err, errlen)) return 1;
+    cudaError_t e;
+    const auto t0 = std::chrono::steady_clock::now();
+    const size_t routes = size_t(rows) * kTopK;
+    const uint32_t pass_rows = rows < kMaxPassRows ? rows : kMaxPassRows;
+    const uint32_t passes = (rows + kMaxPassRows - 1) / kMaxPassRows;
+    if (passes > 64) { set_msg(err, errlen, "m26b ffn: bad rows/handles/pitch"); return 1; }
+    M26B_CK(S->xq.ensure(size_t(rows) * kHidden), "m26b x alloc");
+    M26B_CK(S->xs.ensure(size_t(rows) * (kHidden / kBlockK)), "m26b xs alloc");
+    M26B_CK(S->iw.ensure(routes * 8), "m26b ids/w alloc");
+    M26B_CK(S->gather.ensure(size_t(rows) * kHidden * 2), "m26b out alloc");
+    int rc = ensure_pass(S, pass_rows, L->i_local, false, err, errlen);
+    if (rc) return rc;
+    int32_t* const ids_d = S->iw.as<int32_t>();
+    float* const w_d = reinterpret_cast<float*>(S->iw.as<uint8_t>() + routes * 4);
+    M26B_CK(cudaMemcpy2DAsync(S->xq.p, kHidden, payload, payload_pitch, kHidden, rows, cudaMemcpyHostToDevice, S->st),
+            "m26b x upload");
+    M26B_CK(cudaMemcpy2DAsync(S->xs.p, kHidden / kBlockK, scales, scales_pitch, kHidden / kBlockK, rows,
+                              cudaMemcpyHostToDevice, S->st), "m26b xs upload");
+    S->hiw.resize(routes * 8);
+    std::memcpy(S->hiw.data(), ids, routes * 4);
+    std::memcpy(S->hiw.data() + routes * 4, weights, routes * 4);
+    M26B_CK(cudaMemcpyAsync(S->iw.p, S->hiw.data(), routes * 8, cudaMemcpyHostToDevice, S->st), "m26b ids/w upload");
+    uint16_t* const out_d = S->gather.as<uint16_t>();
+    for (uint32_t ps = 0; ps < passes; ++ps) {
+        const uint32_t r0 = ps * kMaxPassRows, n = rows - r0 < kMaxPassRows ? rows - r0 : kMaxPassRows;
+        rc = enqueue_pass(L, S, S->xq.as<uint8_t>() + size_t(r0) * kHidden, S->xs.as<uint8_t>() + size_t(r0) * (kHidden / kBlockK),
+                          ids_d + size_t(r0) * kTopK, w_d + size_t(r0) * kTopK, n, out_d + size_t(r0) * kHidden,
+                          S->partial.as<float>(), S->status.as<Status>() + ps, S->st, passes == 1, err, errlen);
+        if (rc) return rc;
+    }
+    M26B_CK(cudaMemcpyAsync(bf16_out, out_d, size_t(rows) * kHidden * 2, cudaMemcpyDeviceToHost, S->st), "m26b bf16 download");
+    M26B_CK(cudaMemcpyAsync(S->hstatus, S->status.p, sizeof(Status) * passes, cudaMemcpyDeviceToHost, S->st),
+            "m26b status download");
+    const auto t1 = std::chrono::steady_clock::now();
+    M26B_CK(cudaStreamSynchronize(S->st), "m26b compute sync");
+    S->pending = false;
+    rc = decode_status(S->hstatus, passes, err, errlen);
+    if (rc) return rc;
+    const auto t2 = std::chrono::steady_clock::now();
+    if (ms) {
+        float gpu_ms = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+        if (passes == 1) {
+            cudaEventElapsedTime(&gpu_ms, S->e0, S->e1);
+            cudaEventElapsedTime(&p1, S->e0, S->ea);
+            cudaEventElapsedTime(&p2, S->ea, S->ec);
+            cudaEventElapsedTime(&p3, S->ec, S->e1);
+        }
+        ms[0] = std::chrono::duration<float, std::milli>(t1 - t0).count();
+        ms[1] = gpu_ms;
+        ms[2] = std::chrono::duration<float, std::milli>(t2 - t1).count() - gpu_ms;
+        ms[3] = float(S->hstatus[0].meta.n_tiles);
+        ms[4] = p1; ms[5] = 0.f; ms[6] = p2; ms[7] = p3;
+    }
+    return 0;
+}
+
+int m26b_quantize_dev(const void* x, int x_dtype, uint64_t n_elems, int codec, uint8_t* payload, uint8_t* scales,
+                      uint32_t* fault_dev, void* stream, char* err, size_t errlen) {
+    if (!x || !payload || !scales || !fault_dev || n_elems % 32 || x_dtype < 0 || x_dtype > 1 || codec < 0 || codec > 1) {
+        set_msg(err, errlen, "m26b quantize: bad arguments");
+        return 1;
+    }
+    if (!n_elems) return 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint64_t threads = n_elems / 8;
+    const uint32_t blocks = uint32_t((threads + 255) / 256 < 148 * 16 ? (threads + 255) / 256 : 148 * 16);
+    if (x_dtype == 0 && codec == 0) quantize_rows_kernel<0, uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);
+    else if (x_dtype == 0) quantize_rows_kernel<1, uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);
+    else if (codec == 0) quantize_rows_kernel<0, float><<<blocks, 256, 0, st>>>(static_cast<const float*>(x), n_elems, payload, scales, fault_dev);
+    else quantize_rows_kernel<1, float><<<blocks, 256, 0, st>>>(static_cast<const float*>(x), n_elems, payload, scales, fault_dev);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b quantize launch", e); return 2; }
+    return 0;
+}
+
+int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtype, const uint8_t* x_scales, int codec,
+                 const int32_t* ids, const float* weights, uint32_t rows, uint16_t* bf16_out, float* partial_out,
+                 void* stream, char* err, size_t errlen) {
+    if (!L || !S || !rows || rows > kMaxPassRows || !x || !ids || !weights || !bf16_out || x_dtype < 0 || x_dtype > 2 ||
+        (x_dtype == 2 && !x_scales) || codec < 0 || codec > 1) {
+        set_msg(err, errlen, "m26b ffn: bad rows/handles/pitch");
+        return 1;
+    }
+    if (!device_ok(L->device, err, errlen) || !device_ok(S->device, err, errlen)) return 1;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : S->st;
+    int rc = ensure_pass(S, rows, L->i_local, x_dtype != 2, err, errlen);
+    if (rc) return rc;
+    Status* status = S->status.as<Status>();
+    const uint8_t* xq = static_cast<const uint8_t*>(x);
+    const uint8_t* xs = x_scales;
+    if (x_dtype != 2) {
+        // the quantiser's fault word is cleared with the status block, so clear first
+        cudaError_t e;
+        M26B_CK(cudaMemsetAsync(&status[1], 0, sizeof(Status), st), "m26b status clear");
+        rc = m26b_quantize_dev(x, x_dtype, uint64_t(rows) * kHidden, codec, S->xq.as<uint8_t>(), S->xs.as<uint8_t>(),
+                               &status[1].fault_input, st, err, errlen);
+        if (rc) return rc;
+        xq = S->xq.as<uint8_t>(); xs = S->xs.as<uint8_t>();
+    }
+    rc = enqueue_pass(L, S, xq, xs, ids, weights, rows, bf16_out, partial_out ? partial_out : nullptr, status, st, false,
+                      err, errlen);
+    if (rc) return rc;
+    S->pending = true;
+    S->n_status = x_dtype != 2 ? 2 : 1;
+    return 0;
+}
+
+int m26b_scratch_status(m26b_scratch* S, void* stream, char* err, size_t errlen) {
+    if (!S) { set_msg(err, errlen, "m26b status: null scratch"); return 1; }
+    cudaError_t e;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : S->st;
+    const uint32_t n = S->n_status ? S->n_status : 1;
+    M26B_CK(cudaMemcpyAsync(S->hstatus, S->status.p, sizeof(Status) * n, cudaMemcpyDeviceToHost, st), "m26b status download");
+    M26B_CK(cudaStreamSynchronize(st), "m26b status sync");
+    S->pending = false;
+    return decode_status(S->hstatus, n, err, errlen);
+}
+
+int m26b_route_reduce_dev(const float* y, const float* weights, uint32_t rows, float* partial, uint16_t* bf16,
+                          uint32_t* fault_dev, void* stream, char* err, size_t errlen) {
+    if (!y || !weights || !bf16 || !fault_dev) { set_msg(err, errlen, "m26b reduce: bad arguments"); return 1; }
+    if (!rows) return 0;
+    const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
+    const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
+    route_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(y, weights, rows, partial, bf16, fault_dev);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b reduce launch", e); return 2; }
+    return 0;
+}
+
+int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
+                      size_t errlen) {
+    if (!planes || n_ranks < 1 || n_ranks > 8 || !out) { set_msg(err, errlen, "m26b rank sum: bad arguments"); return 1; }
+    RankPlanes rp{};
+    for (int r = 0; r < n_ranks; ++r) {
+        if (!planes[r]) { set_msg(err, errlen, "m26b rank sum: bad arguments"); return 1; }
+        rp.p[r] = planes[r];
+    }
+    if (!n) return 0;
+    const uint64_t t = (n / 8 + 255) / 256 + 1;
+    rank_sum_kernel<<<uint32_t(t < 148 * 16 ? t : 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(rp, n_ranks, n, out);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b rank sum launch", e); return 2; }
+    return 0;
+}
+
+int m26b_scratch_peek(m26b_scratch* S, int what, void* host_dst, uint64_t bytes, char* err, size_t errlen) {
+    if (!S || !host_dst || !S->last_rows) { set_msg(err, errlen, "m26b peek: nothing to read"); return 1; }
+    cudaError_t e;
+    M26B_CK(cudaDeviceSynchronize(), "m26b peek sync");
+    const uint64_t rows = S->last_rows, routes = rows * kTopK, il = uint64_t(S->last_i_local);
+    const void* src = nullptr;
+    uint64_t have = 0;
+    switch (what) {
+        case M26B_PEEK_META: src = S->status.p; have = 32; break;
+        case M26B_PEEK_INVERSE: src = S->inverse.p; have = routes * 4; break;
+        case M26B_PEEK_ORIGINAL_ROUTES: src = S->original.p; have = routes * 4; break;
+        case M26B_PEEK_GROUPED_WEIGHTS: src = S->gweights.p; have = routes * 4; break;
+        case M26B_PEEK_X_PAYLOAD: src = S->last_xq; have = rows * kHidden; break;
+        case M26B_PEEK_X_SCALES: src = S->last_xs; have = rows * (kHidden / kBlockK); break;
+        case M26B_PEEK_MID_PAYLOAD: src = S->mid_q.p; have = routes * il; break;
+        case M26B_PEEK_MID_F32: src = (S->debug & 1u) ? S->mid_f32.p : nullptr; have = routes * il * 4; break;
+        case M26B_PEEK_Y: src = S->y.p; have = routes * kHidden * 4; break;
+        case M26B_PEEK_PARTIAL: src = S->partial.p; have = rows * kHidden * 4; break;
+        case M26B_PEEK_MID_SCALES: {
+            // gather the scale blocks back to row-major [routes][il/32] on the host
+            if (bytes != routes * (il / kBlockK)) { set_msg(err, errlen, "m26b peek: size mismatch"); return 1; }
+            std::vector<ExpertPlan> ep(kExperts);
+            std::vector<int32_t> orig(routes), hid(routes);
+            std::vector<uint8_t> blocks(S->mid_sf.n);
+            M26B_CK(cudaMemcpy(ep.data(), S->experts.p, kExperts * sizeof(ExpertPlan), cudaMemcpyDeviceToHost), "m26b peek copy");
+            M26B_CK(cudaMemcpy(orig.data(), S->original.p, routes * 4, cudaMemcpyDeviceToHost), "m26b peek copy");
+            M26B_CK(cudaMemcpy(hid.data(), S->last_ids, routes * 4, cudaMemcpyDeviceToHost), "m26b peek copy");
+            M26B_CK(cudaMemcpy(blocks.data(), S->mid_sf.p, S->mid_sf.n, cudaMemcpyDeviceToHost), "m26b peek copy");
+            uint8_t* dst = static_cast<uint8_t*>(host_dst);
+            const uint64_t chunks = il / kChunkK;
+            for (uint64_t g = 0; g < routes; ++g) {
+                const ExpertPlan& p = ep[hid[orig[g]]];
+                const uint64_t local = g - uint64_t(p.rbase), tile = uint64_t(p.tile_start) + local / uint64_t(p.width);
+                const uint64_t lr = local % uint64_t(p.width);
+                for (uint64_t b = 0; b < il / kBlockK; ++b)
+                    dst[g * (il / kBlockK) + b] = blocks[((tile * chunks + b / 4) * 2 + (lr >> 7)) * kScaleBlockBytes +
+                                                        scale_block_offset(int(lr & 127), int(b & 3))];
+            }
+            return 0;
+        }
+        default: break;
+    }
+    if (!src || bytes != have) { set_msg(err, errlen, "m26b peek: unknown buffer or size mismatch"); return 1; }
+    M26B_CK(cudaMemcpy(host_dst, src, bytes, cudaMemcpyDeviceToHost), "m26b peek copy");
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,216 @@
+"""Host-side mirror of the reference's expert-rank wrapper, over the C ABI.
+
+Names, argument meaning and error behaviour follow ``crates/mimo26-spark/src/b1.rs``:
+``Layer`` (b1.rs:57-92) owns one MoE layer's prepared weights, ``Scratch`` (b1.rs:94-120)
+the per-request device buffers and stream, ``ffn`` / ``ffn_strided`` (b1.rs:131-176) run one
+rank's expert FFN on host rows and return ``FfnStats`` (b1.rs:122-129). Failures raise
+``ExpertError`` carrying the library's message, where the Rust returns ``Err(String)``.
+
+Device-pointer entry points take anything with a ``data_ptr()`` (a torch CUDA tensor) or a
+plain integer address; torch is only the allocator here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _native
+
+H = 4096
+TOPK = 8
+
+
+class ExpertError(RuntimeError):
+    """A nonzero return of the C ABI: ``code`` 1 argument, 2 CUDA, 3 plan rejected, 4 numerical fault."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+def _check(rc: int, err) -> None:
+    if rc != 0:
+        raise ExpertError(rc, err.value.decode("utf-8", "replace"))
+
+
+def _ptr(x) -> int:
+    if x is None:
+        return 0
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    if isinstance(x, np.ndarray):
+        return int(x.ctypes.data)
+    raise TypeError(f"cannot take an address of {type(x)!r}")
+
+
+def version() -> str:
+    return _native.lib().m26b_version().decode()
+
+
+class Layer:
+    """One MoE layer's prepared operand image on the current CUDA device (b1.rs:57-92)."""
+
+    def __init__(self, handle: int):
+        self._h = C.c_void_p(handle)
+
+    @classmethod
+    def new(cls, canonical_dev, nbytes: int, rank: int) -> "Layer":
+        """From the reference's canonical-v2 TP4 rank image in device memory (b1.rs:72-84)."""
+        out, err = C.c_void_p(), C.create_string_buffer(256)
+        _check(_native.lib().m26b_layer_new(_ptr(canonical_dev), nbytes, rank, C.byref(out), err, 256), err)
+        return cls(out.value)
+
+    @classmethod
+    def new_tp(cls, canonical_dev, nbytes: int, tp_rank: int, tp_size: int) -> "Layer":
+        out, err = C.c_void_p(), C.create_string_buffer(256)
+        _check(_native.lib().m26b_layer_new_tp(_ptr(canonical_dev), nbytes, tp_rank, tp_size, C.byref(out), err, 256), err)
+        return cls(out.value)
+
+    @classmethod
+    def from_checkpoint(cls, gate_w, gate_s, up_w, up_s, down_w, down_s, tp_rank: int = 0, tp_size: int = 1) -> "Layer":
+        """From the six checkpoint tensors stacked over the 256 experts, all on the device."""
+        out, err = C.c_void_p(), C.create_string_buffer(256)
+        _check(_native.lib().m26b_layer_new_from_checkpoint(
+            _ptr(gate_w), _ptr(gate_s), _ptr(up_w), _ptr(up_s), _ptr(down_w), _ptr(down_s), tp_rank, tp_size,
+            C.byref(out), err, 256), err)
+        return cls(out.value)
+
+    def all_scales_normal(self) -> bool:
+        return _native.lib().m26b_layer_all_normal(self._h) != 0
+
+    @property
+    def i_local(self) -> int:
+        return _native.lib().m26b_layer_i_local(self._h)
+
+    def close(self) -> None:
+        if self._h:
+            _native.lib().m26b_layer_free(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Scratch:
+    """Per-request device scratch and stream (b1.rs:94-120)."""
+
+    PEEK = {"meta": 0, "inverse": 1, "original_routes": 2, "grouped_weights": 3, "x_payload": 4, "x_scales": 5,
+            "mid_payload": 6, "mid_f32": 7, "y": 8, "partial": 9, "mid_scales": 10}
+
+    def __init__(self):
+        out, err = C.c_void_p(), C.create_string_buffer(256)
+        _check(_native.lib().m26b_scratch_new(C.byref(out), err, 256), err)
+        self._h = out
+
+    def set_debug(self, flags: int) -> None:
+        _native.lib().m26b_scratch_set_debug(self._h, flags)
+
+    def status(self, stream=None) -> None:
+        """Wait for the last ``ffn_dev`` on this scratch and raise on a plan or numerical fault."""
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_scratch_status(self._h, _ptr(stream), err, 256), err)
+
+    def peek(self, what: str, dtype, shape) -> np.ndarray:
+        """Copy a stage buffer of the last pass to the host (parity tests)."""
+        out = np.empty(shape, dtype=dtype)
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_scratch_peek(self._h, self.PEEK[what], out.ctypes.data, out.nbytes, err, 256), err)
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            _native.lib().m26b_scratch_free(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+@dataclass
+class FfnStats:
+    """Stage timings of one ``ffn`` call (b1.rs:122-129)."""
+    upload_plan_ms: float
+    gpu_ms: float
+    tail_ms: float
+    groups: int
+    phase_ms: tuple  # FC1 (with plan, permute and the fused quantiser), 0, FC2, combine
+
+
+def _ffn_raw(layer, scratch, payload_ptr, payload_pitch, scales_ptr, scales_pitch, ids, weights, rows, bf16_out):
+    if rows == 0 or ids.size != rows * TOPK or weights.size != rows * TOPK or bf16_out.size != rows * H:
+        raise ExpertError(1, f"b1 ffn: extents do not match {rows} rows")
+    ms = (C.c_float * 8)()
+    err = C.create_string_buffer(256)
+    rc = _native.lib().m26b_ffn(layer._h, scratch._h, payload_ptr, payload_pitch, scales_ptr, scales_pitch,
+                                ids.ctypes.data, weights.ctypes.data, rows, bf16_out.ctypes.data, ms, err, 256)
+    _check(rc, err)
+    return FfnStats(ms[0], ms[1], ms[2], int(ms[3]), (ms[4], ms[5], ms[6], ms[7]))
+
+
+def ffn(layer: Layer, scratch: Scratch, payload: np.ndarray, scales: np.ndarray, ids: np.ndarray, weights: np.ndarray,
+        rows: int, bf16_out: np.ndarray) -> FfnStats:
+    """One rank's FFN for ``rows`` tokens on host arrays (b1.rs:131-152): ``payload`` [rows*4096] E4M3,
+    ``scales`` [rows*128] UE8M0, ``ids`` / ``weights`` [rows*8] token-major top-8; writes BF16 [rows*4096]."""
+    payload = np.ascontiguousarray(payload, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    if rows == 0 or payload.size != rows * H or scales.size != rows * H // 32:
+        raise ExpertError(1, f"b1 ffn: extents do not match {rows} rows")
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    weights = np.ascontiguousarray(weights, dtype=np.float32)
+    return _ffn_raw(layer, scratch, payload.ctypes.data, H, scales.ctypes.data, H // 32, ids, weights, rows, bf16_out)
+
+
+def ffn_strided(layer: Layer, scratch: Scratch, hidden: np.ndarray, row_stride: int, ids: np.ndarray,
+                weights: np.ndarray, rows: int, bf16_out: np.ndarray) -> FfnStats:
+    """``ffn`` on the request frame's interleaved rows read in place (b1.rs:154-176): each row is
+    4096 payload bytes followed by its 128 scale bytes, ``row_stride`` bytes apart."""
+    hidden = np.ascontiguousarray(hidden, dtype=np.uint8)
+    if rows == 0 or row_stride < H + H // 32 or hidden.size < (rows - 1) * row_stride + H + H // 32:
+        raise ExpertError(1, f"b1 ffn: hidden rows do not match {rows} rows of {row_stride} B")
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    weights = np.ascontiguousarray(weights, dtype=np.float32)
+    base = hidden.ctypes.data
+    return _ffn_raw(layer, scratch, base, row_stride, base + H, row_stride, ids, weights, rows, bf16_out)
+
+
+X_BF16, X_F32, X_E4M3 = 0, 1, 2
+CODEC_WIRE, CODEC_QUANT_V1 = 0, 1
+
+
+def ffn_dev(layer: Layer, scratch: Scratch, x, ids, weights, rows: int, bf16_out, *, x_dtype: int = X_BF16,
+            x_scales=None, codec: int = CODEC_WIRE, partial_out=None, stream=None) -> None:
+    """Device-resident FFN: enqueue on ``stream`` and return; ``Scratch.status`` reports faults."""
+    err = C.create_string_buffer(256)
+    rc = _native.lib().m26b_ffn_dev(layer._h, scratch._h, _ptr(x), x_dtype, _ptr(x_scales), codec, _ptr(ids),
+                                    _ptr(weights), rows, _ptr(bf16_out), _ptr(partial_out), _ptr(stream), err, 256)
+    _check(rc, err)
+
+
+def quantize_dev(x, x_dtype: int, n_elems: int, codec: int, payload, scales, fault, stream=None) -> None:
+    err = C.create_string_buffer(256)
+    _check(_native.lib().m26b_quantize_dev(_ptr(x), x_dtype, n_elems, codec, _ptr(payload), _ptr(scales), _ptr(fault),
+                                           _ptr(stream), err, 256), err)
+
+
+def route_reduce_dev(y, weights, rows: int, partial, bf16, fault, stream=None) -> None:
+    err = C.create_string_buffer(256)
+    _check(_native.lib().m26b_route_reduce_dev(_ptr(y), _ptr(weights), rows, _ptr(partial), _ptr(bf16), _ptr(fault),
+                                               _ptr(stream), err, 256), err)
+
+
+def rank_sum_dev(planes, n: int, out, stream=None) -> None:
+    """FP32 sum of BF16 planes in rank order; ``planes`` is a sequence of device buffers."""
+    arr = (C.c_void_p * len(planes))(*[_ptr(p) for p in planes])
+    err = C.create_string_buffer(256)
+    _check(_native.lib().m26b_rank_sum_dev(arr, len(planes), n, _ptr(out), _ptr(stream), err, 256), err)
