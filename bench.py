@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the routed-expert FFN hot path (one MoE layer) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one pass of the hot path over one batch of seeded synthetic input: activation quantisation, route plan,
+token permutation, grouped gate/up GEMM + SwiGLU + intermediate quantiser, grouped down GEMM, ordered top-8
+combine. The headline workload (`value`) is BASELINE.json configs[1], the 16-token decode batch; the same JSON
+line carries the 8,192-token prefill segment (configs[3]) under "prefill". Weights are resident in HBM, inputs are
+resident in HBM for `value`, and on the host (pinned) for `e2e`, which goes through the reference-compatible
+host entry point m26b_ffn with both copies inside the timed region.
+
+With N > 1 ranks the layer is tensor-parallel over the intermediate dimension (the reference's own TP4 scheme,
+generalised): every rank runs the whole batch on its 1/N slice of every expert and the BF16 partial planes are
+exchanged with one NCCL all-gather and summed in rank order on every rank. Total work is fixed: "strong" scaling.
+
+--impl reference times the reference's CPU expert path (the port in oracle/oracle.c of
+crates/mimo26-spark/src/main.rs:75-95) on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, I, E, TOPK = 4096, 2048, 256, 8
+EXPERT_BYTES = 13369344                     # 3 x 2048 x 4096 x 17/32 (payload + scales)
+FLOP_PER_TOKEN = 402653184                  # 3 GEMMs x 2 x 4096 x 2048 x top-8
+MXF8F6F4_PEAK_TFLOPS = 4450.0               # measured on this pool: profiles/mxf8f6f4_mma_rate.md
+WORKLOADS = {
+    "decode16": dict(tokens=16, zipf=0.0, desc="16-token decode batch, uniform routing (BASELINE configs[1])"),
+    "prefill8k": dict(tokens=8192, zipf=0.0, desc="8192-token prefill segment, uniform routing (BASELINE configs[3])"),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.proc.wait(5)
+
+    def summary(self):
+        ok = [r for r in self.rows if len(r) >= 7 and r[0].isdigit()]
+        if not ok:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in ok)]
+        return dict(sm_mhz=float(np.median([int(r[0]) for r in ok])), sm_max_mhz=float(ok[0][1]), reasons=reasons,
+                    samples=len(ok))
+
+
+def cpu_reference_arm(args, rank):
+    """The reference's CPU expert path on the host cores, bounded sample of the headline workload."""
+    if rank != 0:
+        return
+    import oracle
+    from mimo26f_afd_b200 import synth
+
+    wl = WORKLOADS[args.workload]
+    seed, tokens = synth.MASTER_SEED, wl["tokens"]
+    ids, w = synth.routing(seed, tokens, wl["zipf"])
+    x = synth.bf16_to_f32_np(synth.activations_bf16(seed, tokens))
+    xq, xs = oracle.quant_wire(x)
+    active = np.unique(ids)
+    # sample: the first experts (by id) that together hold about `budget` routed rows; the 16-token batch runs whole
+    budget_rows = tokens * TOPK if tokens <= 16 else 256
+    take, rows = [], 0
+    for e in active:
+        take.append(int(e)); rows += int((ids == e).sum())
+        if rows >= budget_rows:
+            break
+    e_lo, e_hi = take[0], take[-1] + 1
+    tensors = synth.layer_np(seed, [e for e in active if e_lo <= e < e_hi])
+    cores = os.cpu_count() or 1
+    times, done = [], 0
+    for it in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        done, _, _ = oracle.cpu_path(tensors, xq, xs, ids, w, e_lo, e_hi)
+        if it >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    step = float(np.mean(times))
+    value = tokens * (done / (tokens * TOPK)) / step          # tokens/s if the whole batch ran at the sample's rate
+    sample = f"experts {e_lo}..{e_hi - 1} of the batch: {done} of {tokens * TOPK} routed rows per step, extrapolated by rows"
+    line = dict(impl="reference", metric="moe_expert_ffn_tokens_per_s_per_layer", value=value, unit="tokens/s",
+                n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=step * 1e3, higher_is_better=True,
+                scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=args.workload, tokens=tokens, routing="uniform" if not wl["zipf"] else f"zipf{wl['zipf']}",
+                            note="reference CPU expert path (E-FP32 lattice), port in oracle/oracle.c"),
+                cpu_baseline=dict(value=value, unit="tokens/s", cores=cores, kind="port", sample=sample),
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
+    """Times `steps` passes (device-resident inputs) and `steps` end-to-end passes (host buffers)."""
+    import torch
+    import torch.distributed as dist
+
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import expert, synth, tp
+
+    wl = WORKLOADS[name]
+    tokens, seed = wl["tokens"], synth.MASTER_SEED
+    x_bits = synth.activations_bf16(seed, tokens)
+    ids, w = synth.routing(seed, tokens, wl["zipf"])
+    active = int(len(np.unique(ids)))
+    xd = torch.from_numpy(x_bits.view(np.int16)).to(dev)
+    idd, wd = torch.from_numpy(ids).to(dev), torch.from_numpy(w).to(dev)
+    out = torch.empty((tokens, H), dtype=torch.int16, device=dev)
+    total = torch.empty((tokens, H), dtype=torch.float32, device=dev) if world > 1 else None
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # > 126 MB L2
+    scratch.set_debug(2)
+
+    def step():
+        expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, out, stream=stream.cuda_stream)
+        if world > 1:
+            tp.tp_combine(out, total, stream=stream.cuda_stream)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    scratch.status(stream.cuda_stream)
+    sync_all()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    kern = []
+    with ClockSampler(dev.index or 0) as clocks:
+        for a, b in ev:
+            flush.fill_(1)                                   # L2 flush between timed iterations (not timed)
+            a.record(stream)
+            step()
+            b.record(stream)
+            b.synchronize()
+            kern.append(scratch.timings())
+        sync_all()
+    scratch.status(stream.cuda_stream)
+    ms = np.array([a.elapsed_time(b) for a, b in ev])
+    t = torch.tensor([float(ms.sum())], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)             # max over ranks
+    total_ms = float(t.item())
+    value = tokens * args.steps / (total_ms * 1e-3)
+
+    # end to end through the reference-compatible host entry point: pinned host buffers, copies inside the timed region
+    xq = scratch.peek("x_payload", np.uint8, (tokens, H))
+    xs = scratch.peek("x_scales", np.uint8, (tokens, H // 32))
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    hq, hs, hi, hw = pin(xq), pin(xs), pin(ids), pin(w)
+    hout = torch.empty((tokens, H), dtype=torch.int16).pin_memory()
+    import ctypes as C
+    from mimo26f_afd_b200 import _native
+    err = C.create_string_buffer(256)
+
+    def e2e_step():
+        rc = _native.lib().m26b_ffn(layer._h, scratch._h, hq.data_ptr(), H, hs.data_ptr(), H // 32, hi.data_ptr(), hw.data_ptr(),
+                                    tokens, hout.data_ptr(), None, err, 256)
+        if rc:
+            raise M.ExpertError(rc, err.value.decode())
+        if world > 1:
+            out.copy_(hout.to(dev, non_blocking=True))
+            tp.tp_combine(out, total)
+            total[:1].cpu()
+
+    for _ in range(min(args.warmup, 3)):
+        e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = tokens * args.steps / float(t.item())
+    h2d = tokens * (H + H // 32 + TOPK * 8)
+    d2h = tokens * H * 2 + 64
+
+    # roofline of the dominant kernel (FC1): algorithmic work of that launch / its mean event-timed duration
+    fc1_ms = float(np.mean([k["fc1"] for k in kern]))
+    il = I // world
+    routes = tokens * TOPK
+    if name == "decode16":
+        fc1_bytes = active * (2 * il * (H // 2) + 2 * il * (H // 32)) + routes * (H + H // 32) + routes * (il + il // 32)
+        roof = dict(bound="hbm", achieved=fc1_bytes / (fc1_ms * 1e-3) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s",
+                    peak_source=f"{peaks['source']} copy bandwidth (MEASURED_PEAKS.json)", kernel="gemm_mx_kernel<FC1>",
+                    algorithmic_bytes=fc1_bytes, traffic=None)
+    else:
+        fc1_flops = 2.0 * 2 * H * il * routes
+        roof = dict(bound="tensor", achieved=fc1_flops / (fc1_ms * 1e-3) / 1e12, peak=MXF8F6F4_PEAK_TFLOPS, unit="TFLOP/s",
+                    peak_source="measured tcgen05 kind::mxf8f6f4 dense rate on this pool (profiles/mxf8f6f4_mma_rate.md); "
+                                f"MEASURED_PEAKS.json holds only bf16 = {peaks['bf16_tflops']} TF/s",
+                    kernel="gemm_mx_kernel<FC1>", algorithmic_flops=fc1_flops, traffic=None)
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["kernel_ms"] = fc1_ms
+    whole = dict(hbm_gbs=(active * EXPERT_BYTES / world + tokens * H * 4 + routes * 8) / (total_ms / args.steps * 1e-3) / 1e9,
+                 tflops=FLOP_PER_TOKEN * tokens / world / (total_ms / args.steps * 1e-3) / 1e12)
+    launches = (6 if routes <= 4096 else 8) + (1 if world > 1 else 0)
+    return dict(workload=name, tokens=tokens, active_experts=active, value=value, ms_per_step=total_ms / args.steps,
+                e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                roofline=roof, whole_step=whole, kernels_ms={k: float(np.mean([x[k] for x in kern])) for k in kern[0]},
+                clocks=clocks.summary(), gpu_launches=launches * args.steps)
+
+
+def cpu_baseline_for(name, steps_budget_s=20.0):
+    """The oracle's port of the reference CPU path on this host, bounded sample (rank 0, N = 1 only)."""
+    import oracle
+    from mimo26f_afd_b200 import synth
+
+    wl = WORKLOADS[name]
+    tokens, seed = wl["tokens"], synth.MASTER_SEED
+    ids, w = synth.routing(seed, tokens, wl["zipf"])
+    sub = min(tokens, 16)                                   # the sample keeps whole tokens of the batch
+    ids_s, w_s = ids[:sub], w[:sub]
+    xq, xs = oracle.quant_wire(synth.bf16_to_f32_np(synth.activations_bf16(seed, tokens)[:sub]))
+    active = np.unique(ids_s)
+    take, rows = [], 0
+    for e in active:                                        # 16 tokens = 128 routed rows: the decode batch runs whole
+        take.append(int(e)); rows += int((ids_s == e).sum())
+        if rows >= sub * TOPK:
+            break
+    tensors = synth.layer_np(seed, take)
+    t0 = time.perf_counter()
+    done, _, _ = oracle.cpu_path(tensors, xq, xs, ids_s, w_s, take[0], take[-1] + 1)
+    dt = time.perf_counter() - t0
+    value = (done / TOPK) / dt
+    return dict(value=value, unit="tokens/s", cores=os.cpu_count() or 1, kind="port",
+                sample=f"{done} routed rows ({done / TOPK:.2f} token-equivalents) of the first {sub} tokens, experts "
+                       f"{take[0]}..{take[-1]}, {dt:.1f} s; reference CPU expert path (E-FP32), OpenMP over output rows")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode16", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 8192-token prefill sub-result")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        cpu_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import synth
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the product has no CPU path (use --impl reference for the CPU baseline)")
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    weights = synth.layer_torch(synth.MASTER_SEED, dev)
+    layer = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS], tp_rank=rank, tp_size=world)
+    del weights
+    torch.cuda.empty_cache()
+    scratch = M.Scratch()
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+
+    main_r = run_workload(args.workload, layer, scratch, dev, stream, args, rank, world, peaks)
+    extra = None
+    if not args.no_prefill and args.workload == "decode16":
+        sub = argparse.Namespace(**vars(args))
+        sub.steps, sub.warmup = max(3, min(args.steps, 10)), max(3, min(args.warmup, 5))
+        extra = run_workload("prefill8k", layer, scratch, dev, stream, sub, rank, world, peaks)
+    if rank == 0:
+        cpu = cpu_baseline_for(args.workload) if world == 1 else None
+        line = dict(metric="moe_expert_ffn_tokens_per_s_per_layer", value=main_r["value"], unit="tokens/s", n_gpus=world,
+                    steps=args.steps, warmup=args.warmup, ms_per_step=main_r["ms_per_step"], higher_is_better=True,
+                    scaling="strong" if world > 1 else "weak", vs_baseline=None, dtype="e4m3 x e2m1 (mxf8f6f4), f32 accumulate",
+                    data="synthetic",
+                    config=dict(workload=args.workload, description=WORKLOADS[args.workload]["desc"], tokens=main_r["tokens"],
+                                top_k=TOPK, experts=E, hidden=H, intermediate=I, active_experts=main_r["active_experts"],
+                                parallelism=f"tp{world}" if world > 1 else "single", l2="flushed between timed iterations",
+                                input_codec="wire (FP8 E4M3 + UE8M0 K32)"),
+                    e2e=main_r["e2e"], gpu_launches=main_r["gpu_launches"], clocks=main_r["clocks"], roofline=main_r["roofline"],
+                    whole_step=main_r["whole_step"], kernels_ms=main_r["kernels_ms"], cpu_baseline=cpu)
+        if extra:
+            line["prefill"] = {k: extra[k] for k in ("workload", "tokens", "value", "ms_per_step", "e2e", "roofline", "whole_step",
+                                                     "kernels_ms", "clocks")}
+            line["prefill"]["unit"] = "tokens/s"
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -103,7 +103,7 @@ int m26b_scratch_status(m26b_scratch* scratch, void* stream, char* err, size_t e
 
 /* Stage dumps for parity tests (the reference's primitive cell dumps stages the
  * same way: crates/mimo26-expert/tests/b1_core/primitive.cu:173-196).
- * flags bit 0: keep an FP32 copy of silu(gate)*up before quantisation. */
+ * flags bit 0: keep an FP32 copy of silu(gate)*up before quantisation; bit 1: record per-kernel events. */
 int m26b_scratch_set_debug(m26b_scratch* scratch, uint32_t flags);
 enum {
     M26B_PEEK_META = 0,            /* 8 x u32: fault, tiles, fc1 items, fc2 items, active experts, max count */
@@ -118,6 +118,11 @@ enum {
     M26B_PEEK_PARTIAL = 9,         /* f32 [rows,4096] */
     M26B_PEEK_MID_SCALES = 10      /* u8 [routes,I_local/32] grouped order, row-major (gathered from the scale blocks) */
 };
+/* Per-kernel GPU time of the last pass in milliseconds, from CUDA events recorded on the launching stream
+ * around each kernel when debug flag bit 1 (value 2) is set (the reference times its phases the same way,
+ * b1_serve.cu:545-550): [0] input quantiser, [1] route plan, [2] permutation, [3] FC1 GEMM, [4] FC2 GEMM,
+ * [5] combine. Waits for the pass to finish. */
+int m26b_scratch_timings(m26b_scratch* scratch, float* ms6, char* err, size_t errlen);
 /* Copies a buffer of the last pass to host memory; returns 0 or 1/2. */
 int m26b_scratch_peek(m26b_scratch* scratch, int what, void* host_dst, uint64_t bytes, char* err, size_t errlen);
 

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libm26b_expert.so")
 SYMBOLS = (
     "m26b_layer_new", "m26b_layer_new_tp", "m26b_layer_new_from_checkpoint", "m26b_layer_all_normal",
     "m26b_layer_i_local", "m26b_layer_free", "m26b_scratch_new", "m26b_scratch_free", "m26b_ffn", "m26b_ffn_dev",
-    "m26b_scratch_status", "m26b_scratch_set_debug", "m26b_scratch_peek", "m26b_quantize_dev",
+    "m26b_scratch_status", "m26b_scratch_set_debug", "m26b_scratch_timings", "m26b_scratch_peek", "m26b_quantize_dev",
     "m26b_route_reduce_dev", "m26b_rank_sum_dev", "m26b_version",
 )
 
@@ -45,6 +45,7 @@ def lib() -> C.CDLL:
     L.m26b_ffn_dev.argtypes = [vp, vp, vp, C.c_int, u8p, C.c_int, i32p, f32p, C.c_uint32, u16p, f32p, vp, *err]
     L.m26b_scratch_status.argtypes = [vp, vp, *err]
     L.m26b_scratch_set_debug.argtypes = [vp, C.c_uint32]
+    L.m26b_scratch_timings.argtypes = [vp, f32p, *err]
     L.m26b_scratch_peek.argtypes = [vp, C.c_int, vp, C.c_uint64, *err]
     L.m26b_quantize_dev.argtypes = [vp, C.c_int, C.c_uint64, C.c_int, u8p, u8p, u32p, vp, *err]
     L.m26b_route_reduce_dev.argtypes = [f32p, f32p, C.c_uint32, f32p, u16p, u32p, vp, *err]

@@ -103,90 +103,268 @@ struct PlanOut {
     PlanMeta* meta;
 };
 
-// One CTA. Validates the routes, counts per expert, then places routes in
-// expert-major order, stable inside an expert (identical to a stable sort by
-// expert id: crates/mimo26-expert/kernels/b1/group_plan.cu:32-79), and cuts
-// each expert's run into token tiles of at most `max_n` rows.
+// One CTA of 32 warps. Validates the routes, counts per expert, then places
+// routes in expert-major order, stable inside an expert (identical to a stable
+// sort by expert id: crates/mimo26-expert/kernels/b1/group_plan.cu:32-79), and
+// cuts each expert's run into token tiles of at most `max_n` rows.
 // Rejection rules as the reference planner (b1_serve.cu:46-59): id in
 // [0,256), expert resident, 0 <= weight <= FLT_MAX, no expert twice in a row.
+//
+// Each warp owns one contiguous segment of the routes. It counts its segment
+// per expert, a 256-thread pass turns the counts into per-(warp, expert) start
+// offsets, and each warp then walks its segment again in route order, 32 routes
+// at a time, ranking equal experts inside the group with match.any. Between
+// the two block-wide barriers no warp waits for another.
+__device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t o = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= uint32_t(d)) v += o;
+    }
+    return v;
+}
 __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                     uint32_t rows, const uint8_t* __restrict__ resident, int max_n,
                                                     int mt_fc1, int mt_fc2, PlanOut o) {
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
-    __shared__ uint32_t i1base[kExperts], i2base[kExperts], cursor[kExperts];
+    __shared__ uint32_t i1base[kExperts], i2base[kExperts];
     __shared__ uint32_t wcnt[32][kExperts];
-    __shared__ uint32_t bad;
-    const uint32_t tid = threadIdx.x, nt = blockDim.x, routes = rows * kTopK;
+    __shared__ uint32_t wsum[4][8];
+    __shared__ uint32_t bad, max_count;
+    const uint32_t tid = threadIdx.x, routes = rows * kTopK;
     const uint32_t lane = tid & 31u, warp = tid >> 5;
-    for (uint32_t e = tid; e < kExperts; e += nt) { cnt[e] = 0; cursor[e] = 0; }
-    if (tid == 0) bad = 0;
+    const uint32_t seg = (((routes + 31u) / 32u) + 31u) & ~31u;          // routes per warp, a multiple of 32
+    const uint32_t lo = warp * seg < routes ? warp * seg : routes;
+    const uint32_t hi = lo + seg < routes ? lo + seg : routes;
+    for (uint32_t i = tid; i < 32 * kExperts; i += 1024) (&wcnt[0][0])[i] = 0;
+    if (tid == 0) { bad = 0; max_count = 0; }
     __syncthreads();
-    for (uint32_t r = tid; r < routes; r += nt) {
-        const int32_t e = ids[r];
-        const float wt = w[r];
-        bool ok = e >= 0 && e < kExperts && resident[e] && wt >= 0.0f && wt <= 3.402823466e+38f;
-        if (ok)
-            for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
-        if (!ok) atomicOr(&bad, 1u); else atomicAdd(&cnt[e], 1u);
+    uint32_t my_bad = 0;
+    for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
+        const uint32_t r = r0 + lane;
+        const bool live = r < hi;
+        int32_t e = -1;
+        bool ok = false;
+        if (live) {
+            e = ids[r];
+            const float wt = w[r];
+            ok = e >= 0 && e < kExperts && resident[e] && wt >= 0.0f && wt <= 3.402823466e+38f;
+            if (ok)
+                for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
+            if (!ok) my_bad = 1;
+        }
+        const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : -1 - int32_t(lane));
+        if (ok && (peers & ((1u << lane) - 1u)) == 0u) wcnt[warp][e] += __popc(peers);
+        __syncwarp();
     }
+    if (my_bad) atomicOr(&bad, 1u);
     __syncthreads();
     if (bad) {
         if (tid == 0) { PlanMeta m{}; m.fault = kFaultPlan; *o.meta = m; }
         return;
     }
-    if (tid == 0) {
-        uint32_t rb = 0, t = 0, i1 = 0, i2 = 0, active = 0, mx = 0;
-        for (int e = 0; e < kExperts; ++e) {
-            const uint32_t c = cnt[e];
-            const uint32_t n = c ? (c + max_n - 1) / max_n : 0;
-            const uint32_t per = n ? (c + n - 1) / n : 0;
-            rbase[e] = rb; tstart[e] = t; ntl[e] = n; width[e] = (per + 15u) & ~15u;
-            i1base[e] = i1; i2base[e] = i2;
-            rb += c; t += n; i1 += n * mt_fc1; i2 += n * mt_fc2;
-            active += c ? 1 : 0; mx = c > mx ? c : mx;
+    uint32_t c = 0, n = 0;
+    if (tid < kExperts) {
+        for (int wi = 0; wi < 32; ++wi) { const uint32_t t = wcnt[wi][tid]; wcnt[wi][tid] = c; c += t; }
+        n = c ? (c + max_n - 1) / max_n : 0;
+        const uint32_t per = n ? (c + n - 1) / n : 0;
+        cnt[tid] = c; ntl[tid] = n; width[tid] = (per + 15u) & ~15u;
+        atomicMax(&max_count, c);
+        // exclusive scans over experts of routes, tiles, FC1 items, FC2 items
+        const uint32_t v[4] = {c, n, n * uint32_t(mt_fc1), n * uint32_t(mt_fc2)};
+        uint32_t inc[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { inc[k] = warp_inclusive_scan(v[k], lane); if (lane == 31) wsum[k][warp] = inc[k]; }
+        rbase[tid] = inc[0] - v[0]; tstart[tid] = inc[1] - v[1]; i1base[tid] = inc[2] - v[2]; i2base[tid] = inc[3] - v[3];
+    }
+    const uint32_t active = __syncthreads_count(tid < kExperts && c > 0);
+    if (tid < kExperts) {
+        uint32_t add[4] = {0, 0, 0, 0};
+        for (uint32_t wi = 0; wi < warp; ++wi)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) add[k] += wsum[k][wi];
+        rbase[tid] += add[0]; tstart[tid] += add[1]; i1base[tid] += add[2]; i2base[tid] += add[3];
+        if (tid == kExperts - 1) {
+            PlanMeta m{};
+            m.fault = 0; m.n_tiles = tstart[tid] + n; m.n_items_fc1 = i1base[tid] + n * mt_fc1;
+            m.n_items_fc2 = i2base[tid] + n * mt_fc2; m.active_experts = active; m.max_count = max_count;
+            *o.meta = m;
         }
-        PlanMeta m{};
-        m.fault = 0; m.n_tiles = t; m.n_items_fc1 = i1; m.n_items_fc2 = i2; m.active_experts = active; m.max_count = mx;
-        *o.meta = m;
     }
     __syncthreads();
-    // stable placement, 1024 routes per pass in route order
-    for (uint32_t base = 0; base < routes; base += nt) {
-        for (uint32_t i = tid; i < 32 * kExperts; i += nt) (&wcnt[0][0])[i] = 0;
-        __syncthreads();
-        const uint32_t r = base + tid;
-        const bool valid = r < routes;
-        const int32_t e = valid ? ids[r] : -1 - int32_t(lane);
+    // stable placement: this warp's segment in route order, 32 routes at a time
+    for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
+        const uint32_t r = r0 + lane;
+        const bool live = r < hi;
+        const int32_t e = live ? ids[r] : -1 - int32_t(lane);
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
-        if (valid && rank == 0) wcnt[warp][e] = __popc(peers);
-        __syncthreads();
-        if (tid < kExperts) {
-            uint32_t run = cursor[tid];
-            for (int wi = 0; wi < 32; ++wi) { const uint32_t t = wcnt[wi][tid]; wcnt[wi][tid] = run; run += t; }
-            cursor[tid] = run;
-        }
-        __syncthreads();
-        if (valid) {
-            const uint32_t g = rbase[e] + wcnt[warp][e] + rank;
+        uint32_t g = 0;
+        if (live) g = rbase[e] + wcnt[warp][e] + rank;
+        __syncwarp();
+        if (live && rank == 0) wcnt[warp][e] += __popc(peers);
+        __syncwarp();
+        if (live) {
             o.inverse[r] = int32_t(g);
             o.original_routes[g] = int32_t(r);
             o.grouped_weights[g] = w[r];
         }
-        __syncthreads();
     }
-    // tiles and work items: one warp per expert, lanes over (weight tile, token tile)
-    for (uint32_t e = warp; e < kExperts; e += nt / 32) {
-        const uint32_t c = cnt[e], n = ntl[e], wd = width[e];
-        if (lane == 0) o.experts[e] = ExpertPlan{int32_t(c), int32_t(rbase[e]), int32_t(tstart[e]), int32_t(wd)};
-        for (uint32_t j = lane; j < n; j += 32) {
-            const uint32_t nv = c - j * wd < wd ? c - j * wd : wd;
+    // tiles and work items: one warp per expert, lanes over (weight tile pair, token tile)
+    for (uint32_t e = warp; e < kExperts; e += 32) {
+        const uint32_t ce = cnt[e], ne = ntl[e], wd = width[e];
+        if (lane == 0) o.experts[e] = ExpertPlan{int32_t(ce), int32_t(rbase[e]), int32_t(tstart[e]), int32_t(wd)};
+        for (uint32_t j = lane; j < ne; j += 32) {
+            const uint32_t nv = ce - j * wd < wd ? ce - j * wd : wd;
             o.tiles[tstart[e] + j] = TokenTile{int32_t(e), int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
-        for (uint32_t i = lane; i < n * mt_fc1; i += 32)
-            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % n), int32_t(i / n)};
-        for (uint32_t i = lane; i < n * mt_fc2; i += 32)
-            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % n), int32_t(i / n)};
+        for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
+            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+        for (uint32_t i = lane; i < ne * mt_fc2; i += 32)
+            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+    }
+}
+
+// ---- the same plan in three launches, for requests too large for one CTA ----
+// CTA c owns routes [c S, (c+1) S). (1) count per (CTA, expert) and validate;
+// (2) one CTA turns the counts into per-(CTA, expert) start offsets, tiles the
+// experts and writes tiles / work items / metadata; (3) every CTA places its
+// routes: global offset of its (CTA, expert) pair + the per-warp offset inside
+// the CTA + the rank inside the 32-route group. Stable by construction.
+__device__ __forceinline__ void plan_warp_counts(const int32_t* __restrict__ ids, const float* __restrict__ w,
+                                                 const uint8_t* __restrict__ resident, uint32_t lo, uint32_t hi,
+                                                 uint32_t lane, uint32_t* __restrict__ wrow, bool validate, uint32_t& bad) {
+    for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
+        const uint32_t r = r0 + lane;
+        const bool live = r < hi;
+        int32_t e = -1;
+        bool ok = false;
+        if (live) {
+            e = ids[r];
+            ok = true;
+            if (validate) {
+                const float wt = w[r];
+                ok = e >= 0 && e < kExperts && resident[e] && wt >= 0.0f && wt <= 3.402823466e+38f;
+                if (ok)
+                    for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
+                if (!ok) bad = 1;
+            }
+        }
+        const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : -1 - int32_t(lane));
+        if (ok && (peers & ((1u << lane) - 1u)) == 0u) wrow[e] += __popc(peers);
+        __syncwarp();
+    }
+}
+__global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
+                                                          uint32_t rows, const uint8_t* __restrict__ resident,
+                                                          uint32_t cta_routes, uint32_t* __restrict__ cta_cnt,
+                                                          PlanMeta* __restrict__ meta) {
+    __shared__ uint32_t wcnt[32][kExperts];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, routes = rows * kTopK;
+    const uint32_t seg = cta_routes / 32u, base = blockIdx.x * cta_routes;
+    const uint32_t lo = base + warp * seg < routes ? base + warp * seg : routes;
+    const uint32_t hi = lo + seg < routes ? lo + seg : routes;
+    for (uint32_t i = tid; i < 32 * kExperts; i += 1024) (&wcnt[0][0])[i] = 0;
+    __syncthreads();
+    uint32_t bad = 0;
+    plan_warp_counts(ids, w, resident, lo, hi, lane, wcnt[warp], true, bad);
+    if (bad) atomicOr(&meta->fault, uint32_t(kFaultPlan));
+    __syncthreads();
+    if (tid < kExperts) {
+        uint32_t c = 0;
+        for (int wi = 0; wi < 32; ++wi) c += wcnt[wi][tid];
+        cta_cnt[blockIdx.x * kExperts + tid] = c;
+    }
+}
+__global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_t* __restrict__ cta_cnt, int max_n,
+                                                         int mt_fc1, int mt_fc2, PlanOut o) {
+    __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
+    __shared__ uint32_t i1base[kExperts], i2base[kExperts];
+    __shared__ uint32_t wsum[4][8];
+    __shared__ uint32_t max_count;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (o.meta->fault) {   // uniform: written by the previous launch
+        if (tid == 0) { PlanMeta m{}; m.fault = kFaultPlan; *o.meta = m; }
+        return;
+    }
+    if (tid == 0) max_count = 0;
+    __syncthreads();
+    uint32_t c = 0, n = 0;
+    if (tid < kExperts) {
+        for (uint32_t k = 0; k < n_cta; ++k) { const uint32_t t = cta_cnt[k * kExperts + tid]; cta_cnt[k * kExperts + tid] = c; c += t; }
+        n = c ? (c + max_n - 1) / max_n : 0;
+        const uint32_t per = n ? (c + n - 1) / n : 0;
+        cnt[tid] = c; ntl[tid] = n; width[tid] = (per + 15u) & ~15u;
+        atomicMax(&max_count, c);
+        const uint32_t v[4] = {c, n, n * uint32_t(mt_fc1), n * uint32_t(mt_fc2)};
+        uint32_t inc[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { inc[k] = warp_inclusive_scan(v[k], lane); if (lane == 31) wsum[k][warp] = inc[k]; }
+        rbase[tid] = inc[0] - v[0]; tstart[tid] = inc[1] - v[1]; i1base[tid] = inc[2] - v[2]; i2base[tid] = inc[3] - v[3];
+    }
+    const uint32_t active = __syncthreads_count(tid < kExperts && c > 0);
+    if (tid < kExperts) {
+        uint32_t add[4] = {0, 0, 0, 0};
+        for (uint32_t wi = 0; wi < warp; ++wi)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) add[k] += wsum[k][wi];
+        rbase[tid] += add[0]; tstart[tid] += add[1]; i1base[tid] += add[2]; i2base[tid] += add[3];
+        if (tid == kExperts - 1) {
+            PlanMeta m{};
+            m.fault = 0; m.n_tiles = tstart[tid] + n; m.n_items_fc1 = i1base[tid] + n * mt_fc1;
+            m.n_items_fc2 = i2base[tid] + n * mt_fc2; m.active_experts = active; m.max_count = max_count;
+            *o.meta = m;
+        }
+    }
+    __syncthreads();
+    for (uint32_t e = warp; e < kExperts; e += 32) {
+        const uint32_t ce = cnt[e], ne = ntl[e], wd = width[e];
+        if (lane == 0) o.experts[e] = ExpertPlan{int32_t(ce), int32_t(rbase[e]), int32_t(tstart[e]), int32_t(wd)};
+        for (uint32_t j = lane; j < ne; j += 32) {
+            const uint32_t nv = ce - j * wd < wd ? ce - j * wd : wd;
+            o.tiles[tstart[e] + j] = TokenTile{int32_t(e), int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
+        }
+        for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
+            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+        for (uint32_t i = lane; i < ne * mt_fc2; i += 32)
+            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+    }
+}
+__global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
+                                                          uint32_t rows, uint32_t cta_routes,
+                                                          const uint32_t* __restrict__ cta_off, PlanOut o) {
+    __shared__ uint32_t wcnt[32][kExperts];
+    if (o.meta->fault) return;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, routes = rows * kTopK;
+    const uint32_t seg = cta_routes / 32u, base = blockIdx.x * cta_routes;
+    const uint32_t lo = base + warp * seg < routes ? base + warp * seg : routes;
+    const uint32_t hi = lo + seg < routes ? lo + seg : routes;
+    for (uint32_t i = tid; i < 32 * kExperts; i += 1024) (&wcnt[0][0])[i] = 0;
+    __syncthreads();
+    uint32_t bad = 0;
+    plan_warp_counts(ids, w, nullptr, lo, hi, lane, wcnt[warp], false, bad);
+    __syncthreads();
+    if (tid < kExperts) {   // per-warp exclusive offsets, on top of this CTA's global start for the expert
+        uint32_t run = uint32_t(o.experts[tid].rbase) + cta_off[blockIdx.x * kExperts + tid];
+        for (int wi = 0; wi < 32; ++wi) { const uint32_t t = wcnt[wi][tid]; wcnt[wi][tid] = run; run += t; }
+    }
+    __syncthreads();
+    for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
+        const uint32_t r = r0 + lane;
+        const bool live = r < hi;
+        const int32_t e = live ? ids[r] : -1 - int32_t(lane);
+        const uint32_t peers = __match_any_sync(0xffffffffu, e);
+        const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+        uint32_t g = 0;
+        if (live) g = wcnt[warp][e] + rank;
+        __syncwarp();
+        if (live && rank == 0) wcnt[warp][e] += __popc(peers);
+        __syncwarp();
+        if (live) {
+            o.inverse[r] = int32_t(g);
+            o.original_routes[g] = int32_t(r);
+            o.grouped_weights[g] = w[r];
+        }
     }
 }
 
@@ -221,8 +399,7 @@ __global__ void __launch_bounds__(256) permute_kernel(const uint8_t* __restrict_
             const uint8_t sb = xs[size_t(token) * (kHidden / kBlockK) + threadIdx.x];
             if (sb < 105 || sb > 247) bad = kFaultInputScale;
             const uint32_t chunk = threadIdx.x >> 2, kb = threadIdx.x & 3u;
-            sfb[((size_t(tile) * (kHidden / kChunkK) + chunk) * 2 + (lr >> 7)) * kScaleBlockBytes +
-                scale_block_offset(int(lr & 127u), int(kb))] = sb;
+            sfb[(size_t(tile) * (kHidden / kChunkK) + chunk) * kScaleBlockBytes + scale_block_offset(int(lr), int(kb))] = sb;
         }
     }
     if (bad) atomicOr(fault, bad);
@@ -314,36 +491,36 @@ struct ProjSrc {
     uint64_t col0_p, col0_s;                     // first payload / scale byte of this rank's K slice
 };
 
-// w13[e][j][r][*]: r < 64 -> gate row 64 j + r, else up row 64 j + r - 64. 16 bytes per thread.
+// w13[e][j][r][*]: r < 128 -> gate row 128 j + r, else up row 128 j + r - 128. 16 bytes per thread.
 __global__ void __launch_bounds__(256) prep_w13_kernel(ProjSrc gate, ProjSrc up, int i_local, uint8_t* __restrict__ dst) {
-    const uint64_t vec_per_row = kHidden / 2 / 16;
-    const uint64_t total = uint64_t(kExperts) * (i_local / 64) * 128 * vec_per_row;
+    const uint64_t vec_per_row = kHidden / 2 / 16, tiles = uint64_t(i_local) / kTileM;
+    const uint64_t total = uint64_t(kExperts) * tiles * kPairM * vec_per_row;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint64_t v = i % vec_per_row, row = i / vec_per_row;
-        const uint64_t r = row % 128, j = (row / 128) % (i_local / 64), e = row / 128 / (i_local / 64);
-        const ProjSrc& s = r < 64 ? gate : up;
-        const uint64_t srow = s.row0 + j * 64 + (r & 63);
+        const uint64_t r = row % kPairM, j = (row / kPairM) % tiles, e = row / kPairM / tiles;
+        const ProjSrc& s = r < kTileM ? gate : up;
+        const uint64_t srow = s.row0 + j * kTileM + (r % kTileM);
         reinterpret_cast<uint4*>(dst)[i] =
             *reinterpret_cast<const uint4*>(s.payload + e * s.expert_stride_p + srow * s.row_stride_p + s.col0_p + v * 16);
     }
 }
-// s13[e][j][c][512]. One byte per thread; byte 255 (reserved) is stored as 254:
+// s13[e][j][c][b][512], b = 0 gate / 1 up. One byte per thread; byte 255 (reserved) is stored as 254:
 // the checkpoint contract clamps it to 2^127 (crates/mimo26-expert/src/mxfp4.rs:24-29).
 __global__ void __launch_bounds__(256) prep_s13_kernel(ProjSrc gate, ProjSrc up, int i_local, uint8_t* __restrict__ dst,
                                                        uint32_t* __restrict__ abnormal) {
-    const uint64_t chunks = kHidden / kChunkK;
-    const uint64_t total = uint64_t(kExperts) * (i_local / 64) * chunks * kScaleBlockBytes;
+    const uint64_t chunks = kHidden / kChunkK, tiles = uint64_t(i_local) / kTileM;
+    const uint64_t total = uint64_t(kExperts) * tiles * chunks * 2 * kScaleBlockBytes;
     uint32_t odd = 0;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint32_t o = uint32_t(i % kScaleBlockBytes);
-        const uint64_t c = (i / kScaleBlockBytes) % chunks, j = (i / kScaleBlockBytes / chunks) % (i_local / 64);
-        const uint64_t e = i / kScaleBlockBytes / chunks / (i_local / 64);
+        const uint64_t b = (i / kScaleBlockBytes) % 2, c = (i / kScaleBlockBytes / 2) % chunks;
+        const uint64_t j = (i / kScaleBlockBytes / 2 / chunks) % tiles, e = i / kScaleBlockBytes / 2 / chunks / tiles;
         const uint32_t r = (o >> 4) + 32u * ((o >> 2) & 3u), kb = o & 3u;
-        const ProjSrc& s = r < 64 ? gate : up;
-        const uint64_t srow = s.row0 + j * 64 + (r & 63);
-        uint8_t b = s.scales[e * s.expert_stride_s + srow * s.row_stride_s + s.col0_s + c * 4 + kb];
-        if (b < 2 || b > 252) odd = 1;
-        dst[i] = b == 255 ? 254 : b;
+        const ProjSrc& s = b == 0 ? gate : up;
+        const uint64_t srow = s.row0 + j * kTileM + r;
+        uint8_t v = s.scales[e * s.expert_stride_s + srow * s.row_stride_s + s.col0_s + c * 4 + kb];
+        if (v < 2 || v > 252) odd = 1;
+        dst[i] = v == 255 ? 254 : v;
     }
     if (odd) atomicOr(abnormal, 1u);
 }
@@ -357,20 +534,21 @@ __global__ void __launch_bounds__(256) prep_w2_kernel(ProjSrc down, int i_local,
             down.payload + e * down.expert_stride_p + (down.row0 + h) * down.row_stride_p + down.col0_p + v * 16);
     }
 }
-// s2[e][h/128][c][512].
+// s2[e][h/256][c][b][512]: block b covers rows 256 t + 128 b + r.
 __global__ void __launch_bounds__(256) prep_s2_kernel(ProjSrc down, int i_local, uint8_t* __restrict__ dst,
                                                       uint32_t* __restrict__ abnormal) {
-    const uint64_t chunks = uint64_t(i_local) / kChunkK, mts = kHidden / kTileM;
-    const uint64_t total = uint64_t(kExperts) * mts * chunks * kScaleBlockBytes;
+    const uint64_t chunks = uint64_t(i_local) / kChunkK, mts = kHidden / kPairM;
+    const uint64_t total = uint64_t(kExperts) * mts * chunks * 2 * kScaleBlockBytes;
     uint32_t odd = 0;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint32_t o = uint32_t(i % kScaleBlockBytes);
-        const uint64_t c = (i / kScaleBlockBytes) % chunks, mt = (i / kScaleBlockBytes / chunks) % mts;
-        const uint64_t e = i / kScaleBlockBytes / chunks / mts;
+        const uint64_t b = (i / kScaleBlockBytes) % 2, c = (i / kScaleBlockBytes / 2) % chunks;
+        const uint64_t mt = (i / kScaleBlockBytes / 2 / chunks) % mts, e = i / kScaleBlockBytes / 2 / chunks / mts;
         const uint32_t r = (o >> 4) + 32u * ((o >> 2) & 3u), kb = o & 3u;
-        uint8_t b = down.scales[e * down.expert_stride_s + (down.row0 + mt * 128 + r) * down.row_stride_s + down.col0_s + c * 4 + kb];
-        if (b < 2 || b > 252) odd = 1;
-        dst[i] = b == 255 ? 254 : b;
+        uint8_t v = down.scales[e * down.expert_stride_s + (down.row0 + mt * kPairM + b * kTileM + r) * down.row_stride_s +
+                                down.col0_s + c * 4 + kb];
+        if (v < 2 || v > 252) odd = 1;
+        dst[i] = v == 255 ? 254 : v;
     }
     if (odd) atomicOr(abnormal, 1u);
 }

@@ -3,24 +3,27 @@
 // Both projections run the same main loop with the weights as the MMA "A"
 // operand and the routed tokens as "B":
 //     D[weight row, token] = sum_k E2M1(w) 2^sw  *  E4M3(x) 2^sx
-// A work item is (token tile of one expert) x (128 weight rows). Weight rows
-// are the tcgen05 M = 128; the token count of the tile is the MMA N (a multiple
-// of 16, up to 240), so one to two routed rows per expert at decode do not pad
-// to a 128-row tile, and a few hundred rows per expert at prefill fill N.
+// A work item is (token tile of one expert) x (256 weight rows = two 128-row
+// MMA tiles). Weight rows are the tcgen05 M = 128; the token count of the tile
+// is the MMA N (a multiple of 16, at most 112), so one or two routed rows per
+// expert at decode do not pad to a 128-row tile. The two MMA tiles of an item
+// share the token operand in shared memory and accumulate side by side in
+// tensor memory: for FC1 they are the gate and up rows of the same 128
+// features, so a feature's gate and up land in the same tensor-memory lane.
 //
-//   producer warp : TMA loads per 128-wide K chunk - the 4-bit weight tile
+//   producer warp : TMA loads per 128-wide K chunk - the 4-bit weight rows
 //                   (unpacked to 8-bit containers by the 16U4_ALIGN16B tensor
-//                   map), the E4M3 token rows, and the two UE8M0 scale blocks.
+//                   map), the E4M3 token rows, and the UE8M0 scale blocks.
 //   MMA warp      : copies the scale blocks to tensor memory (tcgen05.cp) and
-//                   issues 4 x tcgen05.mma kind::mxf8f6f4.block_scale per chunk
+//                   issues 8 x tcgen05.mma kind::mxf8f6f4.block_scale per chunk
 //                   into one of two accumulator buffers in tensor memory.
-//   4 epilogue    : drain the other accumulator buffer.
-//     warps         FC1: lanes 0..63 hold gate, 64..127 up of the same 64
-//                   features; the halves meet through shared memory, then
-//                   SiLU(gate)*up and the e4m3fn-k32-v1 quantiser run in
-//                   registers (one warp = one K32 block per token) and the
-//                   quantised intermediate plus its scale bytes are stored in
-//                   the layout FC2's loads want.
+//   16 epilogue   : drain the other accumulator buffer (four warps per lane
+//     warps         quadrant, so each scheduler has four warps to hide latency).
+//                   FC1: SiLU(gate)*up and the e4m3fn-k32-v1 quantiser run in
+//                   registers - a warp's 32 lanes are the 32 features of one
+//                   K32 block, so the block maximum is one warp reduction -
+//                   and the quantised intermediate plus its scale bytes are
+//                   stored in the layout FC2's loads want.
 //                   FC2: FP32 rows are stored at their original route index.
 //
 // Reference behaviour: FC1 crates/mimo26-expert/kernels/b1/grouped.cu:71-113,
@@ -33,9 +36,12 @@
 
 namespace m26b {
 
-constexpr int kGemmThreads = 192;
-constexpr int kAccStride = 256;     // tensor-memory columns between the two accumulator buffers
-constexpr int kSfaCol0 = 240, kSfbCol0 = 244;          // scale columns, slot 0 (slot 1 = +256)
+constexpr int kEpiWarps = 16;
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
+// Tensor memory, 512 columns: accumulator buffer b occupies columns [256 b, 256 b + 224):
+// tile 0 at +0, tile 1 at +112. The two scale slots sit above buffer 0.
+constexpr int kAccStride = 256, kAcc1 = kMaxN;
+constexpr int kSfSlot0 = 224, kSfSlotStride = 16;      // slot: 4 cols SFA tile 0, 4 cols SFA tile 1, 4 cols SFB
 constexpr uint32_t kTmemCols = 512;
 
 enum { kModeFc1 = 1, kModeFc2 = 2 };
@@ -44,14 +50,14 @@ struct GemmArgs {
     const TokenTile* tiles;
     const WorkItem* items;
     const uint32_t* n_items;
-    const uint8_t* sfa;         // weight scale blocks [E][m_tiles][k_chunks][512]
-    const uint8_t* sfb;         // token scale blocks  [tile][k_chunks][2][512]
-    int m_tiles;                // 128-row weight tiles per expert
+    const uint8_t* sfa;         // weight scale blocks [E][m_tiles][k_chunks][2][512]
+    const uint8_t* sfb;         // token scale blocks  [tile][k_chunks][512]
+    int m_tiles;                // 256-row weight tile pairs per expert
     int k_chunks;               // K / 128
     uint32_t* fault;            // one word, OR of fault codes
     // FC1 epilogue
     uint8_t* mid_q;             // [grouped rows][i_local] E4M3
-    uint8_t* mid_sf;            // scale blocks for FC2 [tile][i_local/128][2][512]
+    uint8_t* mid_sf;            // scale blocks for FC2 [tile][i_local/128][512]
     float* mid_f32;             // optional FP32 copy of silu(gate)*up, same indexing as mid_q
     int i_local;
     // FC2 epilogue
@@ -61,11 +67,10 @@ struct GemmArgs {
 
 template <int B_ROWS, int STAGES>
 struct GemmSmem {
-    alignas(1024) uint8_t a[STAGES][kTileM * 128];
+    alignas(1024) uint8_t a[STAGES][kPairM * 128];
     alignas(1024) uint8_t b[STAGES][B_ROWS * 128];
-    alignas(16) uint8_t sfa[STAGES][kScaleBlockBytes];
-    alignas(16) uint8_t sfb[STAGES][2 * kScaleBlockBytes];
-    alignas(16) float xbuf[2][2][16][64];
+    alignas(16) uint8_t sfa[STAGES][2 * kScaleBlockBytes];
+    alignas(16) uint8_t sfb[STAGES][kScaleBlockBytes];
     uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -79,7 +84,9 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return __fmul_rn(s, u);
 }
 
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+}
 
 template <int MODE, int B_ROWS, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -92,7 +99,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], kEpiWarps); }
         s.abort_flag = 0;
         mbar_init_fence();
     }
@@ -114,20 +121,18 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
                 const WorkItem wi = p.items[it];
                 const TokenTile tt = p.tiles[wi.tile];
-                const int w_row = (tt.expert * p.m_tiles + wi.m_tile) * kTileM;
-                const uint8_t* sfa_g = p.sfa + size_t(tt.expert * p.m_tiles + wi.m_tile) * p.k_chunks * kScaleBlockBytes;
-                const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * 2 * kScaleBlockBytes;
-                const int n_blk = tt.n_mma > 128 ? 2 : 1;
-                const uint32_t tx = kTileM * 64 + tt.n_mma * 128 + kScaleBlockBytes * (1 + n_blk);
+                const int w_row = (tt.expert * p.m_tiles + wi.m_tile) * kPairM;
+                const uint8_t* sfa_g = p.sfa + size_t(tt.expert * p.m_tiles + wi.m_tile) * p.k_chunks * 2 * kScaleBlockBytes;
+                const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
+                const uint32_t tx = kPairM * 64 + tt.n_mma * 128 + 3 * kScaleBlockBytes;
                 for (int c = 0; c < p.k_chunks; ++c) {
                     if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(&s.full[stage], tx);
                     tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
                     for (int r = 0; r < tt.n_mma; r += 16)
                         tma_load_2d(s.b[stage] + r * 128, &map_x, c * kChunkK, tt.row_base + r, &s.full[stage]);
-                    bulk_load(s.sfa[stage], sfa_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
-                    bulk_load(s.sfb[stage], sfb_g + size_t(c) * 2 * kScaleBlockBytes, kScaleBlockBytes * n_blk,
-                              &s.full[stage]);
+                    bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
+                    bulk_load(s.sfb[stage], sfb_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -143,24 +148,26 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
                 if (!mbar_wait(&s.acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tb + acc * kAccStride;
-                const int n_blk = tt.n_mma > 128 ? 2 : 1;
+                const uint32_t d0 = tb + acc * kAccStride, d1 = d0 + kAcc1;
                 for (int c = 0; c < p.k_chunks; ++c) {
                     if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     // consecutive chunks alternate between two scale slots in tensor memory
-                    const uint32_t slot = sf_slot * kAccStride;
+                    const uint32_t t_sf = tb + kSfSlot0 + sf_slot * kSfSlotStride;
                     sf_slot ^= 1u;
-                    const uint32_t t_sfa = tb + slot + kSfaCol0, t_sfb = tb + slot + kSfbCol0;
-                    tc_cp_scales(t_sfa, desc_scale_block(smem_u32(s.sfa[stage])));
-                    tc_cp_scales(t_sfb, desc_scale_block(smem_u32(s.sfb[stage])));
-                    if (n_blk == 2) tc_cp_scales(t_sfb + 4, desc_scale_block(smem_u32(s.sfb[stage]) + kScaleBlockBytes));
+                    const uint32_t sfa_s = smem_u32(s.sfa[stage]);
+                    tc_cp_scales(t_sf, desc_scale_block(sfa_s));
+                    tc_cp_scales(t_sf + 4, desc_scale_block(sfa_s + kScaleBlockBytes));
+                    tc_cp_scales(t_sf + 8, desc_scale_block(smem_u32(s.sfb[stage])));
                     const uint32_t a0 = smem_u32(s.a[stage]), b0 = smem_u32(s.b[stage]);
 #pragma unroll
-                    for (uint32_t kb = 0; kb < 4; ++kb)
-                        tc_mma_mx(d_tmem, desc_sw128(a0 + kb * 32), desc_sw128(b0 + kb * 32),
-                                  idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), kb, kb), t_sfa, t_sfb,
-                                  (c | int(kb)) ? 1u : 0u);
+                    for (uint32_t kb = 0; kb < 4; ++kb) {
+                        const uint32_t idesc = idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), kb, kb);
+                        const uint64_t bd = desc_sw128(b0 + kb * 32);
+                        const uint32_t accum = (c | int(kb)) ? 1u : 0u;
+                        tc_mma_mx(d0, desc_sw128(a0 + kb * 32), bd, idesc, t_sf, t_sf + 8, accum);
+                        tc_mma_mx(d1, desc_sw128(a0 + kTileM * 128 + kb * 32), bd, idesc, t_sf + 4, t_sf + 8, accum);
+                    }
                     tc_commit(&s.empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -170,7 +177,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        const uint32_t q = uint32_t(warp) & 3u;       // tensor-memory lane quadrant this warp may read
+        const uint32_t q = uint32_t(warp) & 3u;            // tensor-memory lane quadrant this warp may read
+        const uint32_t wq = uint32_t(warp - 2) >> 2;       // which of the quadrant's warps this is
+        constexpr uint32_t kWpq = kEpiWarps / 4;
         uint32_t local = 0;
         bool ok = true;
         for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
@@ -178,19 +187,22 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const TokenTile tt = p.tiles[wi.tile];
             const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
             mbar_wait(&s.acc_full[acc], acc_phase, abort_flag);
-            // The four epilogue warps must agree on leaving: they meet at a named barrier below.
+            // all epilogue warps leave together or not at all
             epi_bar_sync();
             if (*abort_flag) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_acc = tb + acc * kAccStride + ((q * 32u) << 16);
             if constexpr (MODE == kModeFc2) {
-                float* ybase = p.y + size_t(wi.m_tile) * kTileM + q * 32u + lane;
-                for (int c0 = 0; c0 < tt.n_mma; c0 += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(t_acc + uint32_t(c0), r);
+                // the quadrant's warps split (weight tile of the pair) x (groups of 8 tokens);
+                // hidden row = 256 m + 128 tile + 32 q + lane
+                const uint32_t tile = wq & 1u;
+                float* ybase = p.y + size_t(wi.m_tile) * kPairM + tile * kTileM + q * 32u + lane;
+                for (int c0 = int(wq >> 1) * 8; c0 < tt.n_mma; c0 += 8 * int(kWpq / 2)) {
+                    uint32_t r[8];
+                    tmem_ld8(t_acc + tile * kAcc1 + uint32_t(c0), r);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < 8; ++j) {
                         const int t = c0 + j;
                         if (t < tt.n_valid) {
                             const int32_t route = p.original_routes[tt.row_base + t];
@@ -199,44 +211,32 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     }
                 }
             } else {
-                const bool is_gate = q < 2u;
-                const uint32_t fblk = q & 1u;                    // which 32-feature block of the 64-feature tile
-                const uint32_t f = fblk * 32u + lane;
-                const int feat0 = wi.m_tile * 64 + int(fblk) * 32;   // first feature of this warp's K32 block
-                const int blk = feat0 / 32, cch = blk >> 2, kb = blk & 3;
-                uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + cch) * 2 * kScaleBlockBytes;
-                uint32_t par = 0;
+                // lanes are the 32 features of K32 block (4 m + q) of the intermediate; the quadrant's
+                // warps take alternate groups of 8 tokens
+                const int feat0 = wi.m_tile * kTileM + int(q) * 32;
+                uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + wi.m_tile) * kScaleBlockBytes;
+                uint8_t* mq = p.mid_q + size_t(tt.row_base) * p.i_local + feat0 + lane;
+                float* mf = p.mid_f32 ? p.mid_f32 + size_t(tt.row_base) * p.i_local + feat0 + lane : nullptr;
                 uint32_t fault = 0;
-                for (int c0 = 0; c0 < tt.n_mma; c0 += 32, par ^= 1u) {
-                    uint32_t lo[16], hi[16];
-                    tmem_ld16(t_acc + uint32_t(c0), lo);
-                    tmem_ld16(t_acc + uint32_t(c0 + 16), hi);
+                for (int c0 = int(wq) * 8; c0 < tt.n_mma; c0 += 8 * int(kWpq)) {
+                    uint32_t g[8], u[8];
+                    tmem_ld8(t_acc + uint32_t(c0), g);
+                    tmem_ld8(t_acc + kAcc1 + uint32_t(c0), u);
                     tmem_wait_ld();
-                    // gate warps keep columns c0..c0+15 and hand the next 16 to the up warps; up warps the reverse
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        s.xbuf[par][is_gate ? 0 : 1][j][f] = __uint_as_float(is_gate ? hi[j] : lo[j]);
-                    epi_bar_sync();
-                    const int t0 = c0 + (is_gate ? 0 : 16);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + j;
+                    for (int j = 0; j < 8; ++j) {
+                        const int t = c0 + j;
                         if (t >= tt.n_valid) continue;   // warp-uniform
-                        const float other = s.xbuf[par][is_gate ? 1 : 0][j][f];
-                        const float g = is_gate ? __uint_as_float(lo[j]) : other;
-                        const float u = is_gate ? other : __uint_as_float(hi[j]);
-                        const float h = silu_mul(g, u);
-                        const size_t row = size_t(tt.row_base + t);
-                        if (p.mid_f32) p.mid_f32[row * p.i_local + feat0 + lane] = h;
+                        const float h = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+                        if (mf) mf[size_t(t) * p.i_local] = h;
                         const uint32_t bits = __float_as_uint(h);
                         const uint32_t amax = __reduce_max_sync(0xffffffffu, bits & 0x7fffffffu);
                         if (amax >= 0x7f800000u) { fault |= kFaultQuantNonfinite; continue; }
                         const int k = quant_v1_scale_exp(amax);
                         const uint32_t code = quant_v1_payload(bits, k);
                         if (__any_sync(0xffffffffu, !quant_v1_finite(code, k))) { fault |= kFaultQuantOverflow; continue; }
-                        p.mid_q[row * p.i_local + feat0 + lane] = uint8_t(code);
-                        if (lane == 0)
-                            sf_tile[(t >> 7) * kScaleBlockBytes + scale_block_offset(t & 127, kb)] = uint8_t(k + 127);
+                        mq[size_t(t) * p.i_local] = uint8_t(code);
+                        if (lane == 0) sf_tile[scale_block_offset(t, int(q))] = uint8_t(k + 127);
                     }
                 }
                 if (fault && lane == 0) atomicOr(p.fault, fault);

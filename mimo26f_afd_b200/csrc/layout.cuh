@@ -5,11 +5,16 @@
 // hidden 4096, expert intermediate 2048, 256 routed experts, top-8.
 //
 // Operand image of one layer on one tensor-parallel rank (I_local = 2048 / G):
-//   w13  [E][I_local/64][128 rows][H/2 bytes]   rows 0..63 gate, 64..127 up of
-//                                               the same 64 intermediate features
-//   s13  [E][I_local/64][H/128][512 bytes]      scale blocks (see scale_block_offset)
+//   w13  [E][I_local/128][256 rows][H/2 bytes]  rows 0..127 gate, 128..255 up of
+//                                               the same 128 intermediate features
+//   s13  [E][I_local/128][H/128][2][512 bytes]  scale blocks (see scale_block_offset):
+//                                               block 0 the gate rows, block 1 the up rows
 //   w2   [E][H rows][I_local/2 bytes]           down_proj rows, this rank's K slice
-//   s2   [E][H/128][I_local/128][512 bytes]
+//   s2   [E][H/256][I_local/128][2][512 bytes]  block b covers rows 256 t + 128 b + r
+// A GEMM work item pairs two 128-row weight tiles (gate/up of the same
+// features, or two consecutive down_proj row tiles) against one token tile:
+// weights are 4-bit, so fetching more weight rows per token tile is the cheap
+// way to raise arithmetic intensity on the L2 -> shared-memory path.
 // Payload bytes keep the checkpoint's nibble order (low nibble = even k,
 // crates/mimo26-expert/src/mxfp4.rs:20-22), which is also the order the TMA
 // 4-bit unpack expects, so payload rows are copied, never re-nibbled.
@@ -25,6 +30,8 @@ constexpr int kTopK = 8;
 constexpr int kBlockK = 32;            // one UE8M0 scale per 32 K elements
 constexpr int kChunkK = 128;           // K elements per pipeline stage (4 MMA K-steps)
 constexpr int kTileM = 128;            // weight rows per MMA (the tcgen05 M)
+constexpr int kPairM = 256;            // weight rows per work item (two MMAs share the token tile)
+constexpr int kMaxN = 112;             // largest token tile: two FP32 accumulators of N columns, double buffered
 constexpr int kScaleBlockBytes = 512;  // 128 rows x 4 K32 blocks
 
 // One 512-byte scale block covers 128 rows x 4 consecutive K32 blocks in the
@@ -42,7 +49,7 @@ struct TokenTile {
     int32_t n_mma;      // n_valid rounded up to a multiple of 16 (the MMA N)
 };
 
-// One unit of GEMM work: a token tile against one 128-row weight tile.
+// One unit of GEMM work: a token tile against one 256-row weight tile pair.
 struct WorkItem {
     int32_t tile;
     int32_t m_tile;
@@ -56,7 +63,7 @@ struct LaunchClass {
     int stages;
 };
 __host__ __device__ constexpr LaunchClass launch_class(uint32_t tokens) {
-    return tokens <= 32 ? LaunchClass{32, 32, 9} : tokens <= 128 ? LaunchClass{128, 128, 6} : LaunchClass{240, 256, 4};
+    return tokens <= 32 ? LaunchClass{32, 32, 6} : LaunchClass{kMaxN, kMaxN, 4};
 }
 
 // Plan metadata written by the planner (one 32-byte record).

@@ -81,9 +81,8 @@ cudaError_t launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm
 template <int MODE>
 cudaError_t launch_gemm_class(uint32_t rows, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int ctas,
                               cudaStream_t st) {
-    if (rows <= 32) return launch_gemm<MODE, 32, 9>(mw, mx, a, ctas, st);
-    if (rows <= 128) return launch_gemm<MODE, 128, 6>(mw, mx, a, ctas, st);
-    return launch_gemm<MODE, 256, 4>(mw, mx, a, ctas, st);
+    if (rows <= 32) return launch_gemm<MODE, 32, 6>(mw, mx, a, ctas, st);
+    return launch_gemm<MODE, kMaxN, 4>(mw, mx, a, ctas, st);
 }
 
 // Device status block of one pass: PlanMeta then four fault words.
@@ -108,10 +107,12 @@ struct m26b_layer {
 struct m26b_scratch {
     cudaStream_t st = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr, ea = nullptr, ec = nullptr;
+    cudaEvent_t kev[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // per-kernel timing (debug bit 1)
+    bool kev_quant = false, kev_valid = false;
     int device = 0, sms = 0;
     uint32_t debug = 0;
     Dev xq, xs, iw, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
-        partial, bf16, status, gather;
+        partial, bf16, status, gather, plan_cnt;
     CUtensorMap map_x, map_mid;
     void* map_x_base = nullptr; void* map_mid_base = nullptr;
     uint64_t map_x_rows = 0, map_mid_rows = 0; int map_mid_cols = 0;
@@ -158,8 +159,8 @@ int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, u
         return fail("m26b layer prepare", e, 2);
     cudaFree(flag); flag = nullptr;
     L->all_normal = h == 0;
-    if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(kExperts) * 2 * i_local, kHidden / 2, kTileM) ||
-        !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(kExperts) * kHidden, uint64_t(i_local) / 2, kTileM)) {
+    if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(kExperts) * 2 * i_local, kHidden / 2, kPairM) ||
+        !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(kExperts) * kHidden, uint64_t(i_local) / 2, kPairM)) {
         set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight operands");
         m26b_layer_free(L);
         return 2;
@@ -194,15 +195,16 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
     M26B_CK(S->gweights.ensure(routes * 4), "m26b gweights alloc");
     M26B_CK(S->experts.ensure(kExperts * sizeof(ExpertPlan)), "m26b experts alloc");
     M26B_CK(S->tiles.ensure(tiles_max * sizeof(TokenTile)), "m26b tiles alloc");
-    M26B_CK(S->items1.ensure(tiles_max * (i_local / 64) * sizeof(WorkItem)), "m26b fc1 items alloc");
-    M26B_CK(S->items2.ensure(tiles_max * (kHidden / kTileM) * sizeof(WorkItem)), "m26b fc2 items alloc");
-    M26B_CK(S->sfb1.ensure(tiles_max * (kHidden / kChunkK) * 2 * kScaleBlockBytes), "m26b sfb alloc");
-    M26B_CK(S->mid_sf.ensure(tiles_max * (i_local / kChunkK) * 2 * kScaleBlockBytes), "m26b mid scale alloc");
+    M26B_CK(S->items1.ensure(tiles_max * (i_local / kTileM) * sizeof(WorkItem)), "m26b fc1 items alloc");
+    M26B_CK(S->items2.ensure(tiles_max * (kHidden / kPairM) * sizeof(WorkItem)), "m26b fc2 items alloc");
+    M26B_CK(S->sfb1.ensure(tiles_max * (kHidden / kChunkK) * kScaleBlockBytes), "m26b sfb alloc");
+    M26B_CK(S->mid_sf.ensure(tiles_max * (i_local / kChunkK) * kScaleBlockBytes), "m26b mid scale alloc");
     if (S->debug & 1u) M26B_CK(S->mid_f32.ensure(rows_cap * i_local * 4), "m26b mid f32 alloc");
     M26B_CK(S->y.ensure(routes * kHidden * 4), "m26b y alloc");
     M26B_CK(S->partial.ensure(size_t(rows) * kHidden * 4), "m26b partial alloc");
     M26B_CK(S->bf16.ensure(size_t(rows) * kHidden * 2), "m26b bf16 alloc");
     M26B_CK(S->status.ensure(sizeof(Status) * 64), "m26b status alloc");
+    M26B_CK(S->plan_cnt.ensure(128 * kExperts * 4), "m26b plan counts alloc");
     M26B_CK(S->x_perm.ensure(rows_cap * kHidden), "m26b x_perm alloc");
     M26B_CK(S->mid_q.ensure(rows_cap * i_local), "m26b mid alloc");
     const uint64_t xr = S->x_perm.n / kHidden, mr = S->mid_q.n / i_local;
@@ -230,17 +232,32 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     cudaError_t e;
     const uint32_t routes = rows * kTopK;
     const LaunchClass lc = launch_class(rows);
-    const int mt1 = L->i_local / 64, mt2 = kHidden / kTileM;
+    const int mt1 = L->i_local / kTileM, mt2 = kHidden / kPairM;
     M26B_CK(cudaMemsetAsync(status, 0, sizeof(Status), st), "m26b status clear");
     if (events) M26B_CK(cudaEventRecord(S->e0, st), "m26b event 0");
     PlanOut po{S->inverse.as<int32_t>(), S->original.as<int32_t>(), S->gweights.as<float>(), S->experts.as<ExpertPlan>(),
                S->tiles.as<TokenTile>(), S->items1.as<WorkItem>(), S->items2.as<WorkItem>(), &status->meta};
-    plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, po);
+    const bool kt = (S->debug & 2u) != 0;
+    if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
+    if (routes <= 4096) {
+        plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, po);
+    } else {
+        // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
+        const uint32_t slabs = (routes + 1023u) / 1024u;
+        const uint32_t n_cta = slabs < 128u ? slabs : 128u;
+        const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
+        uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
+        plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, L->resident, cta_routes, cta_cnt, &status->meta);
+        plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, po);
+        plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po);
+    }
     M26B_CK(cudaGetLastError(), "m26b plan launch");
+    if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
     permute_kernel<<<routes < 65535u * 8u ? routes : 65535u * 8u, 256, 0, st>>>(
         xq, xs, ids, S->original.as<int32_t>(), S->experts.as<ExpertPlan>(), &status->meta, routes,
         S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input);
     M26B_CK(cudaGetLastError(), "m26b permute launch");
+    if (kt) M26B_CK(cudaEventRecord(S->kev[3], st), "m26b event");
     GemmArgs a{};
     a.tiles = S->tiles.as<TokenTile>();
     a.i_local = L->i_local;
@@ -255,17 +272,20 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     a.fault = &status->fault_fc1;
     M26B_CK(launch_gemm_class<kModeFc1>(rows, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
     if (events) M26B_CK(cudaEventRecord(S->ea, st), "m26b event a");
+    if (kt) M26B_CK(cudaEventRecord(S->kev[4], st), "m26b event");
     // FC2: weights w2 (K = i_local), tokens mid_q
     a.items = S->items2.as<WorkItem>(); a.n_items = &status->meta.n_items_fc2;
     a.sfa = L->s2; a.sfb = S->mid_sf.as<uint8_t>(); a.m_tiles = mt2; a.k_chunks = L->i_local / kChunkK;
     a.fault = &status->fault_fc2;
     M26B_CK(launch_gemm_class<kModeFc2>(rows, L->map_w2, S->map_mid, a, S->sms, st), "m26b fc2 launch");
     if (events) M26B_CK(cudaEventRecord(S->ec, st), "m26b event c");
+    if (kt) M26B_CK(cudaEventRecord(S->kev[5], st), "m26b event");
     const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
     const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
     route_reduce_kernel<<<blocks, 256, 0, st>>>(S->y.as<float>(), w, rows, partial_out, bf16_out, &status->fault_reduce);
     M26B_CK(cudaGetLastError(), "m26b reduce launch");
     if (events) M26B_CK(cudaEventRecord(S->e1, st), "m26b event 1");
+    if (kt) { M26B_CK(cudaEventRecord(S->kev[6], st), "m26b event"); S->kev_valid = true; }
     S->last_rows = rows; S->last_i_local = L->i_local; S->last_ids = ids; S->last_xq = xq; S->last_xs = xs;
     return 0;
 }
@@ -378,7 +398,8 @@ int m26b_scratch_new(m26b_scratch** out, char* err, size_t errlen) {
     if ((e = cudaStreamCreateWithFlags(&S->st, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaEventCreate(&S->e0)) != cudaSuccess || (e = cudaEventCreate(&S->e1)) != cudaSuccess ||
         (e = cudaEventCreate(&S->ea)) != cudaSuccess || (e = cudaEventCreate(&S->ec)) != cudaSuccess ||
-        (e = cudaMallocHost(reinterpret_cast<void**>(&S->hstatus), sizeof(Status) * 64)) != cudaSuccess) {
+        (e = cudaMallocHost(reinterpret_cast<void**>(&S->hstatus), sizeof(Status) * 64)) != cudaSuccess ||
+        (e = [&] { cudaError_t r = cudaSuccess; for (auto& ev : S->kev) if (r == cudaSuccess) r = cudaEventCreate(&ev); return r; }()) != cudaSuccess) {
         set_err(err, errlen, "m26b scratch stream/events", e);
         m26b_scratch_free(S);
         return 2;
@@ -393,6 +414,7 @@ void m26b_scratch_free(m26b_scratch* S) {
     if (S->e1) cudaEventDestroy(S->e1);
     if (S->ea) cudaEventDestroy(S->ea);
     if (S->ec) cudaEventDestroy(S->ec);
+    for (auto& ev : S->kev) if (ev) cudaEventDestroy(ev);
     if (S->st) cudaStreamDestroy(S->st);
     if (S->hstatus) cudaFreeHost(S->hstatus);
     delete S;
@@ -478,7 +500,7 @@ int m26b_quantize_dev(const void* x, int x_dtype, uint64_t n_elems, int codec, u
     if (!n_elems) return 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint64_t threads = n_elems / 8;
-    const uint32_t blocks = uint32_t((threads + 255) / 256 < 148 * 16 ? (threads + 255) / 256 : 148 * 16);
+    const uint32_t blocks = uint32_t((threads + 255) / 256 < 148 * 64 ? (threads + 255) / 256 : 148 * 64);
     if (x_dtype == 0 && codec == 0) quantize_rows_kernel<0, uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);
     else if (x_dtype == 0) quantize_rows_kernel<1, uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);
     else if (codec == 0) quantize_rows_kernel<0, float><<<blocks, 256, 0, st>>>(static_cast<const float*>(x), n_elems, payload, scales, fault_dev);
@@ -507,11 +529,13 @@ int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtyp
         // the quantiser's fault word is cleared with the status block, so clear first
         cudaError_t e;
         M26B_CK(cudaMemsetAsync(&status[1], 0, sizeof(Status), st), "m26b status clear");
+        if (S->debug & 2u) M26B_CK(cudaEventRecord(S->kev[0], st), "m26b event");
         rc = m26b_quantize_dev(x, x_dtype, uint64_t(rows) * kHidden, codec, S->xq.as<uint8_t>(), S->xs.as<uint8_t>(),
                                &status[1].fault_input, st, err, errlen);
         if (rc) return rc;
         xq = S->xq.as<uint8_t>(); xs = S->xs.as<uint8_t>();
     }
+    S->kev_quant = x_dtype != 2;
     rc = enqueue_pass(L, S, xq, xs, ids, weights, rows, bf16_out, partial_out ? partial_out : nullptr, status, st, false,
                       err, errlen);
     if (rc) return rc;
@@ -559,6 +583,16 @@ int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, fl
     return 0;
 }
 
+int m26b_scratch_timings(m26b_scratch* S, float* ms6, char* err, size_t errlen) {
+    if (!S || !ms6 || !S->kev_valid) { set_msg(err, errlen, "m26b timings: enable debug flag 2 and run a pass first"); return 1; }
+    cudaError_t e;
+    M26B_CK(cudaEventSynchronize(S->kev[6]), "m26b timings sync");
+    ms6[0] = 0.f;
+    if (S->kev_quant) M26B_CK(cudaEventElapsedTime(&ms6[0], S->kev[0], S->kev[1]), "m26b timings");
+    for (int i = 1; i < 6; ++i) M26B_CK(cudaEventElapsedTime(&ms6[i], S->kev[i], S->kev[i + 1]), "m26b timings");
+    return 0;
+}
+
 int m26b_scratch_peek(m26b_scratch* S, int what, void* host_dst, uint64_t bytes, char* err, size_t errlen) {
     if (!S || !host_dst || !S->last_rows) { set_msg(err, errlen, "m26b peek: nothing to read"); return 1; }
     cudaError_t e;
@@ -594,8 +628,7 @@ int m26b_scratch_peek(m26b_scratch* S, int what, void* host_dst, uint64_t bytes,
                 const uint64_t local = g - uint64_t(p.rbase), tile = uint64_t(p.tile_start) + local / uint64_t(p.width);
                 const uint64_t lr = local % uint64_t(p.width);
                 for (uint64_t b = 0; b < il / kBlockK; ++b)
-                    dst[g * (il / kBlockK) + b] = blocks[((tile * chunks + b / 4) * 2 + (lr >> 7)) * kScaleBlockBytes +
-                                                        scale_block_offset(int(lr & 127), int(b & 3))];
+                    dst[g * (il / kBlockK) + b] = blocks[(tile * chunks + b / 4) * kScaleBlockBytes + scale_block_offset(int(lr), int(b & 3))];
             }
             return 0;
         }

@@ -118,6 +118,13 @@ class Scratch:
         err = C.create_string_buffer(256)
         _check(_native.lib().m26b_scratch_status(self._h, _ptr(stream), err, 256), err)
 
+    def timings(self) -> dict:
+        """Per-kernel GPU milliseconds of the last pass (needs ``set_debug(2)`` before the pass)."""
+        ms = (C.c_float * 6)()
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_scratch_timings(self._h, ms, err, 256), err)
+        return dict(zip(("quantize", "plan", "permute", "fc1", "fc2", "combine"), [float(v) for v in ms]))
+
     def peek(self, what: str, dtype, shape) -> np.ndarray:
         """Copy a stage buffer of the last pass to the host (parity tests)."""
         out = np.empty(shape, dtype=dtype)

@@ -75,10 +75,12 @@ def layer_np(seed: int, experts, scale_lo: int = 118, scale_hi: int = 122) -> di
     return out
 
 
-def layer_torch(seed: int, device, scale_lo: int = 118, scale_hi: int = 122) -> dict:
-    """All 256 experts' tensors generated on ``device`` with torch integer ops; bit-identical to
-    ``expert_tensor_np``. torch is the device allocator here, not a compute path of the product."""
+def layer_torch(seed: int, device, scale_lo: int = 118, scale_hi: int = 122, n_experts: int = E) -> dict:
+    """The first ``n_experts`` (default all 256) experts' tensors generated on ``device`` with torch integer
+    ops; bit-identical to ``expert_tensor_np``. torch is the device allocator here, not a compute path."""
     import torch
+
+    E = n_experts  # noqa: N806 (shadows the module constant inside this function only)
 
     def s64(v: int) -> int:
         return v - (1 << 64) if v >= (1 << 63) else v

@@ -1,0 +1,55 @@
+"""Multi-GPU layouts of the expert FFN on one NVSwitch box: one process per GPU, torch.distributed for the plumbing.
+
+The reference shards the expert intermediate dimension over four machines (TP4: rank r owns gate/up rows
+[512 r, 512 (r+1)) and the matching down columns, ``crates/mimo26-repack/src/geom.rs:29-35``) and sums the four
+BF16 partial planes on the coordinator in FP32, in rank order (``crates/mimo26-coordinator/kernels/glue.cu:202-213``,
+``crates/mimo26-wire/src/l4.rs:169-244``). Here the ranks are G in {1, 2, 4, 8} GPUs: inputs are replicated, each
+rank produces a full-width BF16 partial, and the planes are exchanged with one all-gather over NVLink; every rank
+then adds them in rank order with the library's kernel, which keeps the reference's bit-exact sum
+(an NCCL ring reduce would round per hop, in ring order).
+"""
+from __future__ import annotations
+
+H, I = 4096, 2048
+
+
+def tp_slice(tp_rank: int, tp_size: int):
+    """(first intermediate feature, local width) of a rank; every K32 / K128 block stays inside one rank."""
+    if tp_size not in (1, 2, 4, 8) or not 0 <= tp_rank < tp_size:
+        raise ValueError(f"tp_rank {tp_rank} / tp_size {tp_size}: tp_size must be 1, 2, 4 or 8")
+    il = I // tp_size
+    return tp_rank * il, il
+
+
+def shard_tokens(tokens: int, rank: int, world: int):
+    """Data-parallel split of a token batch: contiguous [lo, hi) for this rank (used when ranks serve
+    independent requests; no collective on the data path)."""
+    base, extra = divmod(tokens, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def all_gather_planes(plane, group=None):
+    """All-gather one BF16 partial plane [tokens, 4096] per rank; returns the list in rank order.
+    Works on CUDA tensors (NCCL) and on CPU tensors (gloo), so the exchange can be tested without GPUs."""
+    import torch.distributed as dist
+
+    import torch
+
+    world = dist.get_world_size(group)
+    # exchanged as raw bytes: the planes are bit patterns, and not every backend moves 16-bit integer tensors
+    raw = plane.contiguous().view(torch.uint8)
+    out = [torch.empty_like(raw) for _ in range(world)]
+    dist.all_gather(out, raw, group=group)
+    return [o.view(plane.dtype).view(plane.shape) for o in out]
+
+
+def tp_combine(plane, out_f32, group=None, stream=None):
+    """Rank-ordered FP32 sum of every rank's BF16 plane into ``out_f32`` (CUDA tensors)."""
+    from . import expert
+
+    planes = all_gather_planes(plane, group)
+    if not plane.is_cuda:
+        raise RuntimeError("tp_combine sums on the GPU; there is no CPU path (tests use the oracle for the sum)")
+    expert.rank_sum_dev(planes, plane.numel(), out_f32, stream=stream)
+    return planes
