@@ -141,6 +141,23 @@ int m26b_route_reduce_dev(const float* y, const float* weights, uint32_t rows, f
 int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
                       size_t errlen);
 
+/* Route plan without any allocation. No counterpart in the reference.
+ * For callers that must not allocate device memory while they run: a serving loop that gave every free byte of the
+ * GPU to resident expert weights at start-up, a request handler that has to stay clear of cudaMalloc's device-wide
+ * synchronisation while other streams compute, or code running where an allocation failure cannot be handled.
+ * It is the multi-CTA stable planner of m26b_ffn / m26b_ffn_dev (expert-major, stable inside an expert); its
+ * working memory (per-CTA expert counts, expert table, token tiles and work items, about 0.47 MB) is a fixed array
+ * inside the library, present on every GPU that loads it until the process exits.
+ * ids / weights: device, [rows*8], token-major top-8. Outputs, device: inverse[rows*8] (original route -> grouped
+ * route), original_routes[rows*8] (grouped route -> original route), grouped_weights[rows*8], meta_out[8]
+ * (word 0: 0 ok / 1 plan rejected, word 1 token tiles, 4 experts with routes, 5 largest per-expert count). Work is
+ * enqueued on `stream`; nothing is synchronised. rows <= 4096, larger requests return 1 with a message.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that call before any
+ * stream capture. All calls on one GPU share the array: calls whose kernels overlap on the GPU race, so keep them on
+ * one stream or order them with events. Calls cudaMalloc / cudaFree never. */
+int m26b_plan_static(const int32_t* ids, const float* weights, uint32_t rows, int32_t* inverse, int32_t* original_routes,
+                     float* grouped_weights, uint32_t* meta_out, void* stream, char* err, size_t errlen);
+
 /* Library identity: "m26b-expert <version> sm_100a". */
 const char* m26b_version(void);
 

@@ -14,6 +14,7 @@ from .expert import (  # noqa: F401
     ffn,
     ffn_dev,
     ffn_strided,
+    plan_static,
     quantize_dev,
     rank_sum_dev,
     route_reduce_dev,

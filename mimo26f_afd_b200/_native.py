@@ -12,7 +12,7 @@ SYMBOLS = (
     "m26b_layer_new", "m26b_layer_new_tp", "m26b_layer_new_from_checkpoint", "m26b_layer_all_normal",
     "m26b_layer_i_local", "m26b_layer_free", "m26b_scratch_new", "m26b_scratch_free", "m26b_ffn", "m26b_ffn_dev",
     "m26b_scratch_status", "m26b_scratch_set_debug", "m26b_scratch_timings", "m26b_scratch_peek", "m26b_quantize_dev",
-    "m26b_route_reduce_dev", "m26b_rank_sum_dev", "m26b_version",
+    "m26b_route_reduce_dev", "m26b_rank_sum_dev", "m26b_plan_static", "m26b_version",
 )
 
 _lib = None
@@ -50,6 +50,7 @@ def lib() -> C.CDLL:
     L.m26b_quantize_dev.argtypes = [vp, C.c_int, C.c_uint64, C.c_int, u8p, u8p, u32p, vp, *err]
     L.m26b_route_reduce_dev.argtypes = [f32p, f32p, C.c_uint32, f32p, u16p, u32p, vp, *err]
     L.m26b_rank_sum_dev.argtypes = [C.POINTER(vp), C.c_int, C.c_uint64, f32p, vp, *err]
+    L.m26b_plan_static.argtypes = [i32p, f32p, C.c_uint32, i32p, i32p, f32p, u32p, vp, *err]
     L.m26b_version.restype = C.c_char_p
     for name in SYMBOLS:
         if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version"):

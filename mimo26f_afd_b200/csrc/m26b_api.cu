@@ -593,6 +593,68 @@ int m26b_scratch_timings(m26b_scratch* S, float* ms6, char* err, size_t errlen) 
     return 0;
 }
 
+// ---- allocation-free route planner ---------------------------------------------------------
+// Scratch of m26b_plan_static: per-CTA expert counts, the expert table, token tiles and work
+// items of the plan, and an all-resident table. It lives in the library's data segment on every
+// GPU that loads the library (about 0.47 MB) instead of coming from cudaMalloc.
+namespace {
+constexpr uint32_t kStaticPlanMaxRows = 4096;
+constexpr size_t kStaticPlanTiles = size_t(kStaticPlanMaxRows) * kTopK / 32 + kExperts;
+struct StaticPlanScratch {
+    uint32_t cta_cnt[128 * kExperts];
+    ExpertPlan experts[kExperts];
+    TokenTile tiles[kStaticPlanTiles];
+    WorkItem items_fc1[kStaticPlanTiles * (kInter / kTileM)];
+    WorkItem items_fc2[kStaticPlanTiles * (kHidden / kPairM)];
+    uint8_t resident[kExperts];
+};
+}  // namespace
+static __device__ __align__(256) unsigned char g_static_plan_scratch[sizeof(StaticPlanScratch)];
+
+int m26b_plan_static(const int32_t* ids, const float* weights, uint32_t rows, int32_t* inverse, int32_t* original_routes,
+                     float* grouped_weights, uint32_t* meta_out, void* stream, char* err, size_t errlen) {
+    if (!ids || !weights || !inverse || !original_routes || !grouped_weights || !meta_out || !rows) {
+        set_msg(err, errlen, "m26b plan_static: bad arguments");
+        return 1;
+    }
+    if (rows > kStaticPlanMaxRows) {
+        if (err && errlen)
+            std::snprintf(err, errlen, "m26b plan_static: %u rows exceed the built-in scratch (at most %u rows per call)", rows,
+                          kStaticPlanMaxRows);
+        return 1;
+    }
+    cudaError_t e;
+    int dev = -1;
+    M26B_CK(cudaGetDevice(&dev), "m26b plan_static device");
+    if (dev < 0 || dev >= 64) { set_msg(err, errlen, "m26b plan_static: device ordinal out of range"); return 1; }
+    // In host code the array's name only stands for the symbol; the device address has to be asked for, once
+    // per device, with that device current.
+    static StaticPlanScratch* addr[64] = {};
+    if (!addr[dev]) {
+        void* p = nullptr;
+        M26B_CK(cudaGetSymbolAddress(&p, g_static_plan_scratch), "m26b plan_static scratch address");
+        addr[dev] = static_cast<StaticPlanScratch*>(p);
+    }
+    StaticPlanScratch* sc = addr[dev];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PlanMeta* meta = reinterpret_cast<PlanMeta*>(meta_out);
+    // the array keeps the previous call's contents: the fault word and the residency table are rewritten
+    // here, every other field is overwritten by the kernels before it is read
+    M26B_CK(cudaMemsetAsync(meta, 0, sizeof(PlanMeta), st), "m26b plan_static clear");
+    M26B_CK(cudaMemsetAsync(sc->resident, 1, kExperts, st), "m26b plan_static residency");
+    const uint32_t routes = rows * kTopK;
+    const LaunchClass lc = launch_class(rows);
+    const uint32_t slabs = (routes + 1023u) / 1024u;
+    const uint32_t n_cta = slabs < 128u ? slabs : 128u;
+    const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
+    PlanOut po{inverse, original_routes, grouped_weights, sc->experts, sc->tiles, sc->items_fc1, sc->items_fc2, meta};
+    plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, sc->resident, cta_routes, sc->cta_cnt, meta);
+    plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, po);
+    plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, cta_routes, sc->cta_cnt, po);
+    M26B_CK(cudaGetLastError(), "m26b plan_static launch");
+    return 0;
+}
+
 int m26b_scratch_peek(m26b_scratch* S, int what, void* host_dst, uint64_t bytes, char* err, size_t errlen) {
     if (!S || !host_dst || !S->last_rows) { set_msg(err, errlen, "m26b peek: nothing to read"); return 1; }
     cudaError_t e;

@@ -221,3 +221,16 @@ def rank_sum_dev(planes, n: int, out, stream=None) -> None:
     arr = (C.c_void_p * len(planes))(*[_ptr(p) for p in planes])
     err = C.create_string_buffer(256)
     _check(_native.lib().m26b_rank_sum_dev(arr, len(planes), n, _ptr(out), _ptr(stream), err, 256), err)
+
+
+PLAN_STATIC_MAX_ROWS = 4096
+
+
+def plan_static(ids, weights, rows: int, inverse, original_routes, grouped_weights, meta, stream=None) -> None:
+    """Stable route plan that allocates nothing: for callers that must not touch the device allocator while
+    they run (all free memory already committed to weights, or no tolerance for cudaMalloc's device-wide stall).
+    Device buffers in and out; at most ``PLAN_STATIC_MAX_ROWS`` rows. The planner's working memory is a fixed array
+    inside the library shared by every call on the GPU, so calls that overlap on the device race."""
+    err = C.create_string_buffer(256)
+    _check(_native.lib().m26b_plan_static(_ptr(ids), _ptr(weights), rows, _ptr(inverse), _ptr(original_routes),
+                                          _ptr(grouped_weights), _ptr(meta), _ptr(stream), err, 256), err)
