@@ -5,7 +5,7 @@
 //     D[weight row, token] = sum_k E2M1(w) 2^sw  *  E4M3(x) 2^sx
 // A work item is (token tile of one expert) x (256 weight rows = two 128-row
 // MMA tiles). Weight rows are the tcgen05 M = 128; the token count of the tile
-// is the MMA N (a multiple of 16, at most 112), so one or two routed rows per
+// is the MMA N (a multiple of 16, at most 128), so one or two routed rows per
 // expert at decode do not pad to a 128-row tile. The two MMA tiles of an item
 // share the token operand in shared memory and accumulate side by side in
 // tensor memory: for FC1 they are the gate and up rows of the same 128
@@ -16,9 +16,13 @@
 //                   map), the E4M3 token rows, and the UE8M0 scale blocks.
 //   MMA warp      : copies the scale blocks to tensor memory (tcgen05.cp) and
 //                   issues 8 x tcgen05.mma kind::mxf8f6f4.block_scale per chunk
-//                   into one of two accumulator buffers in tensor memory.
-//   16 epilogue   : drain the other accumulator buffer (four warps per lane
-//     warps         quadrant, so each scheduler has four warps to hide latency).
+//                   into the accumulator pair in tensor memory.
+//   16 epilogue   : four warps per lane quadrant. Each first pulls its slice of
+//     warps         the accumulators into registers (64 values per thread) and
+//                   hands tensor memory straight back to the MMA warp, so the
+//                   next item's main loop runs while the epilogue math proceeds
+//                   from registers; one accumulator buffer is enough, which is
+//                   what lets the token tile be 128 wide.
 //                   FC1: SiLU(gate)*up and the e4m3fn-k32-v1 quantiser run in
 //                   registers - a warp's 32 lanes are the 32 features of one
 //                   K32 block, so the block maximum is one warp reduction -
@@ -38,10 +42,10 @@ namespace m26b {
 
 constexpr int kEpiWarps = 16;
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
-// Tensor memory, 512 columns: accumulator buffer b occupies columns [256 b, 256 b + 224):
-// tile 0 at +0, tile 1 at +112. The two scale slots sit above buffer 0.
-constexpr int kAccStride = 256, kAcc1 = kMaxN;
-constexpr int kSfSlot0 = 224, kSfSlotStride = 16;      // slot: 4 cols SFA tile 0, 4 cols SFA tile 1, 4 cols SFB
+// Tensor memory: weight tile 0 accumulates in columns [0, 128), tile 1 in [128, 256); the two
+// scale slots sit above them.
+constexpr int kAcc1 = kMaxN;
+constexpr int kSfSlot0 = 256, kSfSlotStride = 16;      // slot: 4 cols SFA tile 0, 4 cols SFA tile 1, 4 cols SFB
 constexpr uint32_t kTmemCols = 512;
 
 enum { kModeFc1 = 1, kModeFc2 = 2 };
@@ -71,21 +75,21 @@ struct GemmSmem {
     alignas(1024) uint8_t b[STAGES][B_ROWS * 128];
     alignas(16) uint8_t sfa[STAGES][2 * kScaleBlockBytes];
     alignas(16) uint8_t sfb[STAGES][kScaleBlockBytes];
-    uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    uint64_t full[STAGES], empty[STAGES], acc_full, acc_empty;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-// E-ACT-CR32 activation: no positive exponential is evaluated, ordered FP32 ops.
+// E-ACT-CR32 activation: e = exp(-|g|) (never a positive exponential), s = g / (1 + e) or g e / (1 + e),
+// h = s u. The exponential and the reciprocal of 1 + e (which lies in [1, 2]) use the hardware
+// approximations: together under 1e-6 relative, inside the 1e-5 stage tolerance, at a fifth of the
+// instructions of expf and an IEEE divide. That matters: this runs once per intermediate element and the
+// epilogue must stay cheaper than the main loop it overlaps.
 __device__ __forceinline__ float silu_mul(float g, float u) {
-    const float e = expf(-fabsf(g));
-    const float d = __fadd_rn(1.0f, e);
-    const float s = g >= 0.0f ? __fdiv_rn(g, d) : __fdiv_rn(__fmul_rn(g, e), d);
-    return __fmul_rn(s, u);
-}
-
-__device__ __forceinline__ void epi_bar_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+    const float e = __expf(-fabsf(g));
+    const float r = __frcp_rn(__fadd_rn(1.0f, e));
+    const float num = g >= 0.0f ? g : __fmul_rn(g, e);
+    return __fmul_rn(__fmul_rn(num, r), u);
 }
 
 template <int MODE, int B_ROWS, int STAGES>
@@ -99,7 +103,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], kEpiWarps); }
+        mbar_init(&s.acc_full, 1);
+        mbar_init(&s.acc_empty, kEpiWarps);
         s.abort_flag = 0;
         mbar_init_fence();
     }
@@ -143,107 +148,132 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (elect_one()) {
             uint32_t stage = 0, phase = 0, local = 0, sf_slot = 0;
             bool ok = true;
+            // everything about a stage that does not change is computed once: this thread issues eleven tensor
+            // operations per chunk and shares its scheduler with four epilogue warps
+            const uint64_t a_desc0 = desc_sw128(smem_u32(s.a[0])), b_desc0 = desc_sw128(smem_u32(s.b[0]));
+            const uint64_t sfa_desc0 = desc_scale_block(smem_u32(s.sfa[0])), sfb_desc0 = desc_scale_block(smem_u32(s.sfb[0]));
+            constexpr uint64_t kAStage = sizeof(s.a[0]) >> 4, kBStage = sizeof(s.b[0]) >> 4;
+            constexpr uint64_t kSfaStage = sizeof(s.sfa[0]) >> 4, kSfbStage = sizeof(s.sfb[0]) >> 4;
             for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
                 const TokenTile tt = p.tiles[p.items[it].tile];
-                const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-                if (!mbar_wait(&s.acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                const uint32_t idesc0 = idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), 0, 0);
+                // the accumulators are free once every epilogue warp has pulled its slice of the previous item
+                if (!mbar_wait(&s.acc_empty, (local & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d0 = tb + acc * kAccStride, d1 = d0 + kAcc1;
+                const uint32_t d0 = tb, d1 = tb + kAcc1;
                 for (int c = 0; c < p.k_chunks; ++c) {
                     if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     // consecutive chunks alternate between two scale slots in tensor memory
                     const uint32_t t_sf = tb + kSfSlot0 + sf_slot * kSfSlotStride;
                     sf_slot ^= 1u;
-                    const uint32_t sfa_s = smem_u32(s.sfa[stage]);
-                    tc_cp_scales(t_sf, desc_scale_block(sfa_s));
-                    tc_cp_scales(t_sf + 4, desc_scale_block(sfa_s + kScaleBlockBytes));
-                    tc_cp_scales(t_sf + 8, desc_scale_block(smem_u32(s.sfb[stage])));
-                    const uint32_t a0 = smem_u32(s.a[stage]), b0 = smem_u32(s.b[stage]);
+                    const uint64_t sfa_d = sfa_desc0 + stage * kSfaStage;
+                    tc_cp_scales(t_sf, sfa_d);
+                    tc_cp_scales(t_sf + 4, sfa_d + (kScaleBlockBytes >> 4));
+                    tc_cp_scales(t_sf + 8, sfb_desc0 + stage * kSfbStage);
+                    const uint64_t ad = a_desc0 + stage * kAStage, bd = b_desc0 + stage * kBStage;
 #pragma unroll
                     for (uint32_t kb = 0; kb < 4; ++kb) {
-                        const uint32_t idesc = idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), kb, kb);
-                        const uint64_t bd = desc_sw128(b0 + kb * 32);
+                        // K32 slice kb: 32 bytes further into the swizzle atom (descriptor addresses count 16 bytes);
+                        // scale-factor byte kb of each tensor-memory column (instruction-descriptor bits 4-5 and 29-30)
+                        const uint32_t idesc = idesc0 | (kb << 4) | (kb << 29);
                         const uint32_t accum = (c | int(kb)) ? 1u : 0u;
-                        tc_mma_mx(d0, desc_sw128(a0 + kb * 32), bd, idesc, t_sf, t_sf + 8, accum);
-                        tc_mma_mx(d1, desc_sw128(a0 + kTileM * 128 + kb * 32), bd, idesc, t_sf + 4, t_sf + 8, accum);
+                        tc_mma_mx(d0, ad + 2 * kb, bd + 2 * kb, idesc, t_sf, t_sf + 8, accum);
+                        tc_mma_mx(d1, ad + ((kTileM * 128) >> 4) + 2 * kb, bd + 2 * kb, idesc, t_sf + 4, t_sf + 8, accum);
                     }
                     tc_commit(&s.empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) tc_commit(&s.acc_full[acc]);
+                if (ok) tc_commit(&s.acc_full);
             }
             if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t q = uint32_t(warp) & 3u;            // tensor-memory lane quadrant this warp may read
-        const uint32_t wq = uint32_t(warp - 2) >> 2;       // which of the quadrant's warps this is
-        constexpr uint32_t kWpq = kEpiWarps / 4;
+        const uint32_t wq = uint32_t(warp - 2) >> 2;       // which of the quadrant's four warps this is
+        static_assert(kEpiWarps == 16 && kMaxN == 128, "the register drain below is sized for 4 warps per quadrant");
         uint32_t local = 0;
         bool ok = true;
         for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
             const WorkItem wi = p.items[it];
             const TokenTile tt = p.tiles[wi.tile];
-            const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-            mbar_wait(&s.acc_full[acc], acc_phase, abort_flag);
-            // all epilogue warps leave together or not at all
-            epi_bar_sync();
-            if (*abort_flag) { ok = false; break; }
+            if (!mbar_wait(&s.acc_full, local & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t t_acc = tb + acc * kAccStride + ((q * 32u) << 16);
+            const uint32_t t_acc = tb + ((q * 32u) << 16);
             if constexpr (MODE == kModeFc2) {
-                // the quadrant's warps split (weight tile of the pair) x (groups of 8 tokens);
+                // warp (q, wq): weight tile (wq & 1) of the pair, token groups (wq >> 1), +2, +4 ... of 8 tokens;
                 // hidden row = 256 m + 128 tile + 32 q + lane
                 const uint32_t tile = wq & 1u;
+                uint32_t r[8][8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int c0 = (int(wq >> 1) + 2 * g) * 8;
+                    if (c0 < tt.n_mma) tmem_ld8(t_acc + tile * kAcc1 + uint32_t(c0), r[g]);
+                }
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.acc_empty);
                 float* ybase = p.y + size_t(wi.m_tile) * kPairM + tile * kTileM + q * 32u + lane;
-                for (int c0 = int(wq >> 1) * 8; c0 < tt.n_mma; c0 += 8 * int(kWpq / 2)) {
-                    uint32_t r[8];
-                    tmem_ld8(t_acc + tile * kAcc1 + uint32_t(c0), r);
-                    tmem_wait_ld();
+                // lane l holds the route of token (wq >> 1) * 8 + 16 (l / 8) + l % 8: one load covers four groups
+                int32_t routes_lo = -1, routes_hi = -1;
+                {
+                    const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
+                    if (t < tt.n_valid) routes_lo = p.original_routes[tt.row_base + t];
+                    if (t + 64 < tt.n_valid) routes_hi = p.original_routes[tt.row_base + t + 64];
+                }
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const int t = c0 + j;
-                        if (t < tt.n_valid) {
-                            const int32_t route = p.original_routes[tt.row_base + t];
-                            ybase[size_t(route) * kHidden] = __uint_as_float(r[j]);
-                        }
+                        const int32_t route = __shfl_sync(0xffffffffu, g < 4 ? routes_lo : routes_hi, (g & 3) * 8 + j);
+                        if (route >= 0) ybase[size_t(route) * kHidden] = __uint_as_float(r[g][j]);
                     }
                 }
             } else {
-                // lanes are the 32 features of K32 block (4 m + q) of the intermediate; the quadrant's
-                // warps take alternate groups of 8 tokens
+                // lanes are the 32 features of K32 block (4 m + q) of the intermediate; warp wq of the quadrant takes
+                // token groups wq, wq + 4, wq + 8, wq + 12 of 8 tokens
+                uint32_t gt[4][8], up[4][8];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int c0 = (int(wq) + 4 * g) * 8;
+                    if (c0 < tt.n_mma) {
+                        tmem_ld8(t_acc + uint32_t(c0), gt[g]);
+                        tmem_ld8(t_acc + kAcc1 + uint32_t(c0), up[g]);
+                    }
+                }
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.acc_empty);
                 const int feat0 = wi.m_tile * kTileM + int(q) * 32;
                 uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + wi.m_tile) * kScaleBlockBytes;
                 uint8_t* mq = p.mid_q + size_t(tt.row_base) * p.i_local + feat0 + lane;
                 float* mf = p.mid_f32 ? p.mid_f32 + size_t(tt.row_base) * p.i_local + feat0 + lane : nullptr;
                 uint32_t fault = 0;
-                for (int c0 = int(wq) * 8; c0 < tt.n_mma; c0 += 8 * int(kWpq)) {
-                    uint32_t g[8], u[8];
-                    tmem_ld8(t_acc + uint32_t(c0), g);
-                    tmem_ld8(t_acc + kAcc1 + uint32_t(c0), u);
-                    tmem_wait_ld();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int c0 = (int(wq) + 4 * g) * 8;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int t = c0 + j;
                         if (t >= tt.n_valid) continue;   // warp-uniform
-                        const float h = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+                        const float h = silu_mul(__uint_as_float(gt[g][j]), __uint_as_float(up[g][j]));
                         if (mf) mf[size_t(t) * p.i_local] = h;
                         const uint32_t bits = __float_as_uint(h);
                         const uint32_t amax = __reduce_max_sync(0xffffffffu, bits & 0x7fffffffu);
                         if (amax >= 0x7f800000u) { fault |= kFaultQuantNonfinite; continue; }
                         const int k = quant_v1_scale_exp(amax);
                         const uint32_t code = quant_v1_payload(bits, k);
-                        if (__any_sync(0xffffffffu, !quant_v1_finite(code, k))) { fault |= kFaultQuantOverflow; continue; }
+                        // a payload exponent is at most 8: payload * 2^k can only leave FP32 range when k > 119
+                        if (k > 119 && __any_sync(0xffffffffu, !quant_v1_finite(code, k))) { fault |= kFaultQuantOverflow; continue; }
                         mq[size_t(t) * p.i_local] = uint8_t(code);
                         if (lane == 0) sf_tile[scale_block_offset(t, int(q))] = uint8_t(k + 127);
                     }
                 }
                 if (fault && lane == 0) atomicOr(p.fault, fault);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.acc_empty[acc]);
         }
         if (!ok && lane == 0) atomicOr(p.fault, uint32_t(kFaultPipeline));
     }

@@ -31,7 +31,7 @@ constexpr int kBlockK = 32;            // one UE8M0 scale per 32 K elements
 constexpr int kChunkK = 128;           // K elements per pipeline stage (4 MMA K-steps)
 constexpr int kTileM = 128;            // weight rows per MMA (the tcgen05 M)
 constexpr int kPairM = 256;            // weight rows per work item (two MMAs share the token tile)
-constexpr int kMaxN = 112;             // largest token tile: two FP32 accumulators of N columns, double buffered
+constexpr int kMaxN = 128;             // largest token tile (the MMA N); two FP32 accumulators of N columns side by side
 constexpr int kScaleBlockBytes = 512;  // 128 rows x 4 K32 blocks
 
 // One 512-byte scale block covers 128 rows x 4 consecutive K32 blocks in the
