@@ -69,6 +69,13 @@ struct GemmArgs {
     const int32_t* original_routes;
 };
 
+// Token-operand tensor maps with boxes of 128, 64, 32 and 16 rows: a tile's rows are fetched with the fewest
+// boxes (binary decomposition of its row count). One 128-row box costs the copy engine about 500 cycles, eight
+// 16-row boxes about 680, and the main loop has 512 cycles per chunk to spare at N = 128.
+struct TokenMaps {
+    CUtensorMap box[4];
+};
+
 template <int B_ROWS, int STAGES>
 struct GemmSmem {
     alignas(1024) uint8_t a[STAGES][kPairM * 128];
@@ -79,6 +86,15 @@ struct GemmSmem {
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
+
+#ifdef M26B_GEMM_TIMING
+__device__ long long g_gemm_timing[148 * 16];
+#define M26B_T0(v) const long long v = clock64()
+#define M26B_ACC(slot, v) g_gemm_timing[blockIdx.x * 16 + (slot)] += clock64() - (v)
+#else
+#define M26B_T0(v)
+#define M26B_ACC(slot, v)
+#endif
 
 // E-ACT-CR32 activation: e = exp(-|g|) (never a positive exponential), s = g / (1 + e) or g e / (1 + e),
 // h = s u. The exponential and the reciprocal of 1 + e (which lies in [1, 2]) use the hardware
@@ -94,8 +110,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 
 template <int MODE, int B_ROWS, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               const GemmArgs p) {
+gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_x, const GemmArgs p) {
     using Smem = GemmSmem<B_ROWS, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -114,13 +129,15 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const uint32_t tb = s.tmem_base;
     const uint32_t n_items = *p.n_items;
+    M26B_T0(t_all);
     volatile uint32_t* abort_flag = &s.abort_flag;
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (elect_one()) {
             tma_prefetch_desc(&map_w);
-            tma_prefetch_desc(&map_x);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tma_prefetch_desc(&maps_x.box[i]);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
@@ -131,11 +148,20 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
                 const uint32_t tx = kPairM * 64 + tt.n_mma * 128 + 3 * kScaleBlockBytes;
                 for (int c = 0; c < p.k_chunks; ++c) {
+                    M26B_T0(tw);
                     if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    M26B_ACC(0, tw);
                     mbar_expect_tx(&s.full[stage], tx);
                     tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
-                    for (int r = 0; r < tt.n_mma; r += 16)
-                        tma_load_2d(s.b[stage] + r * 128, &map_x, c * kChunkK, tt.row_base + r, &s.full[stage]);
+                    int r = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int rows = 128 >> i;
+                        if (tt.n_mma - r >= rows) {   // n_mma <= 128: each size is needed at most once
+                            tma_load_2d(s.b[stage] + r * 128, &maps_x.box[i], c * kChunkK, tt.row_base + r, &s.full[stage]);
+                            r += rows;
+                        }
+                    }
                     bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
                     bulk_load(s.sfb[stage], sfb_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -158,11 +184,15 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const TokenTile tt = p.tiles[p.items[it].tile];
                 const uint32_t idesc0 = idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), 0, 0);
                 // the accumulators are free once every epilogue warp has pulled its slice of the previous item
+                M26B_T0(ta);
                 if (!mbar_wait(&s.acc_empty, (local & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                M26B_ACC(2, ta);
                 tc_fence_after();
                 const uint32_t d0 = tb, d1 = tb + kAcc1;
                 for (int c = 0; c < p.k_chunks; ++c) {
+                    M26B_T0(tf);
                     if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
+                    M26B_ACC(1, tf);
                     tc_fence_after();
                     // consecutive chunks alternate between two scale slots in tensor memory
                     const uint32_t t_sf = tb + kSfSlot0 + sf_slot * kSfSlotStride;
@@ -198,7 +228,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
             const WorkItem wi = p.items[it];
             const TokenTile tt = p.tiles[wi.tile];
+            M26B_T0(te);
             if (!mbar_wait(&s.acc_full, local & 1u, abort_flag)) { ok = false; break; }
+            if (warp == 2 && lane == 0) { M26B_ACC(3, te); }
+            M26B_T0(tc);
             tc_fence_after();
             const uint32_t t_acc = tb + ((q * 32u) << 16);
             if constexpr (MODE == kModeFc2) {
@@ -274,11 +307,13 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (fault && lane == 0) atomicOr(p.fault, fault);
             }
+            if (warp == 2 && lane == 0) { M26B_ACC(4, tc); }
         }
         if (!ok && lane == 0) atomicOr(p.fault, uint32_t(kFaultPipeline));
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) { M26B_ACC(5, t_all); }
     if (warp == 1) tmem_dealloc(tb, kTmemCols);
 }
 

@@ -70,7 +70,7 @@ bool make_map(CUtensorMap* m, bool fp4, void* base, uint64_t cols, uint64_t rows
 }
 
 template <int MODE, int B_ROWS, int STAGES>
-cudaError_t launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
+cudaError_t launch_gemm(const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
     const int smem = int(sizeof(GemmSmem<B_ROWS, STAGES>)) + 1024;
     const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -79,7 +79,7 @@ cudaError_t launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm
     return cudaGetLastError();
 }
 template <int MODE>
-cudaError_t launch_gemm_class(uint32_t rows, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int ctas,
+cudaError_t launch_gemm_class(uint32_t rows, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas,
                               cudaStream_t st) {
     if (rows <= 32) return launch_gemm<MODE, 32, 6>(mw, mx, a, ctas, st);
     return launch_gemm<MODE, kMaxN, 4>(mw, mx, a, ctas, st);
@@ -113,7 +113,7 @@ struct m26b_scratch {
     uint32_t debug = 0;
     Dev xq, xs, iw, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
         partial, bf16, status, gather, plan_cnt;
-    CUtensorMap map_x, map_mid;
+    TokenMaps map_x, map_mid;
     void* map_x_base = nullptr; void* map_mid_base = nullptr;
     uint64_t map_x_rows = 0, map_mid_rows = 0; int map_mid_cols = 0;
     std::vector<uint8_t> hiw;
@@ -209,17 +209,19 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
     M26B_CK(S->mid_q.ensure(rows_cap * i_local), "m26b mid alloc");
     const uint64_t xr = S->x_perm.n / kHidden, mr = S->mid_q.n / i_local;
     if (S->map_x_base != S->x_perm.p || S->map_x_rows != xr) {
-        if (!make_map(&S->map_x, false, S->x_perm.p, kHidden, xr, kHidden, 16)) {
-            set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the token operand");
-            return 2;
-        }
+        for (int i = 0; i < 4; ++i)
+            if (!make_map(&S->map_x.box[i], false, S->x_perm.p, kHidden, xr, kHidden, 128u >> i)) {
+                set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the token operand");
+                return 2;
+            }
         S->map_x_base = S->x_perm.p; S->map_x_rows = xr;
     }
     if (S->map_mid_base != S->mid_q.p || S->map_mid_rows != mr || S->map_mid_cols != i_local) {
-        if (!make_map(&S->map_mid, false, S->mid_q.p, uint64_t(i_local), mr, uint64_t(i_local), 16)) {
-            set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the intermediate operand");
-            return 2;
-        }
+        for (int i = 0; i < 4; ++i)
+            if (!make_map(&S->map_mid.box[i], false, S->mid_q.p, uint64_t(i_local), mr, uint64_t(i_local), 128u >> i)) {
+                set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the intermediate operand");
+                return 2;
+            }
         S->map_mid_base = S->mid_q.p; S->map_mid_rows = mr; S->map_mid_cols = i_local;
     }
     return 0;
@@ -322,6 +324,16 @@ bool device_ok(int dev_of_handle, char* err, size_t errlen) {
 extern "C" {
 
 const char* m26b_version(void) { return "m26b-expert 0.1 sm_100a"; }
+
+#ifdef M26B_GEMM_TIMING
+// working-build only: read and clear the per-CTA cycle counters of the GEMM roles
+int m26b_debug_timing(long long* out, int clear) {
+    cudaDeviceSynchronize();
+    if (out) cudaMemcpyFromSymbol(out, m26b::g_gemm_timing, sizeof(long long) * 148 * 16);
+    if (clear) { static long long z[148 * 16] = {}; cudaMemcpyToSymbol(m26b::g_gemm_timing, z, sizeof z); }
+    return 0;
+}
+#endif
 
 int m26b_layer_new_tp(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t tp_rank, uint32_t tp_size,
                       m26b_layer** out, char* err, size_t errlen) {
