@@ -123,9 +123,13 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lan
     }
     return v;
 }
+// Work items: for every token tile, weight tile pairs 0, m_step, 2 m_step ... (m_step 2 when a CTA pair takes two
+// neighbouring weight tile pairs per item).
 __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                     uint32_t rows, const uint8_t* __restrict__ resident, int max_n,
-                                                    int mt_fc1, int mt_fc2, PlanOut o) {
+                                                    int mt_fc1, int mt_fc2, int m_step, PlanOut o) {
+    mt_fc1 /= m_step;
+    mt_fc2 /= m_step;
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
     __shared__ uint32_t i1base[kExperts], i2base[kExperts];
     __shared__ uint32_t wcnt[32][kExperts];
@@ -219,9 +223,9 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
             o.tiles[tstart[e] + j] = TokenTile{int32_t(e), int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
         for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
-            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
         for (uint32_t i = lane; i < ne * mt_fc2; i += 32)
-            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
     }
 }
 
@@ -277,7 +281,9 @@ __global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restr
     }
 }
 __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_t* __restrict__ cta_cnt, int max_n,
-                                                         int mt_fc1, int mt_fc2, PlanOut o) {
+                                                         int mt_fc1, int mt_fc2, int m_step, PlanOut o) {
+    mt_fc1 /= m_step;
+    mt_fc2 /= m_step;
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
     __shared__ uint32_t i1base[kExperts], i2base[kExperts];
     __shared__ uint32_t wsum[4][8];
@@ -325,9 +331,9 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_
             o.tiles[tstart[e] + j] = TokenTile{int32_t(e), int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
         for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
-            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
         for (uint32_t i = lane; i < ne * mt_fc2; i += 32)
-            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne)};
+            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
     }
 }
 __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,

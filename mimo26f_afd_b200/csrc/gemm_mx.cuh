@@ -89,11 +89,18 @@ struct GemmSmem {
 
 #ifdef M26B_GEMM_TIMING
 __device__ long long g_gemm_timing[148 * 16];
+#define M26B_TDECL long long m26b_tacc[16] = {}
 #define M26B_T0(v) const long long v = clock64()
-#define M26B_ACC(slot, v) g_gemm_timing[blockIdx.x * 16 + (slot)] += clock64() - (v)
+#define M26B_ACC(slot, v) m26b_tacc[slot] += clock64() - (v)
+#define M26B_TFLUSH                                                                                              \
+    _Pragma("unroll") for (int ts = 0; ts < 16; ++ts) if (m26b_tacc[ts])                                         \
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_gemm_timing[blockIdx.x * 16 + ts]),                  \
+                  static_cast<unsigned long long>(m26b_tacc[ts]))
 #else
+#define M26B_TDECL
 #define M26B_T0(v)
 #define M26B_ACC(slot, v)
+#define M26B_TFLUSH
 #endif
 
 // E-ACT-CR32 activation: e = exp(-|g|) (never a positive exponential), s = g / (1 + e) or g e / (1 + e),
@@ -129,6 +136,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const uint32_t tb = s.tmem_base;
     const uint32_t n_items = *p.n_items;
+    M26B_TDECL;
     M26B_T0(t_all);
     volatile uint32_t* abort_flag = &s.abort_flag;
 
@@ -314,6 +322,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) { M26B_ACC(5, t_all); }
+    M26B_TFLUSH;
     if (warp == 1) tmem_dealloc(tb, kTmemCols);
 }
 

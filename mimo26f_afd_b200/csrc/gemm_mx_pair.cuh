@@ -1,0 +1,247 @@
+// The grouped block-scaled GEMM on CTA pairs (tcgen05 cta_group::2), used for prefill-sized requests.
+//
+// Same math and work decomposition as gemm_mx.cuh, but two CTAs of a cluster run one MMA together:
+//     M = 256 = 128 weight rows from each CTA's shared memory, accumulated in that CTA's tensor memory,
+//     N = the token tile, whose rows are split between the two CTAs' shared memories.
+// A pair works on one token tile and two neighbouring 256-row weight tile pairs (CTA r takes pair 2j + r), so
+// each SM fetches only half of the token rows. What bounds the single-CTA kernel at prefill is the L2 -> SM
+// path (about 60 B/clk per SM through the copy engine against 64 B/clk needed at N = 128); the pair needs 48,
+// and the smaller token buffer leaves shared memory for a fifth pipeline stage.
+//
+// Per CTA: one producer warp (its weight rows, its half of the token rows, its weight scales, the whole
+// tile's token scales), sixteen epilogue warps (its 128 + 128 accumulator rows). The pair's first CTA also runs
+// the MMA-issue warp. Barriers: the loads of both CTAs report to `full` of the first CTA, whose producer alone
+// announces the byte count of both (a barrier operation on the partner's shared memory costs about a thousand
+// cycles, one on its own a few; the partner's bytes may land before the announcement, which the barrier's
+// transaction count allows); tcgen05.commit
+// arrives on `empty` / `acc_full` of both; every epilogue warp of both CTAs arrives on `acc_empty` of the
+// first. All loads are ordinary per-CTA copies.
+#pragma once
+#include "gemm_mx.cuh"
+
+namespace m26b {
+
+constexpr int kPairStages = 5;
+
+struct PairMaps {
+    CUtensorMap tok[5];     // token rows, boxes of 128 / 64 / 32 / 16 / 8 rows
+    CUtensorMap sfa;        // weight scale blocks as rows of 128 u32; box 2 rows (the two tiles of a pair)
+    CUtensorMap sfb;        // token scale blocks as rows of 128 u32; box 1 row
+};
+
+struct PairSmem {
+    alignas(1024) uint8_t a[kPairStages][kPairM * 128];
+    alignas(1024) uint8_t b[kPairStages][(kMaxN / 2) * 128];
+    alignas(128) uint8_t sfa[kPairStages][2 * kScaleBlockBytes];
+    alignas(128) uint8_t sfb[kPairStages][kScaleBlockBytes];
+    uint64_t full[kPairStages], empty[kPairStages], acc_full, acc_empty;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ PairMaps maps, const GemmArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    PairSmem& s = *reinterpret_cast<PairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kPairStages; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+        mbar_init(&s.acc_full, 1);
+        mbar_init(&s.acc_empty, 2 * kEpiWarps);
+        s.abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) { tmem_alloc_pair(&s.tmem_base, kTmemCols); tmem_relinquish_pair(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the partner's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tb = s.tmem_base;
+    const uint32_t n_items = *p.n_items;
+    volatile uint32_t* abort_flag = &s.abort_flag;
+    M26B_TDECL;
+    M26B_T0(t_all);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (both CTAs)
+        if (elect_one()) {
+            tma_prefetch_desc(&map_w);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs) {
+                const WorkItem wi = p.items[it];
+                const TokenTile tt = p.tiles[wi.tile];
+                const int m_tile = wi.m_tile + int(rank);
+                const int w_row = (tt.expert * p.m_tiles + m_tile) * kPairM;
+                const int sfa_row = (tt.expert * p.m_tiles + m_tile) * p.k_chunks * 2;
+                const int sfb_row = wi.tile * p.k_chunks;
+                const int half = tt.n_mma >> 1;                   // token rows this CTA holds
+                const int tok_row = tt.row_base + int(rank) * half;
+                const uint32_t tx = kPairM * 64 + uint32_t(half) * 128 + 3 * kScaleBlockBytes;
+                for (int c = 0; c < p.k_chunks; ++c) {
+                    M26B_T0(tw);
+                    if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    M26B_ACC(0, tw);
+                    const uint32_t bar = cluster_map(smem_u32(&s.full[stage]), 0);
+                    if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * tx);   // the bytes of both CTAs' loads
+                    tma_load_2d_pair(s.a[stage], &map_w, c * kChunkK, w_row, bar);
+                    int r = 0;
+#pragma unroll
+                    for (int i = 1; i < 5; ++i) {
+                        const int rows = 128 >> i;
+                        if (half - r >= rows) {
+                            tma_load_2d_pair(s.b[stage] + r * 128, &maps.tok[i], c * kChunkK, tok_row + r, bar);
+                            r += rows;
+                        }
+                    }
+                    tma_load_2d_pair(s.sfa[stage], &maps.sfa, 0, sfa_row + 2 * c, bar);
+                    tma_load_2d_pair(s.sfb[stage], &maps.sfb, 0, sfb_row + c, bar);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issue (first CTA of the pair only)
+        if (rank == 0 && elect_one()) {
+            uint32_t stage = 0, phase = 0, local = 0, sf_slot = 0;
+            bool ok = true;
+            const uint64_t a_desc0 = desc_sw128(smem_u32(s.a[0])), b_desc0 = desc_sw128(smem_u32(s.b[0]));
+            const uint64_t sfa_desc0 = desc_scale_block(smem_u32(s.sfa[0])), sfb_desc0 = desc_scale_block(smem_u32(s.sfb[0]));
+            constexpr uint64_t kAStage = sizeof(s.a[0]) >> 4, kBStage = sizeof(s.b[0]) >> 4;
+            constexpr uint64_t kSfaStage = sizeof(s.sfa[0]) >> 4, kSfbStage = sizeof(s.sfb[0]) >> 4;
+            for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs, ++local) {
+                const TokenTile tt = p.tiles[p.items[it].tile];
+                const uint32_t idesc0 = idesc_mx_pair(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), 0, 0);
+                M26B_T0(ta);
+                if (!mbar_wait(&s.acc_empty, (local & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                M26B_ACC(2, ta);
+                tc_fence_after();
+                const uint32_t d0 = tb, d1 = tb + kAcc1;
+                for (int c = 0; c < p.k_chunks; ++c) {
+                    M26B_T0(tf);
+                    if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
+                    M26B_ACC(1, tf);
+                    tc_fence_after();
+                    const uint32_t t_sf = tb + kSfSlot0 + sf_slot * kSfSlotStride;
+                    sf_slot ^= 1u;
+                    const uint64_t sfa_d = sfa_desc0 + stage * kSfaStage;
+                    tc_cp_scales_pair(t_sf, sfa_d);
+                    tc_cp_scales_pair(t_sf + 4, sfa_d + (kScaleBlockBytes >> 4));
+                    tc_cp_scales_pair(t_sf + 8, sfb_desc0 + stage * kSfbStage);
+                    const uint64_t ad = a_desc0 + stage * kAStage, bd = b_desc0 + stage * kBStage;
+#pragma unroll
+                    for (uint32_t kb = 0; kb < 4; ++kb) {
+                        const uint32_t idesc = idesc0 | (kb << 4) | (kb << 29);
+                        const uint32_t accum = (c | int(kb)) ? 1u : 0u;
+                        tc_mma_mx_pair(d0, ad + 2 * kb, bd + 2 * kb, idesc, t_sf, t_sf + 8, accum);
+                        tc_mma_mx_pair(d1, ad + ((kTileM * 128) >> 4) + 2 * kb, bd + 2 * kb, idesc, t_sf + 4, t_sf + 8, accum);
+                    }
+                    tc_commit_pair(&s.empty[stage]);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit_pair(&s.acc_full);
+            }
+            if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs)
+        const uint32_t q = uint32_t(warp) & 3u;
+        const uint32_t wq = uint32_t(warp - 2) >> 2;
+        const uint32_t acc_empty_leader = cluster_map(smem_u32(&s.acc_empty), 0);
+        uint32_t local = 0;
+        bool ok = true;
+        for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs, ++local) {
+            const WorkItem wi = p.items[it];
+            const TokenTile tt = p.tiles[wi.tile];
+            const int m_tile = wi.m_tile + int(rank);
+            M26B_T0(te);
+            if (!mbar_wait(&s.acc_full, local & 1u, abort_flag)) { ok = false; break; }
+            if (warp == 2 && lane == 0) { M26B_ACC(3, te); }
+            M26B_T0(tc);
+            tc_fence_after();
+            const uint32_t t_acc = tb + ((q * 32u) << 16);
+            if constexpr (MODE == kModeFc2) {
+                const uint32_t tile = wq & 1u;
+                uint32_t r[8][8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int c0 = (int(wq >> 1) + 2 * g) * 8;
+                    if (c0 < tt.n_mma) tmem_ld8(t_acc + tile * kAcc1 + uint32_t(c0), r[g]);
+                }
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+                float* ybase = p.y + size_t(m_tile) * kPairM + tile * kTileM + q * 32u + lane;
+                int32_t routes_lo = -1, routes_hi = -1;
+                {
+                    const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
+                    if (t < tt.n_valid) routes_lo = p.original_routes[tt.row_base + t];
+                    if (t + 64 < tt.n_valid) routes_hi = p.original_routes[tt.row_base + t + 64];
+                }
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int32_t route = __shfl_sync(0xffffffffu, g < 4 ? routes_lo : routes_hi, (g & 3) * 8 + j);
+                        if (route >= 0) ybase[size_t(route) * kHidden] = __uint_as_float(r[g][j]);
+                    }
+                }
+            } else {
+                uint32_t gt[4][8], up[4][8];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int c0 = (int(wq) + 4 * g) * 8;
+                    if (c0 < tt.n_mma) {
+                        tmem_ld8(t_acc + uint32_t(c0), gt[g]);
+                        tmem_ld8(t_acc + kAcc1 + uint32_t(c0), up[g]);
+                    }
+                }
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+                const int feat0 = m_tile * kTileM + int(q) * 32;
+                uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + m_tile) * kScaleBlockBytes;
+                uint8_t* mq = p.mid_q + size_t(tt.row_base) * p.i_local + feat0 + lane;
+                float* mf = p.mid_f32 ? p.mid_f32 + size_t(tt.row_base) * p.i_local + feat0 + lane : nullptr;
+                uint32_t fault = 0;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int c0 = (int(wq) + 4 * g) * 8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int t = c0 + j;
+                        if (t >= tt.n_valid) continue;   // warp-uniform
+                        const float h = silu_mul(__uint_as_float(gt[g][j]), __uint_as_float(up[g][j]));
+                        if (mf) mf[size_t(t) * p.i_local] = h;
+                        const uint32_t bits = __float_as_uint(h);
+                        const uint32_t amax = __reduce_max_sync(0xffffffffu, bits & 0x7fffffffu);
+                        if (amax >= 0x7f800000u) { fault |= kFaultQuantNonfinite; continue; }
+                        const int k = quant_v1_scale_exp(amax);
+                        const uint32_t code = quant_v1_payload(bits, k);
+                        if (k > 119 && __any_sync(0xffffffffu, !quant_v1_finite(code, k))) { fault |= kFaultQuantOverflow; continue; }
+                        mq[size_t(t) * p.i_local] = uint8_t(code);
+                        if (lane == 0) sf_tile[scale_block_offset(t, int(q))] = uint8_t(k + 127);
+                    }
+                }
+                if (fault && lane == 0) atomicOr(p.fault, fault);
+            }
+            if (warp == 2 && lane == 0) { M26B_ACC(4, tc); }
+        }
+        if (!ok && lane == 0) atomicOr(p.fault, uint32_t(kFaultPipeline));
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // nothing of either CTA is torn down while the partner may still signal it
+    if (threadIdx.x == 0) { M26B_ACC(5, t_all); }
+    M26B_TFLUSH;
+    if (warp == 1) tmem_dealloc_pair(tb, kTmemCols);
+}
+
+}  // namespace m26b

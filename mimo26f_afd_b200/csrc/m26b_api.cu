@@ -13,6 +13,7 @@
 #include "layout.cuh"
 #include "ffn_kernels.cuh"
 #include "gemm_mx.cuh"
+#include "gemm_mx_pair.cuh"
 
 using namespace m26b;
 
@@ -78,6 +79,57 @@ cudaError_t launch_gemm(const CUtensorMap& mw, const TokenMaps& mx, const GemmAr
     gemm_mx_kernel<MODE, B_ROWS, STAGES><<<ctas, kGemmThreads, smem, st>>>(mw, mx, a);
     return cudaGetLastError();
 }
+// Scale blocks as a 2-D tensor of 128 x u32 rows (one 512-byte block per row), no swizzle.
+bool make_sf_map(CUtensorMap* m, const void* base, uint64_t blocks, uint32_t box_rows) {
+    EncodeTiledFn f = encode_fn();
+    if (!f) return false;
+    cuuint64_t dims[2] = {128, blocks};
+    cuuint64_t strides[1] = {kScaleBlockBytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t es[2] = {1, 1};
+    return f(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MODE>
+cudaError_t launch_gemm_pair(const CUtensorMap& mw, const PairMaps& maps, const GemmArgs& a, int ctas, cudaStream_t st) {
+    const int smem = int(sizeof(PairSmem)) + 1024;
+    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    gemm_mx_pair_kernel<MODE><<<ctas & ~1, kGemmThreads, smem, st>>>(mw, maps, a);
+    return cudaGetLastError();
+}
+
+// How many CTAs of the pair kernels can be resident at once (2 x the co-resident clusters, at most one per SM).
+// The kernels stride their work by the grid size, so a grid larger than this would run its tail as a second
+// wave after the first has finished everything else. 0 if the device cannot place a single pair.
+template <int MODE>
+int pair_resident_ctas(int sms) {
+    const int smem = int(sizeof(PairSmem)) + 1024;
+    if (cudaFuncSetAttribute(gemm_mx_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(sms & ~1));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = size_t(smem);
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at; cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_mx_pair_kernel<MODE>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    const int ctas = 2 * clusters;
+    return ctas < (sms & ~1) ? ctas : (sms & ~1);
+}
+
+// Requests above this many tokens run the CTA-pair kernels (prefill); below, the single-CTA kernels (decode).
+constexpr uint32_t kPairMinRows = 129;
+
 template <int MODE>
 cudaError_t launch_gemm_class(uint32_t rows, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas,
                               cudaStream_t st) {
@@ -101,7 +153,7 @@ struct m26b_layer {
     uint32_t tp_rank = 0, tp_size = 1;
     bool all_normal = false;
     int device = 0;
-    CUtensorMap map_w13, map_w2;
+    CUtensorMap map_w13, map_w2, map_s13, map_s2;
 };
 
 struct m26b_scratch {
@@ -110,10 +162,13 @@ struct m26b_scratch {
     cudaEvent_t kev[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // per-kernel timing (debug bit 1)
     bool kev_quant = false, kev_valid = false;
     int device = 0, sms = 0;
+    int pair_ctas = 0;          // resident CTAs of the pair kernels (0: the device cannot run them)
     uint32_t debug = 0;
     Dev xq, xs, iw, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
         partial, bf16, status, gather, plan_cnt;
     TokenMaps map_x, map_mid;
+    PairMaps pair_x, pair_mid;
+    void* pair_sfb1_base = nullptr; void* pair_midsf_base = nullptr; size_t pair_sfb1_n = 0, pair_midsf_n = 0;
     void* map_x_base = nullptr; void* map_mid_base = nullptr;
     uint64_t map_x_rows = 0, map_mid_rows = 0; int map_mid_cols = 0;
     std::vector<uint8_t> hiw;
@@ -162,6 +217,12 @@ int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, u
     if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(kExperts) * 2 * i_local, kHidden / 2, kPairM) ||
         !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(kExperts) * kHidden, uint64_t(i_local) / 2, kPairM)) {
         set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight operands");
+        m26b_layer_free(L);
+        return 2;
+    }
+    if (!make_sf_map(&L->map_s13, L->s13, s13_bytes / kScaleBlockBytes, 2) ||
+        !make_sf_map(&L->map_s2, L->s2, s2_bytes / kScaleBlockBytes, 2)) {
+        set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight scales");
         m26b_layer_free(L);
         return 2;
     }
@@ -214,6 +275,11 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
                 set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the token operand");
                 return 2;
             }
+        for (int i = 0; i < 5; ++i)
+            if (!make_map(&S->pair_x.tok[i], false, S->x_perm.p, kHidden, xr, kHidden, 128u >> i)) {
+                set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the token operand");
+                return 2;
+            }
         S->map_x_base = S->x_perm.p; S->map_x_rows = xr;
     }
     if (S->map_mid_base != S->mid_q.p || S->map_mid_rows != mr || S->map_mid_cols != i_local) {
@@ -222,7 +288,26 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
                 set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the intermediate operand");
                 return 2;
             }
+        for (int i = 0; i < 5; ++i)
+            if (!make_map(&S->pair_mid.tok[i], false, S->mid_q.p, uint64_t(i_local), mr, uint64_t(i_local), 128u >> i)) {
+                set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the intermediate operand");
+                return 2;
+            }
         S->map_mid_base = S->mid_q.p; S->map_mid_rows = mr; S->map_mid_cols = i_local;
+    }
+    if (S->pair_sfb1_base != S->sfb1.p || S->pair_sfb1_n != S->sfb1.n) {
+        if (!make_sf_map(&S->pair_x.sfb, S->sfb1.p, S->sfb1.n / kScaleBlockBytes, 1)) {
+            set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the token scales");
+            return 2;
+        }
+        S->pair_sfb1_base = S->sfb1.p; S->pair_sfb1_n = S->sfb1.n;
+    }
+    if (S->pair_midsf_base != S->mid_sf.p || S->pair_midsf_n != S->mid_sf.n) {
+        if (!make_sf_map(&S->pair_mid.sfb, S->mid_sf.p, S->mid_sf.n / kScaleBlockBytes, 1)) {
+            set_msg(err, errlen, "m26b: cuTensorMapEncodeTiled failed for the intermediate scales");
+            return 2;
+        }
+        S->pair_midsf_base = S->mid_sf.p; S->pair_midsf_n = S->mid_sf.n;
     }
     return 0;
 }
@@ -239,10 +324,16 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (events) M26B_CK(cudaEventRecord(S->e0, st), "m26b event 0");
     PlanOut po{S->inverse.as<int32_t>(), S->original.as<int32_t>(), S->gweights.as<float>(), S->experts.as<ExpertPlan>(),
                S->tiles.as<TokenTile>(), S->items1.as<WorkItem>(), S->items2.as<WorkItem>(), &status->meta};
+#ifdef M26B_GEMM_TIMING
+    const bool pair = rows >= kPairMinRows && (mt1 % 2 == 0) && S->pair_ctas >= S->sms / 2 && !getenv("M26B_NO_PAIR");
+#else
+    const bool pair = rows >= kPairMinRows && (mt1 % 2 == 0) && S->pair_ctas >= S->sms / 2;
+#endif
+    const int m_step = pair ? 2 : 1;
     const bool kt = (S->debug & 2u) != 0;
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
     if (routes <= 4096) {
-        plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, po);
+        plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, m_step, po);
     } else {
         // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
         const uint32_t slabs = (routes + 1023u) / 1024u;
@@ -250,7 +341,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
         uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
         plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, L->resident, cta_routes, cta_cnt, &status->meta);
-        plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, po);
+        plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step, po);
         plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po);
     }
     M26B_CK(cudaGetLastError(), "m26b plan launch");
@@ -272,14 +363,26 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     a.items = S->items1.as<WorkItem>(); a.n_items = &status->meta.n_items_fc1;
     a.sfa = L->s13; a.sfb = S->sfb1.as<uint8_t>(); a.m_tiles = mt1; a.k_chunks = kHidden / kChunkK;
     a.fault = &status->fault_fc1;
-    M26B_CK(launch_gemm_class<kModeFc1>(rows, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
+    if (pair) {
+        PairMaps pm = S->pair_x;
+        pm.sfa = L->map_s13;
+        M26B_CK(launch_gemm_pair<kModeFc1>(L->map_w13, pm, a, S->pair_ctas, st), "m26b fc1 launch");
+    } else {
+        M26B_CK(launch_gemm_class<kModeFc1>(rows, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
+    }
     if (events) M26B_CK(cudaEventRecord(S->ea, st), "m26b event a");
     if (kt) M26B_CK(cudaEventRecord(S->kev[4], st), "m26b event");
     // FC2: weights w2 (K = i_local), tokens mid_q
     a.items = S->items2.as<WorkItem>(); a.n_items = &status->meta.n_items_fc2;
     a.sfa = L->s2; a.sfb = S->mid_sf.as<uint8_t>(); a.m_tiles = mt2; a.k_chunks = L->i_local / kChunkK;
     a.fault = &status->fault_fc2;
-    M26B_CK(launch_gemm_class<kModeFc2>(rows, L->map_w2, S->map_mid, a, S->sms, st), "m26b fc2 launch");
+    if (pair) {
+        PairMaps pm = S->pair_mid;
+        pm.sfa = L->map_s2;
+        M26B_CK(launch_gemm_pair<kModeFc2>(L->map_w2, pm, a, S->pair_ctas, st), "m26b fc2 launch");
+    } else {
+        M26B_CK(launch_gemm_class<kModeFc2>(rows, L->map_w2, S->map_mid, a, S->sms, st), "m26b fc2 launch");
+    }
     if (events) M26B_CK(cudaEventRecord(S->ec, st), "m26b event c");
     if (kt) M26B_CK(cudaEventRecord(S->kev[5], st), "m26b event");
     const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
@@ -407,6 +510,13 @@ int m26b_scratch_new(m26b_scratch** out, char* err, size_t errlen) {
         return 2;
     }
     S->sms = prop.multiProcessorCount;
+    {
+        const int c1 = pair_resident_ctas<kModeFc1>(S->sms), c2 = pair_resident_ctas<kModeFc2>(S->sms);
+        S->pair_ctas = c1 < c2 ? c1 : c2;
+#ifdef M26B_GEMM_TIMING
+        std::fprintf(stderr, "m26b: %d SMs, %d resident pair CTAs\n", S->sms, S->pair_ctas);
+#endif
+    }
     if ((e = cudaStreamCreateWithFlags(&S->st, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaEventCreate(&S->e0)) != cudaSuccess || (e = cudaEventCreate(&S->e1)) != cudaSuccess ||
         (e = cudaEventCreate(&S->ea)) != cudaSuccess || (e = cudaEventCreate(&S->ec)) != cudaSuccess ||
@@ -661,7 +771,7 @@ int m26b_plan_static(const int32_t* ids, const float* weights, uint32_t rows, in
     const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
     PlanOut po{inverse, original_routes, grouped_weights, sc->experts, sc->tiles, sc->items_fc1, sc->items_fc2, meta};
     plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, sc->resident, cta_routes, sc->cta_cnt, meta);
-    plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, po);
+    plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, 1, po);
     plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, cta_routes, sc->cta_cnt, po);
     M26B_CK(cudaGetLastError(), "m26b plan_static launch");
     return 0;
