@@ -11,6 +11,11 @@ line carries the 8,192-token prefill segment (configs[3]) under "prefill". Weigh
 resident in HBM for `value`, and on the host (pinned) for `e2e`, which goes through the reference-compatible
 host entry point m26b_ffn with both copies inside the timed region.
 
+The timed region is `steps` plain steps (one CUDA-event pair around each, nothing inside, so consecutive kernels
+overlap their launch and set-up as they do in service). The same steps then run once more with an event between
+every two kernels; those per-kernel durations feed `roofline` and `kernels_ms`, and that slower step time is
+reported beside the plain one as `ms_per_step_with_kernel_events`.
+
 With N > 1 ranks the layer is tensor-parallel over the intermediate dimension (the reference's own TP4 scheme,
 generalised): every rank runs the whole batch on its 1/N slice of every expert and the BF16 partial planes are
 exchanged with one NCCL all-gather and summed in rank order on every rank. Total work is fixed: "strong" scaling.
@@ -148,7 +153,6 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
     out = torch.empty((tokens, H), dtype=torch.int16, device=dev)
     total = torch.empty((tokens, H), dtype=torch.float32, device=dev) if world > 1 else None
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # > 126 MB L2
-    scratch.set_debug(2)
 
     def step():
         expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, out, stream=stream.cuda_stream)
@@ -160,22 +164,38 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    scratch.status(stream.cuda_stream)
-    sync_all()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    kern = []
-    with ClockSampler(dev.index or 0) as clocks:
-        for a, b in ev:
+    def timed_steps(with_kernel_events):
+        """`steps` iterations, each bracketed by CUDA events on the launching stream, L2 flushed before each."""
+        scratch.set_debug(2 if with_kernel_events else 0)
+        step()                                               # the first pass after a mode change is not timed
+        scratch.status(stream.cuda_stream)
+        sync_all()
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        per_kernel = []
+        for a, b in pairs:
             flush.fill_(1)                                   # L2 flush between timed iterations (not timed)
             a.record(stream)
             step()
             b.record(stream)
             b.synchronize()
-            kern.append(scratch.timings())
+            if with_kernel_events:
+                per_kernel.append(scratch.timings())
         sync_all()
+        scratch.status(stream.cuda_stream)
+        return pairs, per_kernel
+
+    scratch.set_debug(0)
+    for _ in range(args.warmup):
+        step()
     scratch.status(stream.cuda_stream)
+    sync_all()
+    with ClockSampler(dev.index or 0) as clocks:
+        # the timed region proper: no events inside a step, so the kernels of a step overlap as they do in service
+        ev, _ = timed_steps(False)
+        # the same steps again with an event between every two kernels: the per-kernel durations of the roofline
+        ev_k, kern = timed_steps(True)
+    scratch.set_debug(2)
+    ms_instrumented = float(np.mean([a.elapsed_time(b) for a, b in ev_k]))
     ms = np.array([a.elapsed_time(b) for a, b in ev])
     t = torch.tensor([float(ms.sum())], device=dev)
     if world > 1:
@@ -237,8 +257,9 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
     roof["kernel_ms"] = fc1_ms
     whole = dict(hbm_gbs=(active * EXPERT_BYTES / world + tokens * H * 4 + routes * 8) / (total_ms / args.steps * 1e-3) / 1e9,
                  tflops=FLOP_PER_TOKEN * tokens / world / (total_ms / args.steps * 1e-3) / 1e12)
-    launches = (6 if routes <= 4096 else 8) + (1 if world > 1 else 0)
+    launches = (4 if tokens <= 32 else 6 if routes <= 4096 else 8) + (1 if world > 1 else 0)
     return dict(workload=name, tokens=tokens, active_experts=active, value=value, ms_per_step=total_ms / args.steps,
+                ms_per_step_with_kernel_events=ms_instrumented,
                 e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
                 roofline=roof, whole_step=whole, kernels_ms={k: float(np.mean([x[k] for x in kern])) for k in kern[0]},
                 clocks=clocks.summary(), gpu_launches=launches * args.steps)
@@ -329,9 +350,10 @@ def main():
                                 parallelism=f"tp{world}" if world > 1 else "single", l2="flushed between timed iterations",
                                 input_codec="wire (FP8 E4M3 + UE8M0 K32)"),
                     e2e=main_r["e2e"], gpu_launches=main_r["gpu_launches"], clocks=main_r["clocks"], roofline=main_r["roofline"],
-                    whole_step=main_r["whole_step"], kernels_ms=main_r["kernels_ms"], cpu_baseline=cpu)
+                    whole_step=main_r["whole_step"], kernels_ms=main_r["kernels_ms"],
+                    ms_per_step_with_kernel_events=main_r["ms_per_step_with_kernel_events"], cpu_baseline=cpu)
         if extra:
-            line["prefill"] = {k: extra[k] for k in ("workload", "tokens", "value", "ms_per_step", "e2e", "roofline", "whole_step",
+            line["prefill"] = {k: extra[k] for k in ("workload", "tokens", "value", "ms_per_step", "ms_per_step_with_kernel_events", "e2e", "roofline", "whole_step",
                                                      "kernels_ms", "clocks")}
             line["prefill"]["unit"] = "tokens/s"
         print(json.dumps(line), flush=True)

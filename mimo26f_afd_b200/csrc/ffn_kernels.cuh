@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include "layout.cuh"
 #include "codec.cuh"
+#include "sm100_ptx.cuh"
 
 namespace m26b {
 
@@ -422,6 +423,7 @@ __global__ void __launch_bounds__(256) route_reduce_kernel(const float* __restri
     const float kMax = 3.402823466e+38f;
     const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
     bool failed = false;
+    grid_dep_wait();             // y comes from the FC2 kernel
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint64_t row = i / (kHidden / 4), c4 = i % (kHidden / 4);
         float4 z[kTopK];

@@ -134,6 +134,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    grid_dep_wait();             // the plan and the token rows come from the kernels before this one
+    grid_dep_launch();
     const uint32_t tb = s.tmem_base;
     const uint32_t n_items = *p.n_items;
     M26B_TDECL;

@@ -60,6 +60,8 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     cluster_sync_all();          // the partner's barriers exist before anything arrives on them
     tc_fence_after();
+    grid_dep_wait();             // the plan and the token rows come from the kernels before this one
+    grid_dep_launch();
     const uint32_t tb = s.tmem_base;
     const uint32_t n_items = *p.n_items;
     volatile uint32_t* abort_flag = &s.abort_flag;

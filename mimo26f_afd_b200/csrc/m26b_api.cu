@@ -14,6 +14,7 @@
 #include "ffn_kernels.cuh"
 #include "gemm_mx.cuh"
 #include "gemm_mx_pair.cuh"
+#include "prologue_small.cuh"
 
 using namespace m26b;
 
@@ -70,14 +71,26 @@ bool make_map(CUtensorMap* m, bool fp4, void* base, uint64_t cols, uint64_t rows
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Launch with the programmatic-serialization attribute: the kernel may be placed while the kernel before it in the
+// stream drains, and orders itself with grid_dep_wait().
+template <typename... P, typename... A>
+cudaError_t launch_dependent(void (*kernel)(P...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, A... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
+}
+
 template <int MODE, int B_ROWS, int STAGES>
 cudaError_t launch_gemm(const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
     const int smem = int(sizeof(GemmSmem<B_ROWS, STAGES>)) + 1024;
     const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    gemm_mx_kernel<MODE, B_ROWS, STAGES><<<ctas, kGemmThreads, smem, st>>>(mw, mx, a);
-    return cudaGetLastError();
+    return launch_dependent(gemm_mx_kernel<MODE, B_ROWS, STAGES>, unsigned(ctas), kGemmThreads, size_t(smem), st, mw, mx, a);
 }
 // Scale blocks as a 2-D tensor of 128 x u32 rows (one 512-byte block per row), no swizzle.
 bool make_sf_map(CUtensorMap* m, const void* base, uint64_t blocks, uint32_t box_rows) {
@@ -96,8 +109,7 @@ cudaError_t launch_gemm_pair(const CUtensorMap& mw, const PairMaps& maps, const 
     const int smem = int(sizeof(PairSmem)) + 1024;
     const cudaError_t e = cudaFuncSetAttribute(gemm_mx_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    gemm_mx_pair_kernel<MODE><<<ctas & ~1, kGemmThreads, smem, st>>>(mw, maps, a);
-    return cudaGetLastError();
+    return launch_dependent(gemm_mx_pair_kernel<MODE>, unsigned(ctas & ~1), kGemmThreads, size_t(smem), st, mw, maps, a);
 }
 
 // How many CTAs of the pair kernels can be resident at once (2 x the co-resident clusters, at most one per SM).
@@ -312,15 +324,31 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
     return 0;
 }
 
-// Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine.
+// Activations that are not quantised yet (requests of at most kSmallRows tokens quantise inside the fused prologue).
+struct RawInput {
+    const void* x;
+    int dtype, codec;          // 0 BF16 / 1 FP32; 0 wire / 1 quant_v1
+    uint32_t* fault_quant;
+};
+
+template <int CODEC, int IN>
+void launch_small_prologue(uint32_t grid, cudaStream_t st, const SmallIo& io, const int32_t* ids, const float* w, uint32_t rows,
+                           const uint8_t* resident, int max_n, int mt1, int mt2, const PlanOut& po) {
+    small_prologue_kernel<CODEC, IN><<<grid, 256, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
+}
+
+// Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine. `raw` (only with at most
+// kSmallRows rows) names activations still to be quantised into xq / xs; `status_cleared`: the caller has already
+// zeroed the status block on the stream.
 int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const uint8_t* xs, const int32_t* ids,
                  const float* w, uint32_t rows, uint16_t* bf16_out, float* partial_out, Status* status,
-                 cudaStream_t st, bool events, char* err, size_t errlen) {
+                 cudaStream_t st, bool events, char* err, size_t errlen, const RawInput* raw = nullptr,
+                 bool status_cleared = false) {
     cudaError_t e;
     const uint32_t routes = rows * kTopK;
     const LaunchClass lc = launch_class(rows);
     const int mt1 = L->i_local / kTileM, mt2 = kHidden / kPairM;
-    M26B_CK(cudaMemsetAsync(status, 0, sizeof(Status), st), "m26b status clear");
+    if (!status_cleared) M26B_CK(cudaMemsetAsync(status, 0, sizeof(Status), st), "m26b status clear");
     if (events) M26B_CK(cudaEventRecord(S->e0, st), "m26b event 0");
     PlanOut po{S->inverse.as<int32_t>(), S->original.as<int32_t>(), S->gweights.as<float>(), S->experts.as<ExpertPlan>(),
                S->tiles.as<TokenTile>(), S->items1.as<WorkItem>(), S->items2.as<WorkItem>(), &status->meta};
@@ -332,24 +360,44 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     const int m_step = pair ? 2 : 1;
     const bool kt = (S->debug & 2u) != 0;
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
-    if (routes <= 4096) {
-        plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, m_step, po);
+    if (rows <= kSmallRows) {
+        // one launch: plan + (quantise) + gate + permutation; timed as the permutation, the plan slot reads zero
+        if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
+        SmallIo io{};
+        io.x = raw ? raw->x : xq; io.xs_in = xs;
+        io.xq_out = raw ? const_cast<uint8_t*>(xq) : nullptr; io.xs_out = raw ? const_cast<uint8_t*>(xs) : nullptr;
+        io.x_perm = S->x_perm.as<uint8_t>(); io.sfb = S->sfb1.as<uint8_t>();
+        io.fault_input = &status->fault_input; io.fault_quant = raw ? raw->fault_quant : nullptr;
+        const uint32_t grid = routes < uint32_t(S->sms) ? routes : uint32_t(S->sms);
+        const int sel = raw ? raw->codec * 2 + raw->dtype : 4;
+        switch (sel) {
+            case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
+            case 1: launch_small_prologue<0, 1>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
+            case 2: launch_small_prologue<1, 0>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
+            case 3: launch_small_prologue<1, 1>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
+            default: launch_small_prologue<0, 2>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
+        }
+        M26B_CK(cudaGetLastError(), "m26b prologue launch");
     } else {
-        // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
-        const uint32_t slabs = (routes + 1023u) / 1024u;
-        const uint32_t n_cta = slabs < 128u ? slabs : 128u;
-        const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
-        uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
-        plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, L->resident, cta_routes, cta_cnt, &status->meta);
-        plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step, po);
-        plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po);
+        if (routes <= 4096) {
+            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, m_step, po);
+        } else {
+            // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
+            const uint32_t slabs = (routes + 1023u) / 1024u;
+            const uint32_t n_cta = slabs < 128u ? slabs : 128u;
+            const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
+            uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
+            plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, L->resident, cta_routes, cta_cnt, &status->meta);
+            plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step, po);
+            plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po);
+        }
+        M26B_CK(cudaGetLastError(), "m26b plan launch");
+        if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
+        permute_kernel<<<routes < 65535u * 8u ? routes : 65535u * 8u, 256, 0, st>>>(
+            xq, xs, ids, S->original.as<int32_t>(), S->experts.as<ExpertPlan>(), &status->meta, routes,
+            S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input);
+        M26B_CK(cudaGetLastError(), "m26b permute launch");
     }
-    M26B_CK(cudaGetLastError(), "m26b plan launch");
-    if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
-    permute_kernel<<<routes < 65535u * 8u ? routes : 65535u * 8u, 256, 0, st>>>(
-        xq, xs, ids, S->original.as<int32_t>(), S->experts.as<ExpertPlan>(), &status->meta, routes,
-        S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input);
-    M26B_CK(cudaGetLastError(), "m26b permute launch");
     if (kt) M26B_CK(cudaEventRecord(S->kev[3], st), "m26b event");
     GemmArgs a{};
     a.tiles = S->tiles.as<TokenTile>();
@@ -387,8 +435,8 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (kt) M26B_CK(cudaEventRecord(S->kev[5], st), "m26b event");
     const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
     const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
-    route_reduce_kernel<<<blocks, 256, 0, st>>>(S->y.as<float>(), w, rows, partial_out, bf16_out, &status->fault_reduce);
-    M26B_CK(cudaGetLastError(), "m26b reduce launch");
+    M26B_CK(launch_dependent(route_reduce_kernel, blocks, 256u, size_t(0), st, static_cast<const float*>(S->y.as<float>()), w,
+                             rows, partial_out, bf16_out, &status->fault_reduce), "m26b reduce launch");
     if (events) M26B_CK(cudaEventRecord(S->e1, st), "m26b event 1");
     if (kt) { M26B_CK(cudaEventRecord(S->kev[6], st), "m26b event"); S->kev_valid = true; }
     S->last_rows = rows; S->last_i_local = L->i_local; S->last_ids = ids; S->last_xq = xq; S->last_xs = xs;
@@ -647,19 +695,23 @@ int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtyp
     Status* status = S->status.as<Status>();
     const uint8_t* xq = static_cast<const uint8_t*>(x);
     const uint8_t* xs = x_scales;
+    RawInput raw{x, x_dtype, codec, &status[1].fault_input};
+    const bool fused = rows <= kSmallRows;
     if (x_dtype != 2) {
-        // the quantiser's fault word is cleared with the status block, so clear first
+        // the quantiser's fault word (second status block) is cleared together with the pass's own block
         cudaError_t e;
-        M26B_CK(cudaMemsetAsync(&status[1], 0, sizeof(Status), st), "m26b status clear");
+        M26B_CK(cudaMemsetAsync(status, 0, 2 * sizeof(Status), st), "m26b status clear");
         if (S->debug & 2u) M26B_CK(cudaEventRecord(S->kev[0], st), "m26b event");
-        rc = m26b_quantize_dev(x, x_dtype, uint64_t(rows) * kHidden, codec, S->xq.as<uint8_t>(), S->xs.as<uint8_t>(),
-                               &status[1].fault_input, st, err, errlen);
-        if (rc) return rc;
+        if (!fused) {
+            rc = m26b_quantize_dev(x, x_dtype, uint64_t(rows) * kHidden, codec, S->xq.as<uint8_t>(), S->xs.as<uint8_t>(),
+                                   &status[1].fault_input, st, err, errlen);
+            if (rc) return rc;
+        }
         xq = S->xq.as<uint8_t>(); xs = S->xs.as<uint8_t>();
     }
     S->kev_quant = x_dtype != 2;
     rc = enqueue_pass(L, S, xq, xs, ids, weights, rows, bf16_out, partial_out ? partial_out : nullptr, status, st, false,
-                      err, errlen);
+                      err, errlen, (x_dtype != 2 && fused) ? &raw : nullptr, x_dtype != 2);
     if (rc) return rc;
     S->pending = true;
     S->n_status = x_dtype != 2 ? 2 : 1;

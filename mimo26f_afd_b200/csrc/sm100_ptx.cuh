@@ -206,6 +206,14 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
     return r;
 }
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may start
+// while its predecessor in the stream still runs; grid_dep_wait() returns once the predecessor has completed and its
+// writes are visible, and everything that reads the predecessor's output must come after it. grid_dep_launch()
+// in the predecessor lets the successor's CTAs be placed as soon as there is room. Both do nothing in a kernel
+// launched the ordinary way.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     // relaxed: a release at cluster scope would first wait for this thread's earlier global stores (thousands of
     // cycles in the epilogue). Callers order what the barrier protects themselves (tcgen05.wait::ld has already

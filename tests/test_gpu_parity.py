@@ -265,6 +265,33 @@ def test_ffn_ragged_token_counts(layer, scratch, dev, oracle_mod, tokens):
     check_ffn(layer, scratch, dev, oracle_mod, tokens, 0.7, codec=0, seed=SEED + tokens)
 
 
+@pytest.mark.parametrize("tokens", [7, 32])
+def test_small_request_prologue_input_forms_agree(layer, scratch, dev, oracle_mod, tokens):
+    """Requests of at most 32 tokens quantise, plan and permute in one launch. BF16 and FP32 activations (both codecs)
+    and caller-quantised E4M3 rows must give the same bytes at every stage, and the quant_v1 faults must surface."""
+    from mimo26f_afd_b200 import synth
+    import mimo26f_afd_b200 as M
+
+    x_bits = synth.activations_bf16(SEED + 7, tokens)
+    x = synth.bf16_to_f32_np(x_bits)
+    ids, w = synth.routing(SEED + 7, tokens, 0.6)
+    for codec in (0, 1):
+        bf_a, part_a = run_dev(layer, scratch, dev, x_bits, ids, w, codec=codec, x_dtype=0)
+        xq = scratch.peek("x_payload", np.uint8, (tokens, H))
+        xs = scratch.peek("x_scales", np.uint8, (tokens, H // 32))
+        oq, os_ = oracle_mod.quant_wire(x) if codec == 0 else oracle_mod.quant_v1(x)[:2]
+        assert np.array_equal(xq, oq) and np.array_equal(xs, os_)
+        bf_b, part_b = run_dev(layer, scratch, dev, x, ids, w, codec=codec, x_dtype=1)
+        assert np.array_equal(bf_a, bf_b) and np.array_equal(part_a.view(np.uint32), part_b.view(np.uint32))
+        bf_c, part_c = run_dev(layer, scratch, dev, xq, ids, w, x_dtype=2, x_scales=xs)
+        assert np.array_equal(bf_a, bf_c) and np.array_equal(part_a.view(np.uint32), part_c.view(np.uint32))
+    bad = x.copy(); bad[tokens - 1, 77] = np.inf
+    with pytest.raises(M.ExpertError) as e:
+        run_dev(layer, scratch, dev, bad, ids, w, codec=1, x_dtype=1)
+    assert e.value.code == 4
+    run_dev(layer, scratch, dev, x_bits, ids, w)              # usable afterwards
+
+
 def test_tp4_from_canonical_image_matches_reference_slices(weights, dev, oracle_mod):
     """m26b_layer_new on the reference's canonical-v2 TP4 rank images: each rank's partial equals the oracle's
     rank slice, and the rank-ordered sum of the four BF16 planes equals the oracle's wire result bit for bit
