@@ -154,7 +154,15 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
     total = torch.empty((tokens, H), dtype=torch.float32, device=dev) if world > 1 else None
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # > 126 MB L2
 
+    # N > 1: the ranks' BF16 planes are summed by the NVLink peer-memory exchange kernel (--exchange peer, default) or by
+    # an NCCL all-gather followed by the rank-sum kernel (--exchange nccl)
+    ex = tp.make_exchange(tokens) if world > 1 and args.exchange == "peer" else None
+
     def step():
+        if ex is not None:
+            expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, ex.plane(), stream=stream.cuda_stream)
+            ex.sum(tokens * H, total, stream=stream.cuda_stream)
+            return
         expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, out, stream=stream.cuda_stream)
         if world > 1:
             tp.tp_combine(out, total, stream=stream.cuda_stream)
@@ -213,15 +221,31 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
     from mimo26f_afd_b200 import _native
     err = C.create_string_buffer(256)
 
+    if world > 1:
+        # tensor-parallel ranks: quantised rows, ids and weights go up from pinned memory, the device entry point runs
+        # the rank's slice, the planes are summed across ranks, and the FP32 result comes back to pinned memory
+        dq, ds = torch.empty_like(hq, device=dev), torch.empty_like(hs, device=dev)
+        di, dw = torch.empty_like(hi, device=dev), torch.empty_like(hw, device=dev)
+        htotal = torch.empty((tokens, H), dtype=torch.float32).pin_memory()
+
     def e2e_step():
-        rc = _native.lib().m26b_ffn(layer._h, scratch._h, hq.data_ptr(), H, hs.data_ptr(), H // 32, hi.data_ptr(), hw.data_ptr(),
-                                    tokens, hout.data_ptr(), None, err, 256)
-        if rc:
-            raise M.ExpertError(rc, err.value.decode())
-        if world > 1:
-            out.copy_(hout.to(dev, non_blocking=True))
-            tp.tp_combine(out, total)
-            total[:1].cpu()
+        if world == 1:
+            rc = _native.lib().m26b_ffn(layer._h, scratch._h, hq.data_ptr(), H, hs.data_ptr(), H // 32, hi.data_ptr(),
+                                        hw.data_ptr(), tokens, hout.data_ptr(), None, err, 256)
+            if rc:
+                raise M.ExpertError(rc, err.value.decode())
+            return
+        with torch.cuda.stream(stream):
+            dq.copy_(hq, non_blocking=True); ds.copy_(hs, non_blocking=True)
+            di.copy_(hi, non_blocking=True); dw.copy_(hw, non_blocking=True)
+            dst = ex.plane() if ex is not None else out
+            expert.ffn_dev(layer, scratch, dq, di, dw, tokens, dst, x_dtype=expert.X_E4M3, x_scales=ds, stream=stream.cuda_stream)
+            if ex is not None:
+                ex.sum(tokens * H, total, stream=stream.cuda_stream)
+            else:
+                tp.tp_combine(out, total, stream=stream.cuda_stream)
+            htotal.copy_(total, non_blocking=True)
+        scratch.status(stream.cuda_stream)
 
     for _ in range(min(args.warmup, 3)):
         e2e_step()
@@ -236,7 +260,11 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = tokens * args.steps / float(t.item())
     h2d = tokens * (H + H // 32 + TOPK * 8)
-    d2h = tokens * H * 2 + 64
+    d2h = (tokens * H * 2 if world == 1 else tokens * H * 4) + 64
+    if ex is not None:
+        ex.status(stream.cuda_stream)
+        sync_all()
+        ex.close()
 
     # roofline of the dominant kernel (FC1): algorithmic work of that launch / its mean event-timed duration
     fc1_ms = float(np.mean([k["fc1"] for k in kern]))
@@ -300,6 +328,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-prefill", action="store_true", help="skip the 8192-token prefill sub-result")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the ranks' planes are summed (NVLink peer-memory kernel, or NCCL all-gather + sum kernel)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -347,7 +377,8 @@ def main():
                     data="synthetic",
                     config=dict(workload=args.workload, description=WORKLOADS[args.workload]["desc"], tokens=main_r["tokens"],
                                 top_k=TOPK, experts=E, hidden=H, intermediate=I, active_experts=main_r["active_experts"],
-                                parallelism=f"tp{world}" if world > 1 else "single", l2="flushed between timed iterations",
+                                parallelism=f"tp{world}" if world > 1 else "single",
+                                exchange=(args.exchange if world > 1 else None), l2="flushed between timed iterations",
                                 input_codec="wire (FP8 E4M3 + UE8M0 K32)"),
                     e2e=main_r["e2e"], gpu_launches=main_r["gpu_launches"], clocks=main_r["clocks"], roofline=main_r["roofline"],
                     whole_step=main_r["whole_step"], kernels_ms=main_r["kernels_ms"],

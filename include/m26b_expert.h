@@ -141,6 +141,34 @@ int m26b_route_reduce_dev(const float* y, const float* weights, uint32_t rows, f
 int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
                       size_t errlen);
 
+/* Plane exchange between the GPUs of one NVLink box, one process per GPU: replaces the return path + coordinator
+ * sum of the reference (crates/mimo26-wire/src/l4.rs:169-244 collects the four ranks' BF16 planes over RDMA,
+ * crates/mimo26-coordinator/kernels/glue.cu:202-213 adds them in rank order) when the ranks are GPUs that can map
+ * each other's memory. Each rank owns a window with two plane slots; the combine writes the rank's BF16 plane into
+ * the slot m26b_exchange_plane() names, and m26b_exchange_sum_dev() enqueues ONE kernel that publishes the plane,
+ * waits (bounded) for every peer's, reads the peers' planes over NVLink and writes the rank-ordered FP32 sum.
+ *   new:      allocate the window (plane_bytes a multiple of 256); handle_out receives 64 bytes for the peers
+ *             (an IPC handle of the window), or pass NULL when every rank lives in this process.
+ *   connect:  `handles` = world x 64 bytes in rank order, gathered by the caller (e.g. an all-gather on the host).
+ *   connect_local: the same for windows of one process (`all` = world handles in rank order).
+ *   plane:    device address the NEXT step's BF16 plane must be written to (alternates between the two slots).
+ *   sum_dev:  n_elems a multiple of 8; out_f32 [n_elems] on this rank. Every rank must call it once per step.
+ *   status:   0, or 5 when a wait ran out (the message names the ranks); the window stays usable.
+ *   set_wait_ms: the bound of the wait (default 2000 ms).
+ *   publish_as: marks the next step as published by `peer_rank` from the host; for single-process tests and for a
+ *             coordinator that stands in for a rank it knows to be idle. */
+typedef struct m26b_exchange m26b_exchange;
+int m26b_exchange_new(uint64_t plane_bytes, uint32_t rank, uint32_t world, m26b_exchange** out, uint8_t* handle_out,
+                      char* err, size_t errlen);
+int m26b_exchange_connect(m26b_exchange* x, const uint8_t* handles, char* err, size_t errlen);
+int m26b_exchange_connect_local(m26b_exchange* x, m26b_exchange* const* all, char* err, size_t errlen);
+void* m26b_exchange_plane(m26b_exchange* x);
+int m26b_exchange_set_wait_ms(m26b_exchange* x, uint32_t ms);
+int m26b_exchange_publish_as(m26b_exchange* x, uint32_t peer_rank, void* stream, char* err, size_t errlen);
+int m26b_exchange_sum_dev(m26b_exchange* x, uint64_t n_elems, float* out_f32, void* stream, char* err, size_t errlen);
+int m26b_exchange_status(m26b_exchange* x, void* stream, char* err, size_t errlen);
+void m26b_exchange_free(m26b_exchange* x);
+
 /* Route plan without any allocation. No counterpart in the reference.
  * For callers that must not allocate device memory while they run: a serving loop that gave every free byte of the
  * GPU to resident expert weights at start-up, a request handler that has to stay clear of cudaMalloc's device-wide

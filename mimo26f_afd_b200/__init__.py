@@ -7,6 +7,7 @@ Rust wrapper (``crates/mimo26-spark/src/b1.rs``): ``Layer``, ``Scratch``, ``ffn`
 built library raises.
 """
 from .expert import (  # noqa: F401
+    Exchange,
     ExpertError,
     FfnStats,
     Layer,

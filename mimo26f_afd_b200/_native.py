@@ -13,6 +13,9 @@ SYMBOLS = (
     "m26b_layer_i_local", "m26b_layer_free", "m26b_scratch_new", "m26b_scratch_free", "m26b_ffn", "m26b_ffn_dev",
     "m26b_scratch_status", "m26b_scratch_set_debug", "m26b_scratch_timings", "m26b_scratch_peek", "m26b_quantize_dev",
     "m26b_route_reduce_dev", "m26b_rank_sum_dev", "m26b_plan_static", "m26b_version",
+    "m26b_exchange_new", "m26b_exchange_connect", "m26b_exchange_connect_local", "m26b_exchange_plane",
+    "m26b_exchange_set_wait_ms", "m26b_exchange_publish_as", "m26b_exchange_sum_dev", "m26b_exchange_status",
+    "m26b_exchange_free",
 )
 
 _lib = None
@@ -52,8 +55,19 @@ def lib() -> C.CDLL:
     L.m26b_rank_sum_dev.argtypes = [C.POINTER(vp), C.c_int, C.c_uint64, f32p, vp, *err]
     L.m26b_plan_static.argtypes = [i32p, f32p, C.c_uint32, i32p, i32p, f32p, u32p, vp, *err]
     L.m26b_version.restype = C.c_char_p
+    L.m26b_exchange_new.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.POINTER(vp), u8p, *err]
+    L.m26b_exchange_connect.argtypes = [vp, u8p, *err]
+    L.m26b_exchange_connect_local.argtypes = [vp, C.POINTER(vp), *err]
+    L.m26b_exchange_plane.argtypes = [vp]
+    L.m26b_exchange_plane.restype = C.c_void_p
+    L.m26b_exchange_set_wait_ms.argtypes = [vp, C.c_uint32]
+    L.m26b_exchange_publish_as.argtypes = [vp, C.c_uint32, vp, *err]
+    L.m26b_exchange_sum_dev.argtypes = [vp, C.c_uint64, f32p, vp, *err]
+    L.m26b_exchange_status.argtypes = [vp, vp, *err]
+    L.m26b_exchange_free.argtypes = [vp]
+    L.m26b_exchange_free.restype = None
     for name in SYMBOLS:
-        if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version"):
+        if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version", "m26b_exchange_plane", "m26b_exchange_free"):
             getattr(L, name).restype = C.c_int
     _lib = L
     return L

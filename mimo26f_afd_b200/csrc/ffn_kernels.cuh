@@ -485,6 +485,82 @@ __global__ void __launch_bounds__(256) rank_sum_kernel(RankPlanes planes, int n_
     }
 }
 
+// ---------------------------------------------------------------- plane exchange between GPUs
+// The same rank-ordered sum, with the planes left where each rank's combine wrote them: every GPU reads its
+// peers' planes through NVLink peer mappings while it adds, instead of gathering copies first.
+//
+// Each rank owns a window: flags[8] (flags[r] = the last step rank r has published), an error word, and two plane
+// slots used alternately. One launch per rank and step:
+//   1. CTA 0 publishes the step to every peer (a system-scope release store into the peer's flags[rank]; the
+//      plane itself was finished by the previous kernel in the stream);
+//   2. every CTA waits until every peer has published this step (system-scope acquire loads of its own flags);
+//      the wait is bounded: past the limit the kernel records the peer in the error word and returns;
+//   3. grid-stride sum over the planes in rank order; peer planes are read around L1, which is not coherent
+//      with another GPU's writes.
+// A slot is rewritten two steps later, after this rank has seen every peer publish the step in between, which a
+// peer only does once its own reads of the earlier step have finished: two slots are enough.
+struct ExchangeWindow {
+    uint32_t flags[8];
+    uint32_t error;            // bit r: gave up waiting for rank r
+    uint32_t pad[55];          // planes start 256 bytes in
+};
+static_assert(sizeof(ExchangeWindow) == 256, "exchange window header is 256 bytes");
+struct ExchangePeers {
+    uint8_t* window[8];        // window[rank] is the local one
+};
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__global__ void __launch_bounds__(256) exchange_sum_kernel(ExchangePeers peers, int rank, int world, uint32_t step,
+                                                           uint64_t plane_offset, uint64_t n, long long wait_cycles,
+                                                           float* __restrict__ out) {
+    __shared__ uint32_t late;
+    ExchangeWindow* mine = reinterpret_cast<ExchangeWindow*>(peers.window[rank]);
+    grid_dep_wait();             // the local plane comes from the combine kernel before this one
+    if (blockIdx.x == 0 && threadIdx.x < uint32_t(world) && int(threadIdx.x) != rank) {
+        __threadfence_system();
+        st_release_sys(&reinterpret_cast<ExchangeWindow*>(peers.window[threadIdx.x])->flags[rank], step);
+    }
+    if (threadIdx.x == 0) late = 0;
+    __syncthreads();
+    if (threadIdx.x < uint32_t(world) && int(threadIdx.x) != rank) {
+        const long long t0 = clock64();
+        while (int32_t(ld_acquire_sys(&mine->flags[threadIdx.x]) - step) < 0) {
+            if (clock64() - t0 > wait_cycles) { atomicOr(&late, 1u << threadIdx.x); break; }
+        }
+    }
+    __syncthreads();
+    if (late) {
+        if (threadIdx.x == 0) atomicOr(&mine->error, late);
+        return;
+    }
+    const uint64_t n8 = n / 8;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += uint64_t(gridDim.x) * blockDim.x) {
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < world) v[r] = __ldcv(reinterpret_cast<const uint4*>(peers.window[r] + plane_offset) + i);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= world) break;
+            const uint32_t wv[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                s[2 * k] = __fadd_rn(s[2 * k], __uint_as_float(wv[k] << 16));
+                s[2 * k + 1] = __fadd_rn(s[2 * k + 1], __uint_as_float(wv[k] & 0xffff0000u));
+            }
+        }
+        reinterpret_cast<float4*>(out)[2 * i] = make_float4(s[0], s[1], s[2], s[3]);
+        reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(s[4], s[5], s[6], s[7]);
+    }
+}
+
 // ---------------------------------------------------------------- weight repack
 // Source of one projection: payload u8 [E][rows][in/2] and scales u8
 // [E][rows][in/32] with explicit strides, so the same kernels read the

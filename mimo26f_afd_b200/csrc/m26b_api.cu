@@ -168,6 +168,16 @@ struct m26b_layer {
     CUtensorMap map_w13, map_w2, map_s13, map_s2;
 };
 
+struct m26b_exchange {
+    void* window = nullptr;
+    ExchangePeers peers{};
+    bool opened[8] = {false, false, false, false, false, false, false, false};
+    int rank = 0, world = 1, device = 0, khz = 0;
+    uint64_t plane_bytes = 0;
+    uint32_t step = 0;                  // steps summed so far; the next step writes slot (step + 1) & 1
+    long long wait_cycles = 0;
+};
+
 struct m26b_scratch {
     cudaStream_t st = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr, ea = nullptr, ec = nullptr;
@@ -755,6 +765,133 @@ int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, fl
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, errlen, "m26b rank sum launch", e); return 2; }
     return 0;
+}
+
+// ---- plane exchange between the GPUs of one box ----------------------------------------------
+int m26b_exchange_new(uint64_t plane_bytes, uint32_t rank, uint32_t world, m26b_exchange** out, uint8_t* handle_out,
+                      char* err, size_t errlen) {
+    if (!out || !plane_bytes || plane_bytes % 256 || world < 1 || world > 8 || rank >= world) {
+        set_msg(err, errlen, "m26b exchange: bad plane size / rank / world (plane bytes must be a multiple of 256)");
+        return 1;
+    }
+    cudaError_t e;
+    m26b_exchange* X = new m26b_exchange();
+    X->rank = int(rank); X->world = int(world); X->plane_bytes = plane_bytes;
+    if ((e = cudaGetDevice(&X->device)) != cudaSuccess ||
+        (e = cudaMalloc(&X->window, sizeof(ExchangeWindow) + 2 * plane_bytes)) != cudaSuccess ||
+        (e = cudaMemset(X->window, 0, sizeof(ExchangeWindow))) != cudaSuccess) {
+        set_err(err, errlen, "m26b exchange window", e);
+        m26b_exchange_free(X);
+        return 2;
+    }
+    int khz = 0;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, X->device);
+    X->khz = khz > 0 ? khz : 1965000;
+    X->wait_cycles = 2000ll * X->khz;                      // two seconds at the nominal clock
+    X->peers.window[rank] = static_cast<uint8_t*>(X->window);
+    if (handle_out) {
+        cudaIpcMemHandle_t h;
+        if ((e = cudaIpcGetMemHandle(&h, X->window)) != cudaSuccess) {
+            set_err(err, errlen, "m26b exchange export", e);
+            m26b_exchange_free(X);
+            return 2;
+        }
+        static_assert(sizeof(h) == 64, "IPC handle is 64 bytes");
+        std::memcpy(handle_out, &h, 64);
+    }
+    *out = X;
+    return 0;
+}
+
+int m26b_exchange_connect(m26b_exchange* X, const uint8_t* handles, char* err, size_t errlen) {
+    if (!X || !handles) { set_msg(err, errlen, "m26b exchange connect: bad arguments"); return 1; }
+    if (!device_ok(X->device, err, errlen)) return 1;
+    for (int r = 0; r < X->world; ++r) {
+        if (r == X->rank || X->peers.window[r]) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handles + size_t(r) * 64, 64);
+        void* p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) { set_err(err, errlen, "m26b exchange: opening a peer window", e); return 2; }
+        X->peers.window[r] = static_cast<uint8_t*>(p);
+        X->opened[r] = true;
+    }
+    return 0;
+}
+
+int m26b_exchange_connect_local(m26b_exchange* X, m26b_exchange* const* all, char* err, size_t errlen) {
+    if (!X || !all) { set_msg(err, errlen, "m26b exchange connect: bad arguments"); return 1; }
+    for (int r = 0; r < X->world; ++r) {
+        if (r == X->rank) continue;
+        if (!all[r] || all[r]->world != X->world || all[r]->rank != r || all[r]->plane_bytes != X->plane_bytes) {
+            set_msg(err, errlen, "m26b exchange connect: windows do not belong together");
+            return 1;
+        }
+        X->peers.window[r] = static_cast<uint8_t*>(all[r]->window);
+    }
+    return 0;
+}
+
+void* m26b_exchange_plane(m26b_exchange* X) {
+    if (!X) return nullptr;
+    return static_cast<uint8_t*>(X->window) + sizeof(ExchangeWindow) + size_t((X->step + 1) & 1u) * X->plane_bytes;
+}
+
+int m26b_exchange_set_wait_ms(m26b_exchange* X, uint32_t ms) {
+    if (!X || !ms) return 1;
+    X->wait_cycles = (long long)ms * X->khz;
+    return 0;
+}
+
+int m26b_exchange_publish_as(m26b_exchange* X, uint32_t peer_rank, void* stream, char* err, size_t errlen) {
+    if (!X || int(peer_rank) >= X->world || int(peer_rank) == X->rank) { set_msg(err, errlen, "m26b exchange: bad peer"); return 1; }
+    const uint32_t next = X->step + 1;
+    const cudaError_t e = cudaMemcpyAsync(&static_cast<ExchangeWindow*>(X->window)->flags[peer_rank], &next, 4,
+                                          cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b exchange publish", e); return 2; }
+    return 0;
+}
+
+int m26b_exchange_sum_dev(m26b_exchange* X, uint64_t n_elems, float* out_f32, void* stream, char* err, size_t errlen) {
+    if (!X || !out_f32 || !n_elems || n_elems % 8 || n_elems * 2 > X->plane_bytes) {
+        set_msg(err, errlen, "m26b exchange sum: bad extent (a multiple of 8 elements that fits the plane)");
+        return 1;
+    }
+    if (!device_ok(X->device, err, errlen)) return 1;
+    for (int r = 0; r < X->world; ++r)
+        if (!X->peers.window[r]) { set_msg(err, errlen, "m26b exchange sum: not connected to every peer"); return 1; }
+    X->step += 1;
+    const uint64_t off = sizeof(ExchangeWindow) + size_t(X->step & 1u) * X->plane_bytes;
+    const uint64_t t = (n_elems / 8 + 255) / 256;
+    const unsigned blocks = unsigned(t < 148 * 8 ? (t ? t : 1) : 148 * 8);
+    const cudaError_t e = launch_dependent(exchange_sum_kernel, blocks, 256u, size_t(0), static_cast<cudaStream_t>(stream), X->peers,
+                                           X->rank, X->world, X->step, off, n_elems, X->wait_cycles, out_f32);
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b exchange sum launch", e); return 2; }
+    return 0;
+}
+
+int m26b_exchange_status(m26b_exchange* X, void* stream, char* err, size_t errlen) {
+    if (!X) { set_msg(err, errlen, "m26b exchange status: null handle"); return 1; }
+    cudaError_t e;
+    uint32_t word = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    M26B_CK(cudaMemcpyAsync(&word, &static_cast<ExchangeWindow*>(X->window)->error, 4, cudaMemcpyDeviceToHost, st), "m26b exchange status");
+    M26B_CK(cudaStreamSynchronize(st), "m26b exchange status sync");
+    if (word) {
+        M26B_CK(cudaMemsetAsync(&static_cast<ExchangeWindow*>(X->window)->error, 0, 4, st), "m26b exchange status clear");
+        M26B_CK(cudaStreamSynchronize(st), "m26b exchange status sync");
+        if (err && errlen) std::snprintf(err, errlen, "m26b exchange: rank %d gave up waiting for peers (mask 0x%x) at step %u; that step's sum was not written", X->rank, word, X->step);
+        return 5;
+    }
+    return 0;
+}
+
+void m26b_exchange_free(m26b_exchange* X) {
+    if (!X) return;
+    for (int r = 0; r < 8; ++r)
+        if (X->opened[r] && X->peers.window[r]) cudaIpcCloseMemHandle(X->peers.window[r]);
+    if (X->window) cudaFree(X->window);
+    delete X;
 }
 
 int m26b_scratch_timings(m26b_scratch* S, float* ms6, char* err, size_t errlen) {

@@ -23,7 +23,8 @@ TOPK = 8
 
 
 class ExpertError(RuntimeError):
-    """A nonzero return of the C ABI: ``code`` 1 argument, 2 CUDA, 3 plan rejected, 4 numerical fault."""
+    """A nonzero return of the C ABI: ``code`` 1 argument, 2 CUDA, 3 plan rejected, 4 numerical fault,
+    5 a peer's plane did not arrive within the exchange's wait bound."""
 
     def __init__(self, code: int, message: str):
         super().__init__(f"[{code}] {message}")
@@ -221,6 +222,69 @@ def rank_sum_dev(planes, n: int, out, stream=None) -> None:
     arr = (C.c_void_p * len(planes))(*[_ptr(p) for p in planes])
     err = C.create_string_buffer(256)
     _check(_native.lib().m26b_rank_sum_dev(arr, len(planes), n, _ptr(out), _ptr(stream), err, 256), err)
+
+
+class Exchange:
+    """This rank's window of the plane exchange between the GPUs of one box (one process per GPU).
+
+    ``plane()`` is the device address the next step's BF16 plane goes to (pass it as ``bf16_out`` of ``ffn_dev``);
+    ``sum(n, out_f32)`` enqueues the one kernel that publishes the plane, waits for the peers' and adds all planes in
+    rank order, reading the peers' over NVLink. Stands where the reference has the RDMA return path and the
+    coordinator's sum (crates/mimo26-wire/src/l4.rs:169-244, crates/mimo26-coordinator/kernels/glue.cu:202-213)."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, plane_bytes: int, rank: int, world: int, export: bool = True):
+        out, err = C.c_void_p(), C.create_string_buffer(256)
+        self.handle = (C.c_uint8 * self.HANDLE_BYTES)() if export else None
+        _check(_native.lib().m26b_exchange_new(plane_bytes, rank, world, C.byref(out),
+                                               C.addressof(self.handle) if export else None, err, 256), err)
+        self._h, self.rank, self.world, self.plane_bytes = out, rank, world, plane_bytes
+
+    def handle_bytes(self) -> bytes:
+        return bytes(self.handle)
+
+    def connect(self, handles: bytes) -> None:
+        """``handles``: every rank's ``handle_bytes()`` concatenated in rank order."""
+        if len(handles) != self.world * self.HANDLE_BYTES:
+            raise ExpertError(1, "m26b exchange connect: need one 64-byte handle per rank")
+        buf = (C.c_uint8 * len(handles)).from_buffer_copy(handles)
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_exchange_connect(self._h, C.addressof(buf), err, 256), err)
+
+    def connect_local(self, windows) -> None:
+        arr = (C.c_void_p * self.world)(*[w._h.value for w in windows])
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_exchange_connect_local(self._h, arr, err, 256), err)
+
+    def plane(self) -> int:
+        return int(_native.lib().m26b_exchange_plane(self._h))
+
+    def set_wait_ms(self, ms: int) -> None:
+        _native.lib().m26b_exchange_set_wait_ms(self._h, ms)
+
+    def publish_as(self, peer_rank: int, stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_exchange_publish_as(self._h, peer_rank, _ptr(stream), err, 256), err)
+
+    def sum(self, n_elems: int, out_f32, stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_exchange_sum_dev(self._h, n_elems, _ptr(out_f32), _ptr(stream), err, 256), err)
+
+    def status(self, stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_exchange_status(self._h, _ptr(stream), err, 256), err)
+
+    def close(self) -> None:
+        if self._h:
+            _native.lib().m26b_exchange_free(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 PLAN_STATIC_MAX_ROWS = 4096

@@ -44,6 +44,23 @@ def all_gather_planes(plane, group=None):
     return [o.view(plane.dtype).view(plane.shape) for o in out]
 
 
+def make_exchange(tokens: int, group=None):
+    """This rank's exchange window for planes of up to ``tokens`` rows, connected to every peer of ``group``:
+    the 64-byte window handles travel through one host-side all-gather, after which the ranks read each other's
+    planes directly over NVLink (``Exchange.sum``) with no library collective on the data path."""
+    import torch.distributed as dist
+
+    from . import expert
+
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ex = expert.Exchange(((tokens * H * 2 + 255) // 256) * 256, rank, world)
+    handles = [None] * world
+    dist.all_gather_object(handles, ex.handle_bytes(), group=group)
+    ex.connect(b"".join(handles))
+    dist.barrier(group)          # every window is mapped everywhere before the first publication
+    return ex
+
+
 def tp_combine(plane, out_f32, group=None, stream=None):
     """Rank-ordered FP32 sum of every rank's BF16 plane into ``out_f32`` (CUDA tensors)."""
     from . import expert

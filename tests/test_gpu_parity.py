@@ -188,6 +188,53 @@ def test_rank_sum_order(dev, oracle_mod):
     assert out.cpu().numpy()[0] == 2.0                        # the swapped order gives the other answer
 
 
+class _DevView:
+    """A device address as something torch can wrap (CUDA array interface)."""
+
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def test_plane_exchange_two_windows_one_process(dev, oracle_mod):
+    """The exchange kernel with both ranks' windows in this process: a rank's peer is published from the host, so no
+    kernel waits for another kernel. Checks the rank-ordered sum, the alternating slots and the bounded wait."""
+    import torch
+
+    import mimo26f_afd_b200 as M
+
+    n = 16 * H
+    rng = np.random.default_rng(11)
+    ex = [M.Exchange(n * 2, r, 2, export=False) for r in range(2)]
+    for e in ex:
+        e.connect_local(ex)
+    out = [torch.empty(n, dtype=torch.float32, device=dev) for _ in range(2)]
+    for step in range(3):
+        planes = (rng.standard_normal((2, n)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        planes[0, 0], planes[1, 0] = 0x4B80, 0x3F80           # 2^24 + 1: the order of the additions shows
+        for r in range(2):
+            torch.as_tensor(_DevView(ex[r].plane(), n, "<i2"), device=dev).copy_(to_dev(planes[r], dev))
+        torch.cuda.synchronize()
+        for r in range(2):
+            ex[r].publish_as(1 - r)
+            ex[r].sum(n, out[r])
+            ex[r].status()
+        want = oracle_mod.rank_sum(planes)
+        for r in range(2):
+            assert np.array_equal(out[r].cpu().numpy().view(np.uint32), want.view(np.uint32)), (step, r)
+    # a peer that never publishes: the wait runs out, the status says so, and the window works again afterwards
+    ex[0].set_wait_ms(20)
+    ex[0].sum(n, out[0])
+    with pytest.raises(M.ExpertError) as e:
+        ex[0].status()
+    assert e.value.code == 5 and "gave up waiting" in e.value.message
+    ex[1].publish_as(0); ex[1].sum(n, out[1]); ex[1].status()   # rank 1 catches up with the step rank 0 lost
+    ex[0].publish_as(1); ex[0].sum(n, out[0]); ex[0].status()
+    with pytest.raises(M.ExpertError):
+        ex[0].sum(n + 4, out[0])                                # not a multiple of 8 / larger than the plane
+    for e_ in ex:
+        e_.close()
+
+
 # ------------------------------------------------------------------------------------------ the whole path
 def check_ffn(layer, scratch, dev, oracle_mod, tokens, zipf, codec, tp_rank=0, tp_size=1, seed=SEED):
     from mimo26f_afd_b200 import synth

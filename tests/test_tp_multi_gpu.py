@@ -1,0 +1,23 @@
+"""Tensor-parallel ranks on real GPUs of one box: the NVLink peer-memory exchange against NCCL and the oracle.
+Needs at least two GPUs (skipped otherwise); the ranks are child processes, one per GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_exchange_matches_nccl_and_oracle(world):
+    import torch
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "tp_worker.py")]
+    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and f"TP_WORKER_OK {world}" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
