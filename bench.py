@@ -39,7 +39,12 @@ sys.path.insert(0, ROOT)
 H, I, E, TOPK = 4096, 2048, 256, 8
 EXPERT_BYTES = 13369344                     # 3 x 2048 x 4096 x 17/32 (payload + scales)
 FLOP_PER_TOKEN = 402653184                  # 3 GEMMs x 2 x 4096 x 2048 x top-8
-MXF8F6F4_PEAK_TFLOPS = 4450.0               # measured on this pool: profiles/mxf8f6f4_mma_rate.md
+MXF8F6F4_PEAK_TFLOPS = 4450.0               # measured on this pool: profiles/mxf8f6f4_mma_rate.md (burst, small codes)
+MXF8F6F4_RANDOM_BURST_TFLOPS = 3694.0       # same probe on random operands, first 7 ms launch
+MXF8F6F4_RANDOM_SUSTAINED_TFLOPS = 3193.0   # same, after three seconds (1.32 GHz under the 1000 W limit)
+# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch at N = 1, from the ncu captures summarised in
+# profiles/gemm_mx_decode16.md and profiles/gemm_mx_prefill8k.md (the seeded workloads are the same every run)
+FC1_TRAFFIC_BYTES = {"decode16": 915384064, "prefill8k": 3002103808}
 WORKLOADS = {
     "decode16": dict(tokens=16, zipf=0.0, desc="16-token decode batch, uniform routing (BASELINE configs[1])"),
     "prefill8k": dict(tokens=8192, zipf=0.0, desc="8192-token prefill segment, uniform routing (BASELINE configs[3])"),
@@ -274,13 +279,16 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
         fc1_bytes = active * (2 * il * (H // 2) + 2 * il * (H // 32)) + routes * (H + H // 32) + routes * (il + il // 32)
         roof = dict(bound="hbm", achieved=fc1_bytes / (fc1_ms * 1e-3) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s",
                     peak_source=f"{peaks['source']} copy bandwidth (MEASURED_PEAKS.json)", kernel="gemm_mx_kernel<FC1>",
-                    algorithmic_bytes=fc1_bytes, traffic=None)
+                    algorithmic_bytes=fc1_bytes, traffic=FC1_TRAFFIC_BYTES[name] if world == 1 else None)
     else:
         fc1_flops = 2.0 * 2 * H * il * routes
         roof = dict(bound="tensor", achieved=fc1_flops / (fc1_ms * 1e-3) / 1e12, peak=MXF8F6F4_PEAK_TFLOPS, unit="TFLOP/s",
                     peak_source="measured tcgen05 kind::mxf8f6f4 dense rate on this pool (profiles/mxf8f6f4_mma_rate.md); "
                                 f"MEASURED_PEAKS.json holds only bf16 = {peaks['bf16_tflops']} TF/s",
-                    kernel="gemm_mx_kernel<FC1>", algorithmic_flops=fc1_flops, traffic=None)
+                    kernel="gemm_mx_pair_kernel<FC1>", algorithmic_flops=fc1_flops,
+                    traffic=FC1_TRAFFIC_BYTES[name] if world == 1 else None)
+        roof["frac_of_random_operand_burst"] = roof["achieved"] / MXF8F6F4_RANDOM_BURST_TFLOPS
+        roof["frac_of_random_operand_sustained"] = roof["achieved"] / MXF8F6F4_RANDOM_SUSTAINED_TFLOPS
     roof["frac"] = roof["achieved"] / roof["peak"]
     roof["kernel_ms"] = fc1_ms
     whole = dict(hbm_gbs=(active * EXPERT_BYTES / world + tokens * H * 4 + routes * 8) / (total_ms / args.steps * 1e-3) / 1e9,

@@ -124,8 +124,11 @@ struct SmemRate {
     uint32_t abort_flag;
 };
 
+// `random_data`: operands are pseudo-random bytes (every E2M1 code, every finite E4M3 code) instead of a few small
+// codes. The tensor pipe's rate per clock does not depend on the data, its power draw does, and with it the clock
+// the GPU holds under its power limit.
 __global__ void __launch_bounds__(128) probe_rate(uint32_t n, uint32_t iters, uint32_t a_fmt, uint32_t two_a,
-                                                  long long* cycles, uint32_t* err) {
+                                                  long long* cycles, uint32_t* err, uint32_t random_data = 0) {
     extern __shared__ uint8_t raw[];
     SmemRate& s = *reinterpret_cast<SmemRate*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x / 32;
@@ -133,6 +136,16 @@ __global__ void __launch_bounds__(128) probe_rate(uint32_t n, uint32_t iters, ui
     for (int i = threadIdx.x; i < int(sizeof(s.a)); i += blockDim.x) (&s.a[0][0])[i] = uint8_t((i * 37 + 11) & 0x33);
     for (int i = threadIdx.x; i < int(sizeof(s.b)); i += blockDim.x) (&s.b[0][0])[i] = uint8_t((i * 29 + 5) & 0x33);
     for (int i = threadIdx.x; i < 512; i += blockDim.x) s.sf[i] = 120;
+    if (random_data) {
+        auto mix = [](uint32_t v) { v ^= v >> 16; v *= 0x7feb352du; v ^= v >> 15; v *= 0x846ca68bu; v ^= v >> 16; return v; };
+        for (int i = threadIdx.x; i < int(sizeof(s.a)); i += blockDim.x) (&s.a[0][0])[i] = uint8_t(mix(i * 2u + blockIdx.x * 7919u));
+        for (int i = threadIdx.x; i < int(sizeof(s.b)); i += blockDim.x) {
+            uint8_t v = uint8_t(mix(i * 2u + 1u + blockIdx.x * 104729u));
+            if ((v & 0x7f) == 0x7f) v ^= 1;                  // no E4M3 NaN codes
+            (&s.b[0][0])[i] = v;
+        }
+        for (int i = threadIdx.x; i < 512; i += blockDim.x) s.sf[i] = uint8_t(118 + (mix(i) & 7));
+    }
     if (threadIdx.x == 0) { mbar_init(&s.done, 1); s.abort_flag = 0; mbar_init_fence(); }
     fence_async_smem();
     if (warp == 0) { tmem_alloc(&s.tmem_base, 512); tmem_relinquish(); }
@@ -297,6 +310,26 @@ int main() {
         float ms; CK(cudaEventElapsedTime(&ms, e0, e1));
         const double flops = 2.0 * 128 * n * 32 * double(iters) * prop.multiProcessorCount;
         printf("rate chip N=%u: %.3f ms, %.1f TFLOP/s (mxf8f6f4 dense, E2M1 x E4M3)\n", n, ms, flops / ms / 1e9);
+    }
+    // sustained: back-to-back launches for about three seconds, the rate of the last second and the SM clock in it
+    // (cycles of one CTA / the launch's duration), for the small-code operands and for random operands
+    for (uint32_t random_data : {0u, 1u}) {
+        const uint32_t n = 128, iters = 200000;
+        const double flops = 2.0 * 128 * n * 32 * double(iters) * prop.multiProcessorCount;
+        double first_tf = 0, last_tf = 0, last_mhz = 0;
+        float total = 0;
+        for (int rep = 0; total < 3000.f && rep < 2000; ++rep) {
+            CK(cudaEventRecord(e0));
+            probe_rate<<<prop.multiProcessorCount, 128, smem2>>>(n, iters, kFmtE2M1, 0, d_cyc, d_err, random_data);
+            CK(cudaEventRecord(e1)); CK(cudaDeviceSynchronize());
+            float ms; CK(cudaEventElapsedTime(&ms, e0, e1));
+            long long cyc; CK(cudaMemcpy(&cyc, d_cyc, 8, cudaMemcpyDeviceToHost));
+            total += ms;
+            if (rep == 0) first_tf = flops / ms / 1e9;
+            last_tf = flops / ms / 1e9; last_mhz = double(cyc) / ms / 1e3;
+        }
+        printf("rate chip sustained N=128 %s operands: first launch %.1f TFLOP/s, after %.1f s %.1f TFLOP/s at %.0f MHz\n",
+               random_data ? "random" : "small-code", first_tf, total / 1e3, last_tf, last_mhz);
     }
     CK(cudaMemcpy(&herr, d_err, 4, cudaMemcpyDeviceToHost));
     printf("final err=0x%x\n", herr);
