@@ -169,6 +169,39 @@ int m26b_exchange_sum_dev(m26b_exchange* x, uint64_t n_elems, float* out_f32, vo
 int m26b_exchange_status(m26b_exchange* x, void* stream, char* err, size_t errlen);
 void m26b_exchange_free(m26b_exchange* x);
 
+/* Expert parallelism inside one NVLink box, one process per GPU (BASELINE configs[4]; the reference has no expert-
+ * parallel mode: it shards every expert's intermediate dimension over its four ranks, crates/mimo26-repack/src/geom.rs:29-35).
+ * Rank r holds experts [r 256/G, (r+1) 256/G) (m26b_layer_new_from_checkpoint_ep: the six checkpoint tensors stacked over
+ * THOSE experts) and owns a contiguous block of the step's tokens (the first `tokens % G` ranks one token more;
+ * m26b_ep_rows). A step on every rank, in this order, on one stream:
+ *   begin_dev:   quantise this rank's rows (or copy rows already quantised, x_dtype 2) and its routes into the rank's
+ *                window, then rendezvous "rows ready";
+ *   compute_dev: pull every rank's routes, plan the routes that go to this rank's experts, gather their token rows from
+ *                the owners' windows (peer loads), FC1, FC2 with every output row written into the owner's window
+ *                (peer stores) at its route index, then rendezvous "results complete";
+ *   finish_dev:  the ordered top-8 combine of this rank's own tokens -> BF16 [rows,4096] (+ optional FP32 plane).
+ * The result equals the single-GPU result bit for bit (rows of the GEMMs do not depend on how routes are tiled).
+ * Plan and numerical faults of compute_dev are read with m26b_scratch_status; m26b_ep_status returns 5 when a
+ * rendezvous ran out of time (default bound 5 s), 4 on a quantiser / combine fault. Windows are connected like the plane
+ * exchange's (64-byte handles gathered by the caller, or connect_local inside one process); publish_as marks a
+ * rendezvous (0 rows ready of the NEXT step, 1 results complete of the CURRENT step) as reached by `peer_rank`. */
+typedef struct m26b_ep m26b_ep;
+int m26b_layer_new_from_checkpoint_ep(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w, const uint8_t* up_s,
+                                      const uint8_t* down_w, const uint8_t* down_s, uint32_t ep_rank, uint32_t ep_size,
+                                      m26b_layer** out, char* err, size_t errlen);
+int m26b_ep_new(uint32_t tokens, uint32_t rank, uint32_t world, m26b_ep** out, uint8_t* handle_out, char* err, size_t errlen);
+int m26b_ep_connect(m26b_ep* e, const uint8_t* handles, char* err, size_t errlen);
+int m26b_ep_connect_local(m26b_ep* e, m26b_ep* const* all, char* err, size_t errlen);
+int m26b_ep_rows(const m26b_ep* e, uint32_t rank);
+int m26b_ep_set_wait_ms(m26b_ep* e, uint32_t ms);
+int m26b_ep_publish_as(m26b_ep* e, uint32_t peer_rank, uint32_t which, void* stream, char* err, size_t errlen);
+int m26b_ep_begin_dev(m26b_ep* e, const void* x, int x_dtype, const uint8_t* x_scales, int codec, const int32_t* ids,
+                      const float* weights, uint32_t rows, void* stream, char* err, size_t errlen);
+int m26b_ep_compute_dev(m26b_ep* e, const m26b_layer* l, m26b_scratch* s, void* stream, char* err, size_t errlen);
+int m26b_ep_finish_dev(m26b_ep* e, uint16_t* bf16_out, float* partial_out, void* stream, char* err, size_t errlen);
+int m26b_ep_status(m26b_ep* e, void* stream, char* err, size_t errlen);
+void m26b_ep_free(m26b_ep* e);
+
 /* Route plan without any allocation. No counterpart in the reference.
  * For callers that must not allocate device memory while they run: a serving loop that gave every free byte of the
  * GPU to resident expert weights at start-up, a request handler that has to stay clear of cudaMalloc's device-wide

@@ -9,6 +9,7 @@ built library raises.
 from .expert import (  # noqa: F401
     Exchange,
     ExpertError,
+    ExpertParallel,
     FfnStats,
     Layer,
     Scratch,

@@ -16,6 +16,9 @@ SYMBOLS = (
     "m26b_exchange_new", "m26b_exchange_connect", "m26b_exchange_connect_local", "m26b_exchange_plane",
     "m26b_exchange_set_wait_ms", "m26b_exchange_publish_as", "m26b_exchange_sum_dev", "m26b_exchange_status",
     "m26b_exchange_free",
+    "m26b_layer_new_from_checkpoint_ep", "m26b_ep_new", "m26b_ep_connect", "m26b_ep_connect_local", "m26b_ep_rows",
+    "m26b_ep_set_wait_ms", "m26b_ep_publish_as", "m26b_ep_begin_dev", "m26b_ep_compute_dev", "m26b_ep_finish_dev",
+    "m26b_ep_status", "m26b_ep_free",
 )
 
 _lib = None
@@ -66,8 +69,22 @@ def lib() -> C.CDLL:
     L.m26b_exchange_status.argtypes = [vp, vp, *err]
     L.m26b_exchange_free.argtypes = [vp]
     L.m26b_exchange_free.restype = None
+    L.m26b_layer_new_from_checkpoint_ep.argtypes = [u8p] * 6 + [C.c_uint32, C.c_uint32, C.POINTER(vp), *err]
+    L.m26b_ep_new.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(vp), u8p, *err]
+    L.m26b_ep_connect.argtypes = [vp, u8p, *err]
+    L.m26b_ep_connect_local.argtypes = [vp, C.POINTER(vp), *err]
+    L.m26b_ep_rows.argtypes = [vp, C.c_uint32]
+    L.m26b_ep_set_wait_ms.argtypes = [vp, C.c_uint32]
+    L.m26b_ep_publish_as.argtypes = [vp, C.c_uint32, C.c_uint32, vp, *err]
+    L.m26b_ep_begin_dev.argtypes = [vp, vp, C.c_int, u8p, C.c_int, i32p, f32p, C.c_uint32, vp, *err]
+    L.m26b_ep_compute_dev.argtypes = [vp, vp, vp, vp, *err]
+    L.m26b_ep_finish_dev.argtypes = [vp, u16p, f32p, vp, *err]
+    L.m26b_ep_status.argtypes = [vp, vp, *err]
+    L.m26b_ep_free.argtypes = [vp]
+    L.m26b_ep_free.restype = None
     for name in SYMBOLS:
-        if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version", "m26b_exchange_plane", "m26b_exchange_free"):
+        if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version", "m26b_exchange_plane", "m26b_exchange_free",
+                        "m26b_ep_free"):
             getattr(L, name).restype = C.c_int
     _lib = L
     return L

@@ -126,9 +126,13 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lan
 }
 // Work items: for every token tile, weight tile pairs 0, m_step, 2 m_step ... (m_step 2 when a CTA pair takes two
 // neighbouring weight tile pairs per item).
+//
+// skip_foreign (expert parallelism: this GPU holds a subset of the experts and sees every route of the request): a
+// route to an expert that is not resident here is left out of the plan (inverse = -1) instead of rejecting the request;
+// the other rules still apply to every route.
 __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                     uint32_t rows, const uint8_t* __restrict__ resident, int max_n,
-                                                    int mt_fc1, int mt_fc2, int m_step, PlanOut o) {
+                                                    int mt_fc1, int mt_fc2, int m_step, int skip_foreign, PlanOut o) {
     mt_fc1 /= m_step;
     mt_fc2 /= m_step;
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
@@ -153,10 +157,12 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
         if (live) {
             e = ids[r];
             const float wt = w[r];
-            ok = e >= 0 && e < kExperts && resident[e] && wt >= 0.0f && wt <= 3.402823466e+38f;
+            ok = e >= 0 && e < kExperts && wt >= 0.0f && wt <= 3.402823466e+38f;
             if (ok)
                 for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
-            if (!ok) my_bad = 1;
+            const bool here = ok && resident[e];
+            if (skip_foreign ? !ok : !here) my_bad = 1;
+            ok = here;
         }
         const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : -1 - int32_t(lane));
         if (ok && (peers & ((1u << lane) - 1u)) == 0u) wcnt[warp][e] += __popc(peers);
@@ -200,8 +206,10 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
     // stable placement: this warp's segment in route order, 32 routes at a time
     for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
         const uint32_t r = r0 + lane;
-        const bool live = r < hi;
-        const int32_t e = live ? ids[r] : -1 - int32_t(lane);
+        const bool in = r < hi;
+        int32_t e = in ? ids[r] : -1;
+        const bool live = in && (!skip_foreign || resident[e]);
+        if (!live) e = -1 - int32_t(lane);
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
         uint32_t g = 0;
@@ -213,6 +221,8 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
             o.inverse[r] = int32_t(g);
             o.original_routes[g] = int32_t(r);
             o.grouped_weights[g] = w[r];
+        } else if (in) {
+            o.inverse[r] = -1;
         }
     }
     // tiles and work items: one warp per expert, lanes over (weight tile pair, token tile)
@@ -238,7 +248,8 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
 // the CTA + the rank inside the 32-route group. Stable by construction.
 __device__ __forceinline__ void plan_warp_counts(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                  const uint8_t* __restrict__ resident, uint32_t lo, uint32_t hi,
-                                                 uint32_t lane, uint32_t* __restrict__ wrow, bool validate, uint32_t& bad) {
+                                                 uint32_t lane, uint32_t* __restrict__ wrow, bool validate, uint32_t& bad,
+                                                 int skip_foreign) {
     for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
         const uint32_t r = r0 + lane;
         const bool live = r < hi;
@@ -249,10 +260,14 @@ __device__ __forceinline__ void plan_warp_counts(const int32_t* __restrict__ ids
             ok = true;
             if (validate) {
                 const float wt = w[r];
-                ok = e >= 0 && e < kExperts && resident[e] && wt >= 0.0f && wt <= 3.402823466e+38f;
+                ok = e >= 0 && e < kExperts && wt >= 0.0f && wt <= 3.402823466e+38f;
                 if (ok)
                     for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
-                if (!ok) bad = 1;
+                const bool here = ok && resident[e];
+                if (skip_foreign ? !ok : !here) bad = 1;
+                ok = here;
+            } else if (skip_foreign) {
+                ok = resident[e] != 0;      // validated by the counting launch
             }
         }
         const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : -1 - int32_t(lane));
@@ -263,7 +278,7 @@ __device__ __forceinline__ void plan_warp_counts(const int32_t* __restrict__ ids
 __global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                           uint32_t rows, const uint8_t* __restrict__ resident,
                                                           uint32_t cta_routes, uint32_t* __restrict__ cta_cnt,
-                                                          PlanMeta* __restrict__ meta) {
+                                                          PlanMeta* __restrict__ meta, int skip_foreign) {
     __shared__ uint32_t wcnt[32][kExperts];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, routes = rows * kTopK;
     const uint32_t seg = cta_routes / 32u, base = blockIdx.x * cta_routes;
@@ -272,7 +287,7 @@ __global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restr
     for (uint32_t i = tid; i < 32 * kExperts; i += 1024) (&wcnt[0][0])[i] = 0;
     __syncthreads();
     uint32_t bad = 0;
-    plan_warp_counts(ids, w, resident, lo, hi, lane, wcnt[warp], true, bad);
+    plan_warp_counts(ids, w, resident, lo, hi, lane, wcnt[warp], true, bad, skip_foreign);
     if (bad) atomicOr(&meta->fault, uint32_t(kFaultPlan));
     __syncthreads();
     if (tid < kExperts) {
@@ -339,7 +354,8 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_
 }
 __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                           uint32_t rows, uint32_t cta_routes,
-                                                          const uint32_t* __restrict__ cta_off, PlanOut o) {
+                                                          const uint32_t* __restrict__ cta_off, PlanOut o,
+                                                          const uint8_t* __restrict__ resident, int skip_foreign) {
     __shared__ uint32_t wcnt[32][kExperts];
     if (o.meta->fault) return;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, routes = rows * kTopK;
@@ -349,7 +365,7 @@ __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restr
     for (uint32_t i = tid; i < 32 * kExperts; i += 1024) (&wcnt[0][0])[i] = 0;
     __syncthreads();
     uint32_t bad = 0;
-    plan_warp_counts(ids, w, nullptr, lo, hi, lane, wcnt[warp], false, bad);
+    plan_warp_counts(ids, w, resident, lo, hi, lane, wcnt[warp], false, bad, skip_foreign);
     __syncthreads();
     if (tid < kExperts) {   // per-warp exclusive offsets, on top of this CTA's global start for the expert
         uint32_t run = uint32_t(o.experts[tid].rbase) + cta_off[blockIdx.x * kExperts + tid];
@@ -358,8 +374,10 @@ __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restr
     __syncthreads();
     for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
         const uint32_t r = r0 + lane;
-        const bool live = r < hi;
-        const int32_t e = live ? ids[r] : -1 - int32_t(lane);
+        const bool in = r < hi;
+        int32_t e = in ? ids[r] : -1;
+        const bool live = in && (!skip_foreign || resident[e]);
+        if (!live) e = -1 - int32_t(lane);
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
         uint32_t g = 0;
@@ -371,6 +389,8 @@ __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restr
             o.inverse[r] = int32_t(g);
             o.original_routes[g] = int32_t(r);
             o.grouped_weights[g] = w[r];
+        } else if (in) {
+            o.inverse[r] = -1;
         }
     }
 }
@@ -381,19 +401,43 @@ __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restr
 // tile's scale blocks. Also the input gate of the path: a scale byte outside
 // 105..247 or a NaN payload code raises kFaultInputScale, as the reference's
 // activation view poisons them (kernels/b1/grouped.cu:28,36).
+//
+// With expert parallelism the request's token rows live on several GPUs (TokenSources): token t is row t - lo[k] of
+// owner k, read through the peer mapping and around L1 (another GPU wrote it). `routes` is then read from the plan
+// (only the routes to this GPU's experts are grouped).
+struct TokenSources {
+    uint32_t n;                 // 0: one local array
+    uint32_t token_base;        // request-wide index of the pass's first token
+    uint32_t lo[9];
+    const uint8_t* xq[8];
+    const uint8_t* xs[8];
+};
 __global__ void __launch_bounds__(256) permute_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs,
                                                       const int32_t* __restrict__ ids,
                                                       const int32_t* __restrict__ original_routes,
                                                       const ExpertPlan* __restrict__ experts,
                                                       const PlanMeta* __restrict__ meta, uint32_t routes,
                                                       uint8_t* __restrict__ x_perm, uint8_t* __restrict__ sfb,
-                                                      uint32_t* __restrict__ fault) {
+                                                      uint32_t* __restrict__ fault, TokenSources src) {
     if (meta->fault) return;   // a rejected plan leaves no valid route tables
     uint32_t bad = 0;
+    if (src.n) {
+        const ExpertPlan last = experts[kExperts - 1];
+        routes = uint32_t(last.rbase + last.count);
+    }
     for (uint32_t p = blockIdx.x; p < routes; p += gridDim.x) {
         const int32_t route = original_routes[p];
-        const uint32_t token = uint32_t(route) / kTopK;
-        const uint4 v = reinterpret_cast<const uint4*>(xq + size_t(token) * kHidden)[threadIdx.x];
+        uint32_t token = uint32_t(route) / kTopK;
+        if (src.n) {
+            token += src.token_base;
+            uint32_t k = 0;
+#pragma unroll
+            for (uint32_t i = 1; i < 8; ++i)
+                if (i < src.n && token >= src.lo[i]) k = i;
+            token -= src.lo[k];
+            xq = src.xq[k]; xs = src.xs[k];
+        }
+        const uint4 v = __ldcv(reinterpret_cast<const uint4*>(xq + size_t(token) * kHidden) + threadIdx.x);
         const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -403,7 +447,7 @@ __global__ void __launch_bounds__(256) permute_kernel(const uint8_t* __restrict_
             const ExpertPlan ep = experts[ids[route]];
             const uint32_t local = p - uint32_t(ep.rbase);
             const uint32_t tile = uint32_t(ep.tile_start) + local / uint32_t(ep.width), lr = local % uint32_t(ep.width);
-            const uint8_t sb = xs[size_t(token) * (kHidden / kBlockK) + threadIdx.x];
+            const uint8_t sb = __ldcv(xs + size_t(token) * (kHidden / kBlockK) + threadIdx.x);
             if (sb < 105 || sb > 247) bad = kFaultInputScale;
             const uint32_t chunk = threadIdx.x >> 2, kb = threadIdx.x & 3u;
             sfb[(size_t(tile) * (kHidden / kChunkK) + chunk) * kScaleBlockBytes + scale_block_offset(int(lr), int(kb))] = sb;
@@ -576,9 +620,9 @@ struct ProjSrc {
 };
 
 // w13[e][j][r][*]: r < 128 -> gate row 128 j + r, else up row 128 j + r - 128. 16 bytes per thread.
-__global__ void __launch_bounds__(256) prep_w13_kernel(ProjSrc gate, ProjSrc up, int i_local, uint8_t* __restrict__ dst) {
+__global__ void __launch_bounds__(256) prep_w13_kernel(ProjSrc gate, ProjSrc up, int i_local, uint8_t* __restrict__ dst, int n_experts) {
     const uint64_t vec_per_row = kHidden / 2 / 16, tiles = uint64_t(i_local) / kTileM;
-    const uint64_t total = uint64_t(kExperts) * tiles * kPairM * vec_per_row;
+    const uint64_t total = uint64_t(n_experts) * tiles * kPairM * vec_per_row;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint64_t v = i % vec_per_row, row = i / vec_per_row;
         const uint64_t r = row % kPairM, j = (row / kPairM) % tiles, e = row / kPairM / tiles;
@@ -591,9 +635,9 @@ __global__ void __launch_bounds__(256) prep_w13_kernel(ProjSrc gate, ProjSrc up,
 // s13[e][j][c][b][512], b = 0 gate / 1 up. One byte per thread; byte 255 (reserved) is stored as 254:
 // the checkpoint contract clamps it to 2^127 (crates/mimo26-expert/src/mxfp4.rs:24-29).
 __global__ void __launch_bounds__(256) prep_s13_kernel(ProjSrc gate, ProjSrc up, int i_local, uint8_t* __restrict__ dst,
-                                                       uint32_t* __restrict__ abnormal) {
+                                                       uint32_t* __restrict__ abnormal, int n_experts) {
     const uint64_t chunks = kHidden / kChunkK, tiles = uint64_t(i_local) / kTileM;
-    const uint64_t total = uint64_t(kExperts) * tiles * chunks * 2 * kScaleBlockBytes;
+    const uint64_t total = uint64_t(n_experts) * tiles * chunks * 2 * kScaleBlockBytes;
     uint32_t odd = 0;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint32_t o = uint32_t(i % kScaleBlockBytes);
@@ -609,9 +653,9 @@ __global__ void __launch_bounds__(256) prep_s13_kernel(ProjSrc gate, ProjSrc up,
     if (odd) atomicOr(abnormal, 1u);
 }
 // w2[e][h][i_local/2]: this rank's K slice of every down_proj row.
-__global__ void __launch_bounds__(256) prep_w2_kernel(ProjSrc down, int i_local, uint8_t* __restrict__ dst) {
+__global__ void __launch_bounds__(256) prep_w2_kernel(ProjSrc down, int i_local, uint8_t* __restrict__ dst, int n_experts) {
     const uint64_t vec_per_row = uint64_t(i_local) / 2 / 16;
-    const uint64_t total = uint64_t(kExperts) * kHidden * vec_per_row;
+    const uint64_t total = uint64_t(n_experts) * kHidden * vec_per_row;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint64_t v = i % vec_per_row, h = (i / vec_per_row) % kHidden, e = i / vec_per_row / kHidden;
         reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(
@@ -620,9 +664,9 @@ __global__ void __launch_bounds__(256) prep_w2_kernel(ProjSrc down, int i_local,
 }
 // s2[e][h/256][c][b][512]: block b covers rows 256 t + 128 b + r.
 __global__ void __launch_bounds__(256) prep_s2_kernel(ProjSrc down, int i_local, uint8_t* __restrict__ dst,
-                                                      uint32_t* __restrict__ abnormal) {
+                                                      uint32_t* __restrict__ abnormal, int n_experts) {
     const uint64_t chunks = uint64_t(i_local) / kChunkK, mts = kHidden / kPairM;
-    const uint64_t total = uint64_t(kExperts) * mts * chunks * 2 * kScaleBlockBytes;
+    const uint64_t total = uint64_t(n_experts) * mts * chunks * 2 * kScaleBlockBytes;
     uint32_t odd = 0;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint32_t o = uint32_t(i % kScaleBlockBytes);

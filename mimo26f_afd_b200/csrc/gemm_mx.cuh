@@ -50,6 +50,17 @@ constexpr uint32_t kTmemCols = 512;
 
 enum { kModeFc1 = 1, kModeFc2 = 2 };
 
+// Where FC2 puts its rows when the tokens belong to several GPUs (expert parallelism): token t of the request is row
+// t - lo[k] of owner k, the k with lo[k] <= t < lo[k + 1]; route (t, slot) goes to y[k] + ((t - lo[k]) * 8 + slot) * 4096.
+// The pointers are ordinary device addresses: the local buffer, or a peer's buffer mapped into this process.
+// n = 0: everything goes to GemmArgs::y.
+struct RouteSinks {
+    uint32_t n;
+    uint32_t token_base;        // request-wide index of the pass's first token
+    uint32_t lo[9];
+    float* y[8];
+};
+
 struct GemmArgs {
     const TokenTile* tiles;
     const WorkItem* items;
@@ -67,7 +78,20 @@ struct GemmArgs {
     // FC2 epilogue
     float* y;                   // [routes][4096] FP32, original route order
     const int32_t* original_routes;
+    int expert_base;            // first expert of the weight image (a layer may hold a contiguous subset of the experts)
+    RouteSinks sinks;
 };
+
+// Row of the FC2 output for a route of the pass.
+__device__ __forceinline__ float* y_row(const GemmArgs& p, int32_t route) {
+    if (p.sinks.n == 0) return p.y + size_t(route) * kHidden;
+    const uint32_t token = p.sinks.token_base + uint32_t(route) / kTopK, slot = uint32_t(route) % kTopK;
+    uint32_t k = 0;
+#pragma unroll
+    for (uint32_t i = 1; i < 8; ++i)
+        if (i < p.sinks.n && token >= p.sinks.lo[i]) k = i;
+    return p.sinks.y[k] + (size_t(token - p.sinks.lo[k]) * kTopK + slot) * kHidden;
+}
 
 // Token-operand tensor maps with boxes of 128, 64, 32 and 16 rows: a tile's rows are fetched with the fewest
 // boxes (binary decomposition of its row count). One 128-row box costs the copy engine about 500 cycles, eight
@@ -153,8 +177,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
                 const WorkItem wi = p.items[it];
                 const TokenTile tt = p.tiles[wi.tile];
-                const int w_row = (tt.expert * p.m_tiles + wi.m_tile) * kPairM;
-                const uint8_t* sfa_g = p.sfa + size_t(tt.expert * p.m_tiles + wi.m_tile) * p.k_chunks * 2 * kScaleBlockBytes;
+                const int w_row = ((tt.expert - p.expert_base) * p.m_tiles + wi.m_tile) * kPairM;
+                const uint8_t* sfa_g = p.sfa + size_t((tt.expert - p.expert_base) * p.m_tiles + wi.m_tile) * p.k_chunks * 2 * kScaleBlockBytes;
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
                 const uint32_t tx = kPairM * 64 + tt.n_mma * 128 + 3 * kScaleBlockBytes;
                 for (int c = 0; c < p.k_chunks; ++c) {
@@ -258,7 +282,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.acc_empty);
-                float* ybase = p.y + size_t(wi.m_tile) * kPairM + tile * kTileM + q * 32u + lane;
+                const uint32_t ycol = uint32_t(wi.m_tile) * kPairM + tile * kTileM + q * 32u + lane;
                 // lane l holds the route of token (wq >> 1) * 8 + 16 (l / 8) + l % 8: one load covers four groups
                 int32_t routes_lo = -1, routes_hi = -1;
                 {
@@ -271,7 +295,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int32_t route = __shfl_sync(0xffffffffu, g < 4 ? routes_lo : routes_hi, (g & 3) * 8 + j);
-                        if (route >= 0) ybase[size_t(route) * kHidden] = __uint_as_float(r[g][j]);
+                        if (route >= 0) y_row(p, route)[ycol] = __uint_as_float(r[g][j]);
                     }
                 }
             } else {

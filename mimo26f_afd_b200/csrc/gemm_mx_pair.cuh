@@ -78,8 +78,8 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const WorkItem wi = p.items[it];
                 const TokenTile tt = p.tiles[wi.tile];
                 const int m_tile = wi.m_tile + int(rank);
-                const int w_row = (tt.expert * p.m_tiles + m_tile) * kPairM;
-                const int sfa_row = (tt.expert * p.m_tiles + m_tile) * p.k_chunks * 2;
+                const int w_row = ((tt.expert - p.expert_base) * p.m_tiles + m_tile) * kPairM;
+                const int sfa_row = ((tt.expert - p.expert_base) * p.m_tiles + m_tile) * p.k_chunks * 2;
                 const int sfb_row = wi.tile * p.k_chunks;
                 const int half = tt.n_mma >> 1;                   // token rows this CTA holds
                 const int tok_row = tt.row_base + int(rank) * half;
@@ -179,7 +179,7 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-                float* ybase = p.y + size_t(m_tile) * kPairM + tile * kTileM + q * 32u + lane;
+                const uint32_t ycol = uint32_t(m_tile) * kPairM + tile * kTileM + q * 32u + lane;
                 int32_t routes_lo = -1, routes_hi = -1;
                 {
                     const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
@@ -191,7 +191,7 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int32_t route = __shfl_sync(0xffffffffu, g < 4 ? routes_lo : routes_hi, (g & 3) * 8 + j);
-                        if (route >= 0) ybase[size_t(route) * kHidden] = __uint_as_float(r[g][j]);
+                        if (route >= 0) y_row(p, route)[ycol] = __uint_as_float(r[g][j]);
                     }
                 }
             } else {

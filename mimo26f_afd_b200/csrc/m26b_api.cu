@@ -15,6 +15,7 @@
 #include "gemm_mx.cuh"
 #include "gemm_mx_pair.cuh"
 #include "prologue_small.cuh"
+#include "ep_kernels.cuh"
 
 using namespace m26b;
 
@@ -163,6 +164,7 @@ struct m26b_layer {
     uint8_t *w13 = nullptr, *s13 = nullptr, *w2 = nullptr, *s2 = nullptr, *resident = nullptr;
     int i_local = 0;
     uint32_t tp_rank = 0, tp_size = 1;
+    int expert_lo = 0, n_local = kExperts;      // the experts this layer holds: [expert_lo, expert_lo + n_local)
     bool all_normal = false;
     int device = 0;
     CUtensorMap map_w13, map_w2, map_s13, map_s2;
@@ -176,6 +178,21 @@ struct m26b_exchange {
     uint64_t plane_bytes = 0;
     uint32_t step = 0;                  // steps summed so far; the next step writes slot (step + 1) & 1
     long long wait_cycles = 0;
+};
+
+struct m26b_ep {
+    void* window = nullptr;
+    EpPeers peers{};
+    EpLayout lay{};
+    bool opened[8] = {false, false, false, false, false, false, false, false};
+    int rank = 0, world = 1, device = 0, khz = 0;
+    uint32_t tokens = 0;                 // tokens of a step, over all ranks
+    uint32_t lo[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // token block of rank r: [lo[r], lo[r + 1])
+    uint32_t step = 0;
+    long long wait_cycles = 0;
+    Dev ids, w;                          // every rank's routes, request order
+    uint32_t* fault = nullptr;           // device word: quantiser / combine faults of the step
+    uint32_t* hfault = nullptr;          // pinned copy
 };
 
 struct m26b_scratch {
@@ -203,15 +220,16 @@ struct m26b_scratch {
 namespace {
 
 int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, uint32_t tp_rank, uint32_t tp_size,
-                  m26b_layer** out, char* err, size_t errlen) {
+                  m26b_layer** out, char* err, size_t errlen, int expert_lo = 0, int n_local = kExperts) {
     const int i_local = kInter / int(tp_size);
     auto* L = new m26b_layer();
     L->i_local = i_local; L->tp_rank = tp_rank; L->tp_size = tp_size;
+    L->expert_lo = expert_lo; L->n_local = n_local;
     cudaGetDevice(&L->device);
-    const size_t w13_bytes = size_t(kExperts) * 2 * i_local * (kHidden / 2);
-    const size_t s13_bytes = size_t(kExperts) * 2 * i_local * (kHidden / kBlockK);
-    const size_t w2_bytes = size_t(kExperts) * kHidden * (i_local / 2);
-    const size_t s2_bytes = size_t(kExperts) * kHidden * (i_local / kBlockK);
+    const size_t w13_bytes = size_t(n_local) * 2 * i_local * (kHidden / 2);
+    const size_t s13_bytes = size_t(n_local) * 2 * i_local * (kHidden / kBlockK);
+    const size_t w2_bytes = size_t(n_local) * kHidden * (i_local / 2);
+    const size_t s2_bytes = size_t(n_local) * kHidden * (i_local / kBlockK);
     cudaError_t e;
     uint32_t* flag = nullptr;
     auto fail = [&](const char* what, cudaError_t ce, int rc) {
@@ -224,20 +242,21 @@ int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, u
         (e = cudaMalloc(&L->w2, w2_bytes)) != cudaSuccess || (e = cudaMalloc(&L->s2, s2_bytes)) != cudaSuccess ||
         (e = cudaMalloc(&L->resident, kExperts)) != cudaSuccess || (e = cudaMalloc(&flag, 4)) != cudaSuccess)
         return fail("m26b layer alloc", e, 2);
-    if ((e = cudaMemset(flag, 0, 4)) != cudaSuccess || (e = cudaMemset(L->resident, 1, kExperts)) != cudaSuccess)
+    if ((e = cudaMemset(flag, 0, 4)) != cudaSuccess || (e = cudaMemset(L->resident, 0, kExperts)) != cudaSuccess ||
+        (e = cudaMemset(L->resident + expert_lo, 1, size_t(n_local))) != cudaSuccess)
         return fail("m26b layer metadata", e, 2);
-    prep_w13_kernel<<<2048, 256>>>(gate, up, i_local, L->w13);
-    prep_s13_kernel<<<2048, 256>>>(gate, up, i_local, L->s13, flag);
-    prep_w2_kernel<<<2048, 256>>>(down, i_local, L->w2);
-    prep_s2_kernel<<<2048, 256>>>(down, i_local, L->s2, flag);
+    prep_w13_kernel<<<2048, 256>>>(gate, up, i_local, L->w13, n_local);
+    prep_s13_kernel<<<2048, 256>>>(gate, up, i_local, L->s13, flag, n_local);
+    prep_w2_kernel<<<2048, 256>>>(down, i_local, L->w2, n_local);
+    prep_s2_kernel<<<2048, 256>>>(down, i_local, L->s2, flag, n_local);
     uint32_t h = 1;
     if ((e = cudaGetLastError()) != cudaSuccess || (e = cudaMemcpy(&h, flag, 4, cudaMemcpyDeviceToHost)) != cudaSuccess ||
         (e = cudaDeviceSynchronize()) != cudaSuccess)
         return fail("m26b layer prepare", e, 2);
     cudaFree(flag); flag = nullptr;
     L->all_normal = h == 0;
-    if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(kExperts) * 2 * i_local, kHidden / 2, kPairM) ||
-        !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(kExperts) * kHidden, uint64_t(i_local) / 2, kPairM)) {
+    if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(n_local) * 2 * i_local, kHidden / 2, kPairM) ||
+        !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(n_local) * kHidden, uint64_t(i_local) / 2, kPairM)) {
         set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight operands");
         m26b_layer_free(L);
         return 2;
@@ -347,13 +366,19 @@ void launch_small_prologue(uint32_t grid, cudaStream_t st, const SmallIo& io, co
     small_prologue_kernel<CODEC, IN><<<grid, 256, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
 }
 
+// A pass of an expert-parallel step: where the pass's token rows live and where its FC2 rows go.
+struct EpPass {
+    TokenSources src;
+    RouteSinks sinks;
+};
+
 // Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine. `raw` (only with at most
 // kSmallRows rows) names activations still to be quantised into xq / xs; `status_cleared`: the caller has already
 // zeroed the status block on the stream.
 int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const uint8_t* xs, const int32_t* ids,
                  const float* w, uint32_t rows, uint16_t* bf16_out, float* partial_out, Status* status,
                  cudaStream_t st, bool events, char* err, size_t errlen, const RawInput* raw = nullptr,
-                 bool status_cleared = false) {
+                 bool status_cleared = false, const EpPass* ep = nullptr) {
     cudaError_t e;
     const uint32_t routes = rows * kTopK;
     const LaunchClass lc = launch_class(rows);
@@ -370,7 +395,9 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     const int m_step = pair ? 2 : 1;
     const bool kt = (S->debug & 2u) != 0;
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
-    if (rows <= kSmallRows) {
+    const int skip_foreign = ep ? 1 : 0;
+    const TokenSources src = ep ? ep->src : TokenSources{};
+    if (rows <= kSmallRows && !ep) {
         // one launch: plan + (quantise) + gate + permutation; timed as the permutation, the plan slot reads zero
         if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
         SmallIo io{};
@@ -390,22 +417,22 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         M26B_CK(cudaGetLastError(), "m26b prologue launch");
     } else {
         if (routes <= 4096) {
-            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, m_step, po);
+            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, m_step, skip_foreign, po);
         } else {
             // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
             const uint32_t slabs = (routes + 1023u) / 1024u;
             const uint32_t n_cta = slabs < 128u ? slabs : 128u;
             const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
             uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
-            plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, L->resident, cta_routes, cta_cnt, &status->meta);
+            plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, L->resident, cta_routes, cta_cnt, &status->meta, skip_foreign);
             plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step, po);
-            plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po);
+            plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po, L->resident, skip_foreign);
         }
         M26B_CK(cudaGetLastError(), "m26b plan launch");
         if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
         permute_kernel<<<routes < 65535u * 8u ? routes : 65535u * 8u, 256, 0, st>>>(
             xq, xs, ids, S->original.as<int32_t>(), S->experts.as<ExpertPlan>(), &status->meta, routes,
-            S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input);
+            S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input, src);
         M26B_CK(cudaGetLastError(), "m26b permute launch");
     }
     if (kt) M26B_CK(cudaEventRecord(S->kev[3], st), "m26b event");
@@ -417,6 +444,8 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     a.mid_f32 = (S->debug & 1u) ? S->mid_f32.as<float>() : nullptr;
     a.y = S->y.as<float>();
     a.original_routes = S->original.as<int32_t>();
+    a.expert_base = L->expert_lo;
+    if (ep) a.sinks = ep->sinks;
     // FC1: weights w13 (K = hidden), tokens x_perm
     a.items = S->items1.as<WorkItem>(); a.n_items = &status->meta.n_items_fc1;
     a.sfa = L->s13; a.sfb = S->sfb1.as<uint8_t>(); a.m_tiles = mt1; a.k_chunks = kHidden / kChunkK;
@@ -445,8 +474,9 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (kt) M26B_CK(cudaEventRecord(S->kev[5], st), "m26b event");
     const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
     const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
-    M26B_CK(launch_dependent(route_reduce_kernel, blocks, 256u, size_t(0), st, static_cast<const float*>(S->y.as<float>()), w,
-                             rows, partial_out, bf16_out, &status->fault_reduce), "m26b reduce launch");
+    if (!ep)   // an expert-parallel pass leaves its rows with the tokens' owners; they combine after the step's rendezvous
+        M26B_CK(launch_dependent(route_reduce_kernel, blocks, 256u, size_t(0), st, static_cast<const float*>(S->y.as<float>()), w,
+                                 rows, partial_out, bf16_out, &status->fault_reduce), "m26b reduce launch");
     if (events) M26B_CK(cudaEventRecord(S->e1, st), "m26b event 1");
     if (kt) { M26B_CK(cudaEventRecord(S->kev[6], st), "m26b event"); S->kev_valid = true; }
     S->last_rows = rows; S->last_i_local = L->i_local; S->last_ids = ids; S->last_xq = xq; S->last_xs = xs;
@@ -541,6 +571,26 @@ int m26b_layer_new_from_checkpoint(const uint8_t* gate_w, const uint8_t* gate_s,
     down.row_stride_p = kInter / 2; down.row_stride_s = kInter / kBlockK;
     down.col0_p = il * tp_rank / 2; down.col0_s = il * tp_rank / kBlockK;
     return prepare_layer(gate, up, down, tp_rank, tp_size, out, err, errlen);
+}
+
+int m26b_layer_new_from_checkpoint_ep(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w,
+                                      const uint8_t* up_s, const uint8_t* down_w, const uint8_t* down_s,
+                                      uint32_t ep_rank, uint32_t ep_size, m26b_layer** out, char* err, size_t errlen) {
+    if (!out || !gate_w || !gate_s || !up_w || !up_s || !down_w || !down_s ||
+        !(ep_size == 1 || ep_size == 2 || ep_size == 4 || ep_size == 8) || ep_rank >= ep_size) {
+        set_msg(err, errlen, "m26b layer: bad checkpoint tensors/rank");
+        return 1;
+    }
+    ProjSrc gate{}, up{}, down{};
+    gate.payload = gate_w; gate.scales = gate_s;
+    gate.expert_stride_p = uint64_t(kInter) * (kHidden / 2); gate.expert_stride_s = uint64_t(kInter) * (kHidden / kBlockK);
+    gate.row_stride_p = kHidden / 2; gate.row_stride_s = kHidden / kBlockK;
+    up = gate; up.payload = up_w; up.scales = up_s;
+    down.payload = down_w; down.scales = down_s;
+    down.expert_stride_p = uint64_t(kHidden) * (kInter / 2); down.expert_stride_s = uint64_t(kHidden) * (kInter / kBlockK);
+    down.row_stride_p = kInter / 2; down.row_stride_s = kInter / kBlockK;
+    const int n_local = kExperts / int(ep_size);
+    return prepare_layer(gate, up, down, 0, 1, out, err, errlen, int(ep_rank) * n_local, n_local);
 }
 
 int m26b_layer_all_normal(const m26b_layer* L) { return L && L->all_normal ? 1 : 0; }
@@ -894,6 +944,227 @@ void m26b_exchange_free(m26b_exchange* X) {
     delete X;
 }
 
+// ---- expert parallelism inside one box ---------------------------------------------------------
+namespace {
+uint8_t* ep_ptr(const m26b_ep* E, int r, size_t off) { return E->peers.window[r] + off; }
+bool ep_connected(const m26b_ep* E) {
+    for (int r = 0; r < E->world; ++r)
+        if (!E->peers.window[r]) return false;
+    return true;
+}
+}  // namespace
+
+int m26b_ep_new(uint32_t tokens, uint32_t rank, uint32_t world, m26b_ep** out, uint8_t* handle_out, char* err, size_t errlen) {
+    if (!out || !tokens || tokens > (1u << 20) || !(world == 1 || world == 2 || world == 4 || world == 8) || rank >= world) {
+        set_msg(err, errlen, "m26b ep: bad token count / rank / world");
+        return 1;
+    }
+    cudaError_t e;
+    m26b_ep* E = new m26b_ep();
+    E->rank = int(rank); E->world = int(world); E->tokens = tokens;
+    const uint32_t base = tokens / world, extra = tokens % world;    // contiguous blocks, the first `extra` one longer
+    for (uint32_t r = 0; r <= world; ++r) E->lo[r] = r * base + (r < extra ? r : extra);
+    for (uint32_t r = world + 1; r < 9; ++r) E->lo[r] = tokens;
+    E->lay.cap = base + (extra ? 1u : 0u);
+    if (E->lay.cap == 0) E->lay.cap = 1;
+    if ((e = cudaGetDevice(&E->device)) != cudaSuccess || (e = cudaMalloc(&E->window, E->lay.bytes())) != cudaSuccess ||
+        (e = cudaMemset(E->window, 0, sizeof(EpHeader))) != cudaSuccess || (e = cudaMalloc(&E->fault, 4)) != cudaSuccess ||
+        (e = cudaMemset(E->fault, 0, 4)) != cudaSuccess ||
+        (e = cudaMallocHost(reinterpret_cast<void**>(&E->hfault), 8)) != cudaSuccess ||
+        (e = E->ids.ensure(size_t(tokens) * kTopK * 4)) != cudaSuccess || (e = E->w.ensure(size_t(tokens) * kTopK * 4)) != cudaSuccess) {
+        set_err(err, errlen, "m26b ep window", e);
+        m26b_ep_free(E);
+        return 2;
+    }
+    int khz = 0;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, E->device);
+    E->khz = khz > 0 ? khz : 1965000;
+    E->wait_cycles = 5000ll * E->khz;
+    E->peers.window[rank] = static_cast<uint8_t*>(E->window);
+    if (handle_out) {
+        cudaIpcMemHandle_t h;
+        if ((e = cudaIpcGetMemHandle(&h, E->window)) != cudaSuccess) {
+            set_err(err, errlen, "m26b ep export", e);
+            m26b_ep_free(E);
+            return 2;
+        }
+        std::memcpy(handle_out, &h, 64);
+    }
+    *out = E;
+    return 0;
+}
+
+int m26b_ep_connect(m26b_ep* E, const uint8_t* handles, char* err, size_t errlen) {
+    if (!E || !handles) { set_msg(err, errlen, "m26b ep connect: bad arguments"); return 1; }
+    if (!device_ok(E->device, err, errlen)) return 1;
+    for (int r = 0; r < E->world; ++r) {
+        if (r == E->rank || E->peers.window[r]) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handles + size_t(r) * 64, 64);
+        void* p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) { set_err(err, errlen, "m26b ep: opening a peer window", e); return 2; }
+        E->peers.window[r] = static_cast<uint8_t*>(p);
+        E->opened[r] = true;
+    }
+    return 0;
+}
+
+int m26b_ep_connect_local(m26b_ep* E, m26b_ep* const* all, char* err, size_t errlen) {
+    if (!E || !all) { set_msg(err, errlen, "m26b ep connect: bad arguments"); return 1; }
+    for (int r = 0; r < E->world; ++r) {
+        if (r == E->rank) continue;
+        if (!all[r] || all[r]->world != E->world || all[r]->rank != r || all[r]->tokens != E->tokens) {
+            set_msg(err, errlen, "m26b ep connect: windows do not belong together");
+            return 1;
+        }
+        E->peers.window[r] = static_cast<uint8_t*>(all[r]->window);
+    }
+    return 0;
+}
+
+int m26b_ep_rows(const m26b_ep* E, uint32_t rank) { return E && int(rank) < E->world ? int(E->lo[rank + 1] - E->lo[rank]) : -1; }
+
+int m26b_ep_set_wait_ms(m26b_ep* E, uint32_t ms) {
+    if (!E || !ms) return 1;
+    E->wait_cycles = (long long)ms * E->khz;
+    return 0;
+}
+
+int m26b_ep_publish_as(m26b_ep* E, uint32_t peer_rank, uint32_t which, void* stream, char* err, size_t errlen) {
+    if (!E || int(peer_rank) >= E->world || int(peer_rank) == E->rank || which > 1) { set_msg(err, errlen, "m26b ep: bad peer"); return 1; }
+    const uint32_t v = which == 0 ? E->step + 1 : E->step;     // rendezvous 0 opens a step, rendezvous 1 closes it
+    const cudaError_t e = cudaMemcpyAsync(&static_cast<EpHeader*>(E->window)->flags[which][peer_rank], &v, 4, cudaMemcpyHostToDevice,
+                                          static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b ep publish", e); return 2; }
+    return 0;
+}
+
+// Phase 1: this rank's tokens into its window (quantised rows, routes), then the "rows ready" rendezvous.
+int m26b_ep_begin_dev(m26b_ep* E, const void* x, int x_dtype, const uint8_t* x_scales, int codec, const int32_t* ids,
+                      const float* weights, uint32_t rows, void* stream, char* err, size_t errlen) {
+    if (!E || !x || !ids || !weights || x_dtype < 0 || x_dtype > 2 || (x_dtype == 2 && !x_scales) || codec < 0 || codec > 1 ||
+        rows != E->lo[E->rank + 1] - E->lo[E->rank]) {
+        set_msg(err, errlen, "m26b ep begin: bad arguments (rows must be this rank's token block)");
+        return 1;
+    }
+    if (!device_ok(E->device, err, errlen)) return 1;
+    if (!ep_connected(E)) { set_msg(err, errlen, "m26b ep: not connected to every peer"); return 1; }
+    cudaError_t e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* xq = ep_ptr(E, E->rank, E->lay.xq_off());
+    uint8_t* xs = ep_ptr(E, E->rank, E->lay.xs_off());
+    M26B_CK(cudaMemsetAsync(E->fault, 0, 4, st), "m26b ep fault clear");
+    if (rows) {
+        if (x_dtype == 2) {
+            M26B_CK(cudaMemcpyAsync(xq, x, size_t(rows) * kHidden, cudaMemcpyDeviceToDevice, st), "m26b ep rows");
+            M26B_CK(cudaMemcpyAsync(xs, x_scales, size_t(rows) * (kHidden / kBlockK), cudaMemcpyDeviceToDevice, st), "m26b ep scales");
+        } else {
+            const int rc = m26b_quantize_dev(x, x_dtype, uint64_t(rows) * kHidden, codec, xq, xs, E->fault, st, err, errlen);
+            if (rc) return rc;
+        }
+        M26B_CK(cudaMemcpyAsync(ep_ptr(E, E->rank, E->lay.ids_off()), ids, size_t(rows) * kTopK * 4, cudaMemcpyDeviceToDevice, st), "m26b ep ids");
+        M26B_CK(cudaMemcpyAsync(ep_ptr(E, E->rank, E->lay.w_off()), weights, size_t(rows) * kTopK * 4, cudaMemcpyDeviceToDevice, st), "m26b ep weights");
+    }
+    E->step += 1;
+    ep_rendezvous_kernel<<<1, 32, 0, st>>>(E->peers, E->rank, E->world, 0, E->step, E->wait_cycles);
+    M26B_CK(cudaGetLastError(), "m26b ep rendezvous launch");
+    return 0;
+}
+
+// Phase 2: this rank's experts on every rank's tokens, in passes of at most kMaxPassRows tokens; then the
+// "results complete" rendezvous.
+int m26b_ep_compute_dev(m26b_ep* E, const m26b_layer* L, m26b_scratch* S, void* stream, char* err, size_t errlen) {
+    if (!E || !L || !S) { set_msg(err, errlen, "m26b ep compute: null handle"); return 1; }
+    if (!device_ok(E->device, err, errlen) || !device_ok(L->device, err, errlen) || !device_ok(S->device, err, errlen)) return 1;
+    if (L->tp_size != 1 || L->n_local * E->world != kExperts || L->expert_lo != E->rank * L->n_local) {
+        set_msg(err, errlen, "m26b ep compute: the layer does not hold this rank's block of experts");
+        return 1;
+    }
+    cudaError_t e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t pass_rows = E->tokens < kMaxPassRows ? E->tokens : kMaxPassRows;
+    const uint32_t passes = (E->tokens + kMaxPassRows - 1) / kMaxPassRows;
+    if (passes > 64) { set_msg(err, errlen, "m26b ep compute: too many tokens"); return 1; }
+    int rc = ensure_pass(S, pass_rows, L->i_local, false, err, errlen);
+    if (rc) return rc;
+    TokenSources shards{};
+    shards.n = uint32_t(E->world);
+    RouteSinks sinks{};
+    sinks.n = uint32_t(E->world);
+    for (int r = 0; r < 9; ++r) { shards.lo[r] = E->lo[r]; sinks.lo[r] = E->lo[r]; }
+    for (int r = 0; r < E->world; ++r) {
+        shards.xq[r] = ep_ptr(E, r, E->lay.xq_off());
+        shards.xs[r] = ep_ptr(E, r, E->lay.xs_off());
+        sinks.y[r] = reinterpret_cast<float*>(ep_ptr(E, r, E->lay.y_off()));
+    }
+    const uint32_t total = E->tokens * kTopK;
+    const unsigned gb = (total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184;
+    ep_gather_routes_kernel<<<gb, 256, 0, st>>>(E->peers, E->lay, E->world, shards, E->ids.as<int32_t>(), E->w.as<float>());
+    M26B_CK(cudaGetLastError(), "m26b ep gather launch");
+    for (uint32_t ps = 0; ps < passes; ++ps) {
+        const uint32_t r0 = ps * kMaxPassRows, n = E->tokens - r0 < kMaxPassRows ? E->tokens - r0 : kMaxPassRows;
+        EpPass pass{shards, sinks};
+        pass.src.token_base = r0; pass.sinks.token_base = r0;
+        rc = enqueue_pass(L, S, nullptr, nullptr, E->ids.as<int32_t>() + size_t(r0) * kTopK, E->w.as<float>() + size_t(r0) * kTopK, n,
+                          nullptr, nullptr, S->status.as<Status>() + ps, st, false, err, errlen, nullptr, false, &pass);
+        if (rc) return rc;
+    }
+    S->pending = true;
+    S->n_status = passes;
+    ep_rendezvous_kernel<<<1, 32, 0, st>>>(E->peers, E->rank, E->world, 1, E->step, E->wait_cycles);
+    M26B_CK(cudaGetLastError(), "m26b ep rendezvous launch");
+    return 0;
+}
+
+// Phase 3: the ordered top-8 combine of this rank's tokens from the rows its peers (and itself) delivered.
+int m26b_ep_finish_dev(m26b_ep* E, uint16_t* bf16_out, float* partial_out, void* stream, char* err, size_t errlen) {
+    if (!E || !bf16_out) { set_msg(err, errlen, "m26b ep finish: bad arguments"); return 1; }
+    if (!device_ok(E->device, err, errlen)) return 1;
+    const uint32_t rows = E->lo[E->rank + 1] - E->lo[E->rank];
+    if (!rows) return 0;
+    const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
+    const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
+    route_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float*>(ep_ptr(E, E->rank, E->lay.y_off())), reinterpret_cast<const float*>(ep_ptr(E, E->rank, E->lay.w_off())),
+        rows, partial_out, bf16_out, E->fault);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b ep reduce launch", e); return 2; }
+    return 0;
+}
+
+int m26b_ep_status(m26b_ep* E, void* stream, char* err, size_t errlen) {
+    if (!E) { set_msg(err, errlen, "m26b ep status: null handle"); return 1; }
+    cudaError_t e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    M26B_CK(cudaMemcpyAsync(&E->hfault[0], &static_cast<EpHeader*>(E->window)->error, 4, cudaMemcpyDeviceToHost, st), "m26b ep status");
+    M26B_CK(cudaMemcpyAsync(&E->hfault[1], E->fault, 4, cudaMemcpyDeviceToHost, st), "m26b ep status");
+    M26B_CK(cudaStreamSynchronize(st), "m26b ep status sync");
+    if (E->hfault[0]) {
+        M26B_CK(cudaMemsetAsync(&static_cast<EpHeader*>(E->window)->error, 0, 4, st), "m26b ep status clear");
+        M26B_CK(cudaStreamSynchronize(st), "m26b ep status sync");
+        if (err && errlen)
+            std::snprintf(err, errlen, "m26b ep: rank %d gave up waiting for peers (mask 0x%x: bits 0-7 rows ready, 8-15 results complete) at step %u",
+                          E->rank, E->hfault[0], E->step);
+        return 5;
+    }
+    if (E->hfault[1]) {
+        if (err && errlen) std::snprintf(err, errlen, "m26b ep: quantizer/reduce fault %u on rank %d", E->hfault[1], E->rank);
+        return 4;
+    }
+    return 0;
+}
+
+void m26b_ep_free(m26b_ep* E) {
+    if (!E) return;
+    for (int r = 0; r < 8; ++r)
+        if (E->opened[r] && E->peers.window[r]) cudaIpcCloseMemHandle(E->peers.window[r]);
+    if (E->window) cudaFree(E->window);
+    if (E->fault) cudaFree(E->fault);
+    if (E->hfault) cudaFreeHost(E->hfault);
+    delete E;
+}
+
 int m26b_scratch_timings(m26b_scratch* S, float* ms6, char* err, size_t errlen) {
     if (!S || !ms6 || !S->kev_valid) { set_msg(err, errlen, "m26b timings: enable debug flag 2 and run a pass first"); return 1; }
     cudaError_t e;
@@ -959,9 +1230,9 @@ int m26b_plan_static(const int32_t* ids, const float* weights, uint32_t rows, in
     const uint32_t n_cta = slabs < 128u ? slabs : 128u;
     const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
     PlanOut po{inverse, original_routes, grouped_weights, sc->experts, sc->tiles, sc->items_fc1, sc->items_fc2, meta};
-    plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, sc->resident, cta_routes, sc->cta_cnt, meta);
+    plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, sc->resident, cta_routes, sc->cta_cnt, meta, 0);
     plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, 1, po);
-    plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, cta_routes, sc->cta_cnt, po);
+    plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, cta_routes, sc->cta_cnt, po, sc->resident, 0);
     M26B_CK(cudaGetLastError(), "m26b plan_static launch");
     return 0;
 }

@@ -81,6 +81,15 @@ class Layer:
             C.byref(out), err, 256), err)
         return cls(out.value)
 
+    @classmethod
+    def from_checkpoint_ep(cls, gate_w, gate_s, up_w, up_s, down_w, down_s, ep_rank: int, ep_size: int) -> "Layer":
+        """Expert-parallel rank: the six tensors stacked over this rank's 256 / ep_size experts only."""
+        out, err = C.c_void_p(), C.create_string_buffer(256)
+        _check(_native.lib().m26b_layer_new_from_checkpoint_ep(
+            _ptr(gate_w), _ptr(gate_s), _ptr(up_w), _ptr(up_s), _ptr(down_w), _ptr(down_s), ep_rank, ep_size,
+            C.byref(out), err, 256), err)
+        return cls(out.value)
+
     def all_scales_normal(self) -> bool:
         return _native.lib().m26b_layer_all_normal(self._h) != 0
 
@@ -278,6 +287,80 @@ class Exchange:
     def close(self) -> None:
         if self._h:
             _native.lib().m26b_exchange_free(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ExpertParallel:
+    """This rank's side of expert parallelism inside one box (one process per GPU): experts are split over the ranks,
+    tokens too; token rows are read from their owners and result rows written to them through peer mappings.
+    ``step`` = ``begin`` + ``compute`` + ``finish``; every rank runs the three in the same order."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, tokens: int, rank: int, world: int, export: bool = True):
+        out, err = C.c_void_p(), C.create_string_buffer(256)
+        self.handle = (C.c_uint8 * self.HANDLE_BYTES)() if export else None
+        _check(_native.lib().m26b_ep_new(tokens, rank, world, C.byref(out), C.addressof(self.handle) if export else None,
+                                         err, 256), err)
+        self._h, self.rank, self.world, self.tokens = out, rank, world, tokens
+
+    def handle_bytes(self) -> bytes:
+        return bytes(self.handle)
+
+    def rows(self, rank=None) -> int:
+        return _native.lib().m26b_ep_rows(self._h, self.rank if rank is None else rank)
+
+    def connect(self, handles: bytes) -> None:
+        if len(handles) != self.world * self.HANDLE_BYTES:
+            raise ExpertError(1, "m26b ep connect: need one 64-byte handle per rank")
+        buf = (C.c_uint8 * len(handles)).from_buffer_copy(handles)
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_connect(self._h, C.addressof(buf), err, 256), err)
+
+    def connect_local(self, all_ranks) -> None:
+        arr = (C.c_void_p * self.world)(*[w._h.value for w in all_ranks])
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_connect_local(self._h, arr, err, 256), err)
+
+    def set_wait_ms(self, ms: int) -> None:
+        _native.lib().m26b_ep_set_wait_ms(self._h, ms)
+
+    def publish_as(self, peer_rank: int, which: int, stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_publish_as(self._h, peer_rank, which, _ptr(stream), err, 256), err)
+
+    def begin(self, x, ids, weights, rows: int, *, x_dtype: int = 0, x_scales=None, codec: int = 0, stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_begin_dev(self._h, _ptr(x), x_dtype, _ptr(x_scales), codec, _ptr(ids), _ptr(weights), rows,
+                                               _ptr(stream), err, 256), err)
+
+    def compute(self, layer: "Layer", scratch: "Scratch", stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_compute_dev(self._h, layer._h, scratch._h, _ptr(stream), err, 256), err)
+
+    def finish(self, bf16_out, partial_out=None, stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_finish_dev(self._h, _ptr(bf16_out), _ptr(partial_out), _ptr(stream), err, 256), err)
+
+    def step(self, layer, scratch, x, ids, weights, rows, bf16_out, *, partial_out=None, x_dtype=0, x_scales=None, codec=0,
+             stream=None) -> None:
+        self.begin(x, ids, weights, rows, x_dtype=x_dtype, x_scales=x_scales, codec=codec, stream=stream)
+        self.compute(layer, scratch, stream=stream)
+        self.finish(bf16_out, partial_out, stream=stream)
+
+    def status(self, stream=None) -> None:
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_status(self._h, _ptr(stream), err, 256), err)
+
+    def close(self) -> None:
+        if self._h:
+            _native.lib().m26b_ep_free(self._h)
             self._h = C.c_void_p(0)
 
     def __del__(self):

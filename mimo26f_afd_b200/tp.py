@@ -61,6 +61,24 @@ def make_exchange(tokens: int, group=None):
     return ex
 
 
+def make_expert_parallel(tokens: int, group=None):
+    """This rank's expert-parallel window for steps of ``tokens`` tokens (over all ranks), connected to every peer.
+    Rank r owns tokens ``shard_tokens(tokens, r, world)`` and experts [r 256 / world, (r + 1) 256 / world)."""
+    import torch.distributed as dist
+
+    from . import expert
+
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ep = expert.ExpertParallel(tokens, rank, world)
+    lo, hi = shard_tokens(tokens, rank, world)
+    assert ep.rows() == hi - lo
+    handles = [None] * world
+    dist.all_gather_object(handles, ep.handle_bytes(), group=group)
+    ep.connect(b"".join(handles))
+    dist.barrier(group)
+    return ep
+
+
 def tp_combine(plane, out_f32, group=None, stream=None):
     """Rank-ordered FP32 sum of every rank's BF16 plane into ``out_f32`` (CUDA tensors)."""
     from . import expert

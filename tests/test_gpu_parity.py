@@ -235,6 +235,74 @@ def test_plane_exchange_two_windows_one_process(dev, oracle_mod):
         e_.close()
 
 
+@pytest.mark.parametrize("tokens,zipf", [(9, 0.0), (96, 1.2), (300, 0.0)])
+def test_expert_parallel_two_ranks_one_process_equals_single_gpu(layer, scratch, dev, tokens, zipf):
+    """Expert parallelism with both ranks in this process (each rank's rendezvous is marked reached from the host, so no
+    kernel waits for another kernel): experts split 128 / 128, tokens split in two blocks, rows gathered from and
+    results scattered to the owner's window. Output must equal the single-GPU layer's bit for bit."""
+    import torch
+
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import synth
+
+    x_bits = synth.activations_bf16(SEED + 3, tokens)
+    ids, w = synth.routing(SEED + 3, tokens, zipf)
+    bf_ref, part_ref = run_dev(layer, scratch, dev, x_bits, ids, w)
+    layers, eps = [], []
+    for r in range(2):
+        wt = synth.layer_torch(SEED, dev, n_experts=128, first_expert=128 * r)
+        layers.append(M.Layer.from_checkpoint_ep(*[wt[n] for n in synth.TENSORS], ep_rank=r, ep_size=2))
+        del wt
+        eps.append(M.ExpertParallel(tokens, r, 2, export=False))
+    for e in eps:
+        e.connect_local(eps)
+    s2 = M.Scratch()
+    lo = [0, eps[0].rows(0), tokens]
+    assert eps[0].rows(0) + eps[0].rows(1) == tokens and eps[1].rows() == tokens - lo[1]
+    xd, idd, wd = to_dev(x_bits, dev), to_dev(ids, dev), to_dev(w, dev)
+    outs = [torch.empty((lo[r + 1] - lo[r], H), dtype=torch.int16, device=dev) for r in range(2)]
+    parts = [torch.empty((lo[r + 1] - lo[r], H), dtype=torch.float32, device=dev) for r in range(2)]
+    for step in range(2):
+        for r in range(2):
+            eps[r].publish_as(1 - r, 0)
+            eps[r].begin(xd[lo[r]:lo[r + 1]], idd[lo[r]:lo[r + 1]], wd[lo[r]:lo[r + 1]], lo[r + 1] - lo[r])
+        for r in range(2):
+            eps[r].publish_as(1 - r, 1)
+            eps[r].compute(layers[r], s2)
+            s2.status()
+        for r in range(2):
+            eps[r].finish(outs[r], parts[r])
+            eps[r].status()
+        torch.cuda.synchronize()
+        for r in range(2):
+            assert np.array_equal(outs[r].cpu().numpy().view(np.uint16), bf_ref[lo[r]:lo[r + 1]]), (step, r)
+            assert np.array_equal(parts[r].cpu().numpy().view(np.uint32), part_ref[lo[r]:lo[r + 1]].view(np.uint32)), (step, r)
+    # a rendezvous nobody else reaches: bounded wait, status 5, window usable afterwards
+    eps[0].set_wait_ms(20)
+    eps[0].begin(xd[lo[0]:lo[1]], idd[lo[0]:lo[1]], wd[lo[0]:lo[1]], lo[1])
+    with pytest.raises(M.ExpertError) as e:
+        eps[0].status()
+    assert e.value.code == 5
+    eps[1].publish_as(0, 0)                                  # rank 1 catches up with the step rank 0 lost
+    eps[1].begin(xd[lo[1]:], idd[lo[1]:], wd[lo[1]:], tokens - lo[1])
+    eps[1].status()
+    # an expert id outside [0, 256) on any rank's tokens is still a plan rejection on every expert-parallel rank
+    bad = to_dev(np.where(np.arange(tokens * TOPK).reshape(tokens, TOPK) == tokens * TOPK - 1, 300, ids).astype(np.int32), dev)
+    for r in range(2):
+        eps[r].publish_as(1 - r, 0)
+        eps[r].begin(xd[lo[r]:lo[r + 1]], bad[lo[r]:lo[r + 1]], wd[lo[r]:lo[r + 1]], lo[r + 1] - lo[r])
+    eps[0].publish_as(1, 1)
+    eps[0].compute(layers[0], s2)
+    with pytest.raises(M.ExpertError) as e:
+        s2.status()
+    assert e.value.code == 3
+    with pytest.raises(M.ExpertError) as e:
+        eps[0].compute(layers[1], s2)                       # the other rank's layer: refused before anything is launched
+    assert e.value.code == 1
+    for e_ in eps:
+        e_.close()
+
+
 # ------------------------------------------------------------------------------------------ the whole path
 def check_ffn(layer, scratch, dev, oracle_mod, tokens, zipf, codec, tp_rank=0, tp_size=1, seed=SEED):
     from mimo26f_afd_b200 import synth

@@ -1,5 +1,6 @@
-"""Tensor-parallel ranks on real GPUs of one box: the NVLink peer-memory exchange against NCCL and the oracle.
-Needs at least two GPUs (skipped otherwise); the ranks are child processes, one per GPU."""
+"""Tensor-parallel and expert-parallel ranks on real GPUs of one box: the NVLink peer-memory exchange against NCCL and
+the oracle, and the expert-parallel step against the single-GPU layer. Needs at least two GPUs (skipped otherwise); the
+ranks are child processes, one per GPU."""
 import os
 import subprocess
 import sys
@@ -21,3 +22,16 @@ def test_peer_exchange_matches_nccl_and_oracle(world):
            "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "tp_worker.py")]
     r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and f"TP_WORKER_OK {world}" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_equals_single_gpu(world):
+    import torch
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29520 + world), os.path.join(ROOT, "tests", "ep_worker.py")]
+    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=1200)
+    assert r.returncode == 0 and f"EP_WORKER_OK {world}" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
