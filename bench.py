@@ -48,6 +48,8 @@ FC1_TRAFFIC_BYTES = {"decode16": 915384064, "prefill8k": 3002103808}
 WORKLOADS = {
     "decode16": dict(tokens=16, zipf=0.0, desc="16-token decode batch, uniform routing (BASELINE configs[1])"),
     "prefill8k": dict(tokens=8192, zipf=0.0, desc="8192-token prefill segment, uniform routing (BASELINE configs[3])"),
+    "prefill64k": dict(tokens=65536, zipf=1.0, desc="65536-token batch, Zipf(1.0) expert popularity (BASELINE configs[4]; "
+                                                     "expert-parallel only: --parallel ep with --gpus 2/4/8)"),
 }
 
 
@@ -328,6 +330,103 @@ def cpu_baseline_for(name, steps_budget_s=20.0):
                        f"{take[0]}..{take[-1]}, {dt:.1f} s; reference CPU expert path (E-FP32), OpenMP over output rows")
 
 
+def run_expert_parallel(name, dev, stream, args, rank, world):
+    """Expert-parallel step (--parallel ep): rank r holds 256 / N experts and owns 1 / N of the tokens; rows are gathered
+    from and results scattered to their owners over NVLink inside the permutation and FC2 kernels."""
+    import torch
+    import torch.distributed as dist
+
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import expert, synth, tp
+
+    wl = WORKLOADS[name]
+    tokens, seed = wl["tokens"], synth.MASTER_SEED
+    n_local = E // world
+    wts = synth.layer_torch(seed, dev, n_experts=n_local, first_expert=rank * n_local)
+    layer = M.Layer.from_checkpoint_ep(*[wts[n] for n in synth.TENSORS], ep_rank=rank, ep_size=world)
+    del wts
+    torch.cuda.empty_cache()
+    scratch = M.Scratch()
+    ep = tp.make_expert_parallel(tokens)
+    lo, hi = tp.shard_tokens(tokens, rank, world)
+    rows = hi - lo
+    ids, w = synth.routing(seed, tokens, wl["zipf"])
+    counts = np.bincount(ids.reshape(-1), minlength=E)
+    per_rank = counts.reshape(world, n_local).sum(1)
+    x_bits = synth.activations_bf16(seed, rows, first_token=lo)
+    xd = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).to(dev)
+    idd, wd = torch.from_numpy(np.ascontiguousarray(ids[lo:hi])).to(dev), torch.from_numpy(np.ascontiguousarray(w[lo:hi])).to(dev)
+    out = torch.empty((rows, H), dtype=torch.int16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        ep.step(layer, scratch, xd, idd, wd, rows, out, stream=stream.cuda_stream)
+
+    def sync_all():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    scratch.status(stream.cuda_stream); ep.status(stream.cuda_stream)
+    sync_all()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    with ClockSampler(dev.index or 0) as clocks:
+        for a, b in ev:
+            flush.fill_(1)
+            a.record(stream); step(); b.record(stream)
+            b.synchronize()
+        sync_all()
+    scratch.status(stream.cuda_stream); ep.status(stream.cuda_stream)
+    t = torch.tensor([float(sum(a.elapsed_time(b) for a, b in ev))], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    value = tokens * args.steps / (total_ms * 1e-3)
+
+    # end to end: this rank's BF16 rows, ids and weights from pinned memory, its BF16 result rows back to pinned memory
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    hx, hi_, hw = pin(x_bits.view(np.int16)), pin(ids[lo:hi]), pin(w[lo:hi])
+    hout = torch.empty((rows, H), dtype=torch.int16).pin_memory()
+
+    def e2e_step():
+        with torch.cuda.stream(stream):
+            xd.copy_(hx, non_blocking=True); idd.copy_(hi_, non_blocking=True); wd.copy_(hw, non_blocking=True)
+            step()
+            hout.copy_(out, non_blocking=True)
+        scratch.status(stream.cuda_stream)
+
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    t = torch.tensor([time.perf_counter() - t0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = tokens * args.steps / float(t.item())
+    ep.status(stream.cuda_stream)
+    sync_all()
+    ep.close()
+    step_s = total_ms / args.steps * 1e-3
+    # the busiest rank bounds the step: its share of the routed rows x FLOP per routed row
+    busiest = float(per_rank.max()) * (FLOP_PER_TOKEN / TOPK)
+    roof = dict(bound="tensor", kernel="whole expert-parallel step on the busiest rank (FC1 + FC2 + gather/scatter over NVLink)",
+                achieved=busiest / step_s / 1e12, peak=MXF8F6F4_PEAK_TFLOPS, unit="TFLOP/s", traffic=None,
+                algorithmic_flops=busiest, peak_source="measured tcgen05 kind::mxf8f6f4 dense rate (profiles/mxf8f6f4_mma_rate.md)")
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    launches = 3 + 2 + 8 * ((tokens + 16383) // 16384) + 1
+    return dict(workload=name, tokens=tokens, active_experts=int((counts > 0).sum()), value=value, ms_per_step=total_ms / args.steps,
+                e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=rows * (H * 2 + TOPK * 8) * world,
+                         d2h_bytes_per_step=rows * H * 2 * world),
+                roofline=roof, clocks=clocks.summary(), gpu_launches=launches * args.steps,
+                whole_step=dict(tflops=FLOP_PER_TOKEN * tokens / step_s / 1e12, tflops_per_gpu=FLOP_PER_TOKEN * tokens / world / step_s / 1e12,
+                                routed_rows_per_rank=[int(v) for v in per_rank],
+                                imbalance=float(per_rank.max() / per_rank.mean()),
+                                nvlink_bytes_in_busiest_rank=int(per_rank.max() * (world - 1) / world * (H + H // 32)),
+                                nvlink_bytes_out_busiest_rank=int(per_rank.max() * (world - 1) / world * H * 4)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -338,6 +437,8 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the 8192-token prefill sub-result")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the ranks' planes are summed (NVLink peer-memory kernel, or NCCL all-gather + sum kernel)")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "ep"],
+                    help="N > 1: tensor parallel over the intermediate dimension (default) or expert parallel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -363,6 +464,26 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
+    if args.parallel == "ep" or args.workload == "prefill64k":
+        if world < 2:
+            raise SystemExit("--parallel ep / prefill64k need --gpus 2, 4 or 8 (launch with torch.distributed.run)")
+        stream = torch.cuda.Stream(device=dev)
+        torch.cuda.set_stream(stream)
+        r = run_expert_parallel(args.workload, dev, stream, args, rank, world)
+        if rank == 0:
+            line = dict(metric="moe_expert_ffn_tokens_per_s_per_layer", value=r["value"], unit="tokens/s", n_gpus=world,
+                        steps=args.steps, warmup=args.warmup, ms_per_step=r["ms_per_step"], higher_is_better=True,
+                        scaling="strong", vs_baseline=None, dtype="e4m3 x e2m1 (mxf8f6f4), f32 accumulate", data="synthetic",
+                        config=dict(workload=args.workload, description=WORKLOADS[args.workload]["desc"], tokens=r["tokens"],
+                                    top_k=TOPK, experts=E, hidden=H, intermediate=I, active_experts=r["active_experts"],
+                                    parallelism=f"ep{world}", l2="flushed between timed iterations",
+                                    input_codec="wire (FP8 E4M3 + UE8M0 K32)"),
+                        e2e=r["e2e"], gpu_launches=r["gpu_launches"], clocks=r["clocks"], roofline=r["roofline"],
+                        whole_step=r["whole_step"], cpu_baseline=None)
+            print(json.dumps(line), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     weights = synth.layer_torch(synth.MASTER_SEED, dev)
     layer = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS], tp_rank=rank, tp_size=world)
     del weights
@@ -398,6 +519,7 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+        dist.destroy_process_group()
         dist.destroy_process_group()
 
 

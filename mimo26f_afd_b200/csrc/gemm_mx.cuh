@@ -82,6 +82,18 @@ struct GemmArgs {
     RouteSinks sinks;
 };
 
+// A work item and its token tile (two dependent global loads at the top of an item in every role; loading the next
+// item's pair one item ahead was tried and changed nothing for short items while costing FC1 3 %).
+struct ItemInfo {
+    WorkItem wi;
+    TokenTile tt;
+};
+__device__ __forceinline__ ItemInfo load_item(const GemmArgs& p, uint32_t it, uint32_t n_items) {
+    ItemInfo r{};
+    if (it < n_items) { r.wi = p.items[it]; r.tt = p.tiles[r.wi.tile]; }
+    return r;
+}
+
 // Row of the FC2 output for a route of the pass.
 __device__ __forceinline__ float* y_row(const GemmArgs& p, int32_t route) {
     if (p.sinks.n == 0) return p.y + size_t(route) * kHidden;
@@ -106,7 +118,7 @@ struct GemmSmem {
     alignas(1024) uint8_t b[STAGES][B_ROWS * 128];
     alignas(16) uint8_t sfa[STAGES][2 * kScaleBlockBytes];
     alignas(16) uint8_t sfb[STAGES][kScaleBlockBytes];
-    uint64_t full[STAGES], empty[STAGES], acc_full, acc_empty;
+    uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -139,18 +151,24 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return __fmul_rn(__fmul_rn(num, r), u);
 }
 
+static_assert(sizeof(GemmSmem<32, 6>) + 1024 <= 232448 && sizeof(GemmSmem<kMaxN, 4>) + 1024 <= 232448,
+              "a CTA has at most 227 KB of shared memory");
+
 template <int MODE, int B_ROWS, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_x, const GemmArgs p) {
     using Smem = GemmSmem<B_ROWS, STAGES>;
+    // Token tiles of at most 64 columns leave room for two accumulator sets in each tile's 128 tensor-memory columns
+    // (set b at column offset b * B_ROWS): the MMAs of item i + 1 start while the epilogue still pulls item i. With items
+    // as short as a rank's K slice under tensor parallelism (2-8 chunks) the hand-over would otherwise be half the time.
+    constexpr uint32_t kAccSets = B_ROWS <= 64 ? 2u : 1u;
     extern __shared__ uint8_t smem_raw[];
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
-        mbar_init(&s.acc_full, 1);
-        mbar_init(&s.acc_empty, kEpiWarps);
+        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], kEpiWarps); }
         s.abort_flag = 0;
         mbar_init_fence();
     }
@@ -174,9 +192,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int i = 0; i < 4; ++i) tma_prefetch_desc(&maps_x.box[i]);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-                const WorkItem wi = p.items[it];
-                const TokenTile tt = p.tiles[wi.tile];
+                        for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
+                const ItemInfo cur = load_item(p, it, n_items);
+                const WorkItem wi = cur.wi;
+                const TokenTile tt = cur.tt;
                 const int w_row = ((tt.expert - p.expert_base) * p.m_tiles + wi.m_tile) * kPairM;
                 const uint8_t* sfa_g = p.sfa + size_t((tt.expert - p.expert_base) * p.m_tiles + wi.m_tile) * p.k_chunks * 2 * kScaleBlockBytes;
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
@@ -214,15 +233,17 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint64_t sfa_desc0 = desc_scale_block(smem_u32(s.sfa[0])), sfb_desc0 = desc_scale_block(smem_u32(s.sfb[0]));
             constexpr uint64_t kAStage = sizeof(s.a[0]) >> 4, kBStage = sizeof(s.b[0]) >> 4;
             constexpr uint64_t kSfaStage = sizeof(s.sfa[0]) >> 4, kSfbStage = sizeof(s.sfb[0]) >> 4;
-            for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
-                const TokenTile tt = p.tiles[p.items[it].tile];
+                        for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
+                const ItemInfo cur = load_item(p, it, n_items);
+                const TokenTile tt = cur.tt;
                 const uint32_t idesc0 = idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), 0, 0);
                 // the accumulators are free once every epilogue warp has pulled its slice of the previous item
                 M26B_T0(ta);
-                if (!mbar_wait(&s.acc_empty, (local & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                const uint32_t aset = local % kAccSets, ause = local / kAccSets;
+                if (!mbar_wait(&s.acc_empty[aset], (ause & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 M26B_ACC(2, ta);
                 tc_fence_after();
-                const uint32_t d0 = tb, d1 = tb + kAcc1;
+                const uint32_t d0 = tb + aset * B_ROWS, d1 = d0 + kAcc1;
                 for (int c = 0; c < p.k_chunks; ++c) {
                     M26B_T0(tf);
                     if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
@@ -248,7 +269,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tc_commit(&s.empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) tc_commit(&s.acc_full);
+                if (ok) tc_commit(&s.acc_full[aset]);
             }
             if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
         }
@@ -259,15 +280,25 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         static_assert(kEpiWarps == 16 && kMaxN == 128, "the register drain below is sized for 4 warps per quadrant");
         uint32_t local = 0;
         bool ok = true;
-        for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
-            const WorkItem wi = p.items[it];
-            const TokenTile tt = p.tiles[wi.tile];
+                for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
+            const ItemInfo cur = load_item(p, it, n_items);
+            const WorkItem wi = cur.wi;
+            const TokenTile tt = cur.tt;
+            // FC2: where this warp's token columns go. Lane l holds the route of token (wq >> 1) * 8 + 16 (l / 8) + l % 8 as
+            // the address of its output row (0 for a padding column), fetched before the accumulators are waited for.
+            unsigned long long row_lo = 0, row_hi = 0;
+            if constexpr (MODE == kModeFc2) {
+                const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
+                if (t < tt.n_valid) row_lo = reinterpret_cast<unsigned long long>(y_row(p, p.original_routes[tt.row_base + t]));
+                if (t + 64 < tt.n_valid) row_hi = reinterpret_cast<unsigned long long>(y_row(p, p.original_routes[tt.row_base + t + 64]));
+            }
             M26B_T0(te);
-            if (!mbar_wait(&s.acc_full, local & 1u, abort_flag)) { ok = false; break; }
+            const uint32_t aset = local % kAccSets, ause = local / kAccSets;
+            if (!mbar_wait(&s.acc_full[aset], ause & 1u, abort_flag)) { ok = false; break; }
             if (warp == 2 && lane == 0) { M26B_ACC(3, te); }
             M26B_T0(tc);
             tc_fence_after();
-            const uint32_t t_acc = tb + ((q * 32u) << 16);
+            const uint32_t t_acc = tb + ((q * 32u) << 16) + aset * B_ROWS;
             if constexpr (MODE == kModeFc2) {
                 // warp (q, wq): weight tile (wq & 1) of the pair, token groups (wq >> 1), +2, +4 ... of 8 tokens;
                 // hidden row = 256 m + 128 tile + 32 q + lane
@@ -281,21 +312,15 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tmem_wait_ld();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&s.acc_empty);
+                if (lane == 0) mbar_arrive(&s.acc_empty[aset]);
                 const uint32_t ycol = uint32_t(wi.m_tile) * kPairM + tile * kTileM + q * 32u + lane;
-                // lane l holds the route of token (wq >> 1) * 8 + 16 (l / 8) + l % 8: one load covers four groups
-                int32_t routes_lo = -1, routes_hi = -1;
-                {
-                    const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
-                    if (t < tt.n_valid) routes_lo = p.original_routes[tt.row_base + t];
-                    if (t + 64 < tt.n_valid) routes_hi = p.original_routes[tt.row_base + t + 64];
-                }
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
+                    if ((int(wq >> 1) + 2 * g) * 8 >= tt.n_mma) break;      // warp-uniform: no columns beyond the tile
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const int32_t route = __shfl_sync(0xffffffffu, g < 4 ? routes_lo : routes_hi, (g & 3) * 8 + j);
-                        if (route >= 0) y_row(p, route)[ycol] = __uint_as_float(r[g][j]);
+                        const unsigned long long row = __shfl_sync(0xffffffffu, g < 4 ? row_lo : row_hi, (g & 3) * 8 + j);
+                        if (row) reinterpret_cast<float*>(row)[ycol] = __uint_as_float(r[g][j]);
                     }
                 }
             } else {
@@ -313,7 +338,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tmem_wait_ld();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&s.acc_empty);
+                if (lane == 0) mbar_arrive(&s.acc_empty[aset]);
                 const int feat0 = wi.m_tile * kTileM + int(q) * 32;
                 uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + wi.m_tile) * kScaleBlockBytes;
                 uint8_t* mq = p.mid_q + size_t(tt.row_base) * p.i_local + feat0 + lane;

@@ -74,9 +74,10 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tma_prefetch_desc(&map_w);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs) {
-                const WorkItem wi = p.items[it];
-                const TokenTile tt = p.tiles[wi.tile];
+                        for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs) {
+                const ItemInfo cur = load_item(p, it, n_items);
+                const WorkItem wi = cur.wi;
+                const TokenTile tt = cur.tt;
                 const int m_tile = wi.m_tile + int(rank);
                 const int w_row = ((tt.expert - p.expert_base) * p.m_tiles + m_tile) * kPairM;
                 const int sfa_row = ((tt.expert - p.expert_base) * p.m_tiles + m_tile) * p.k_chunks * 2;
@@ -116,8 +117,9 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const uint64_t sfa_desc0 = desc_scale_block(smem_u32(s.sfa[0])), sfb_desc0 = desc_scale_block(smem_u32(s.sfb[0]));
             constexpr uint64_t kAStage = sizeof(s.a[0]) >> 4, kBStage = sizeof(s.b[0]) >> 4;
             constexpr uint64_t kSfaStage = sizeof(s.sfa[0]) >> 4, kSfbStage = sizeof(s.sfb[0]) >> 4;
-            for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs, ++local) {
-                const TokenTile tt = p.tiles[p.items[it].tile];
+                        for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs, ++local) {
+                const ItemInfo cur = load_item(p, it, n_items);
+                const TokenTile tt = cur.tt;
                 const uint32_t idesc0 = idesc_mx_pair(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), 0, 0);
                 M26B_T0(ta);
                 if (!mbar_wait(&s.acc_empty, (local & 1u) ^ 1u, abort_flag)) { ok = false; break; }
@@ -157,10 +159,19 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const uint32_t acc_empty_leader = cluster_map(smem_u32(&s.acc_empty), 0);
         uint32_t local = 0;
         bool ok = true;
-        for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs, ++local) {
-            const WorkItem wi = p.items[it];
-            const TokenTile tt = p.tiles[wi.tile];
+                for (uint32_t it = pair_id; it < n_items && ok; it += n_pairs, ++local) {
+            const ItemInfo cur = load_item(p, it, n_items);
+            const WorkItem wi = cur.wi;
+            const TokenTile tt = cur.tt;
             const int m_tile = wi.m_tile + int(rank);
+            // FC2: where this warp's token columns go. Lane l holds the route of token (wq >> 1) * 8 + 16 (l / 8) + l % 8 as
+            // the address of its output row (0 for a padding column), fetched before the accumulators are waited for.
+            unsigned long long row_lo = 0, row_hi = 0;
+            if constexpr (MODE == kModeFc2) {
+                const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
+                if (t < tt.n_valid) row_lo = reinterpret_cast<unsigned long long>(y_row(p, p.original_routes[tt.row_base + t]));
+                if (t + 64 < tt.n_valid) row_hi = reinterpret_cast<unsigned long long>(y_row(p, p.original_routes[tt.row_base + t + 64]));
+            }
             M26B_T0(te);
             if (!mbar_wait(&s.acc_full, local & 1u, abort_flag)) { ok = false; break; }
             if (warp == 2 && lane == 0) { M26B_ACC(3, te); }
@@ -180,18 +191,13 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
                 const uint32_t ycol = uint32_t(m_tile) * kPairM + tile * kTileM + q * 32u + lane;
-                int32_t routes_lo = -1, routes_hi = -1;
-                {
-                    const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
-                    if (t < tt.n_valid) routes_lo = p.original_routes[tt.row_base + t];
-                    if (t + 64 < tt.n_valid) routes_hi = p.original_routes[tt.row_base + t + 64];
-                }
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
+                    if ((int(wq >> 1) + 2 * g) * 8 >= tt.n_mma) break;      // warp-uniform: no columns beyond the tile
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const int32_t route = __shfl_sync(0xffffffffu, g < 4 ? routes_lo : routes_hi, (g & 3) * 8 + j);
-                        if (route >= 0) y_row(p, route)[ycol] = __uint_as_float(r[g][j]);
+                        const unsigned long long row = __shfl_sync(0xffffffffu, g < 4 ? row_lo : row_hi, (g & 3) * 8 + j);
+                        if (row) reinterpret_cast<float*>(row)[ycol] = __uint_as_float(r[g][j]);
                     }
                 }
             } else {

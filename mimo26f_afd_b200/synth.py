@@ -118,17 +118,18 @@ def bf16_to_f32_np(bits: np.ndarray) -> np.ndarray:
     return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
-def normal_np(seed: int, stream: int, n: int) -> np.ndarray:
-    """``n`` N(0,1) float32 values by Box-Muller on the stream's words."""
-    w = words_np(stream_base(seed, 100 + stream), n)
+def normal_np(seed: int, stream: int, n: int, start: int = 0) -> np.ndarray:
+    """Values ``start .. start + n`` of a stream of N(0,1) float32 (Box-Muller on the stream's words)."""
+    w = words_np(stream_base(seed, 100 + stream), n, start)
     u1 = ((w >> _U64(40)).astype(np.float64) + 1.0) / 16777217.0
     u2 = ((w & _U64(0xFFFFFF)).astype(np.float64)) / 16777216.0
     return (np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)).astype(np.float32)
 
 
-def activations_bf16(seed: int, tokens: int) -> np.ndarray:
-    """BF16 activations N(0,1), shape [tokens, 4096], as uint16 bit patterns."""
-    return bf16_rne_np(normal_np(seed, 0, tokens * H)).reshape(tokens, H)
+def activations_bf16(seed: int, tokens: int, first_token: int = 0) -> np.ndarray:
+    """BF16 activations N(0,1) of tokens ``first_token .. first_token + tokens``, shape [tokens, 4096], as uint16 bit
+    patterns. The values of a token do not depend on how the batch is cut."""
+    return bf16_rne_np(normal_np(seed, 0, tokens * H, first_token * H)).reshape(tokens, H)
 
 
 def routing(seed: int, tokens: int, zipf_s: float = 0.0):
