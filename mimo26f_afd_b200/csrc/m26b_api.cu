@@ -679,20 +679,29 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     if (rc) return rc;
     int32_t* const ids_d = S->iw.as<int32_t>();
     float* const w_d = reinterpret_cast<float*>(S->iw.as<uint8_t>() + routes * 4);
-    M26B_CK(cudaMemcpy2DAsync(S->xq.p, kHidden, payload, payload_pitch, kHidden, rows, cudaMemcpyHostToDevice, S->st),
-            "m26b x upload");
-    M26B_CK(cudaMemcpy2DAsync(S->xs.p, kHidden / kBlockK, scales, scales_pitch, kHidden / kBlockK, rows,
-                              cudaMemcpyHostToDevice, S->st), "m26b xs upload");
+    // contiguous rows go up as one linear copy (a pitched copy of the same bytes takes a slower path)
+    if (payload_pitch == kHidden)
+        M26B_CK(cudaMemcpyAsync(S->xq.p, payload, size_t(rows) * kHidden, cudaMemcpyHostToDevice, S->st), "m26b x upload");
+    else
+        M26B_CK(cudaMemcpy2DAsync(S->xq.p, kHidden, payload, payload_pitch, kHidden, rows, cudaMemcpyHostToDevice, S->st),
+                "m26b x upload");
+    if (scales_pitch == kHidden / kBlockK)
+        M26B_CK(cudaMemcpyAsync(S->xs.p, scales, size_t(rows) * (kHidden / kBlockK), cudaMemcpyHostToDevice, S->st), "m26b xs upload");
+    else
+        M26B_CK(cudaMemcpy2DAsync(S->xs.p, kHidden / kBlockK, scales, scales_pitch, kHidden / kBlockK, rows,
+                                  cudaMemcpyHostToDevice, S->st), "m26b xs upload");
     S->hiw.resize(routes * 8);
     std::memcpy(S->hiw.data(), ids, routes * 4);
     std::memcpy(S->hiw.data() + routes * 4, weights, routes * 4);
     M26B_CK(cudaMemcpyAsync(S->iw.p, S->hiw.data(), routes * 8, cudaMemcpyHostToDevice, S->st), "m26b ids/w upload");
     uint16_t* const out_d = S->gather.as<uint16_t>();
+    // stage timings cost four events between the kernels (and the overlap of dependent launches): only when asked for
+    const bool timed = ms != nullptr && passes == 1;
     for (uint32_t ps = 0; ps < passes; ++ps) {
         const uint32_t r0 = ps * kMaxPassRows, n = rows - r0 < kMaxPassRows ? rows - r0 : kMaxPassRows;
         rc = enqueue_pass(L, S, S->xq.as<uint8_t>() + size_t(r0) * kHidden, S->xs.as<uint8_t>() + size_t(r0) * (kHidden / kBlockK),
                           ids_d + size_t(r0) * kTopK, w_d + size_t(r0) * kTopK, n, out_d + size_t(r0) * kHidden,
-                          S->partial.as<float>(), S->status.as<Status>() + ps, S->st, passes == 1, err, errlen);
+                          S->partial.as<float>(), S->status.as<Status>() + ps, S->st, timed, err, errlen);
         if (rc) return rc;
     }
     M26B_CK(cudaMemcpyAsync(bf16_out, out_d, size_t(rows) * kHidden * 2, cudaMemcpyDeviceToHost, S->st), "m26b bf16 download");
@@ -706,7 +715,7 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     const auto t2 = std::chrono::steady_clock::now();
     if (ms) {
         float gpu_ms = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-        if (passes == 1) {
+        if (timed) {
             cudaEventElapsedTime(&gpu_ms, S->e0, S->e1);
             cudaEventElapsedTime(&p1, S->e0, S->ea);
             cudaEventElapsedTime(&p2, S->ea, S->ec);

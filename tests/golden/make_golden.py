@@ -2,7 +2,7 @@
 
 Run in the development container, where the reference tree is mounted:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [REFERENCE_TREE]
 
 Imports (never copies) from the reference tree:
   oracle/lattice/quant_v1.py                     codec of record e4m3fn-k32-v1
