@@ -407,6 +407,73 @@ def test_small_request_prologue_input_forms_agree(layer, scratch, dev, oracle_mo
     run_dev(layer, scratch, dev, x_bits, ids, w)              # usable afterwards
 
 
+def test_wrong_nibble_order_is_visible_and_outputs_stay_inside_their_rows(layer, scratch, dev, oracle_mod):
+    """Two negatives on the whole path. (1) Against an oracle fed nibble-swapped weights (high nibble = even k, the
+    naive order) the result is nowhere near the tolerance, so the parity tests do see the nibble order. (2) Poisoned
+    guard rows after both output planes are untouched."""
+    import torch
+
+    from mimo26f_afd_b200 import expert, synth
+
+    tokens = 5
+    x_bits = synth.activations_bf16(SEED + 9, tokens)
+    ids, w = synth.routing(SEED + 9, tokens, 0.0)
+    out = torch.full((tokens + 2, H), 0x7FC1, dtype=torch.int16, device=dev)
+    part = torch.full((tokens + 2, H), float("nan"), dtype=torch.float32, device=dev)
+    expert.ffn_dev(layer, scratch, to_dev(x_bits, dev), to_dev(ids, dev), to_dev(w, dev), tokens, out, partial_out=part)
+    scratch.status()
+    assert (out[tokens:].cpu().numpy() == 0x7FC1).all() and np.isnan(part[tokens:].cpu().numpy()).all()
+    got = part[:tokens].cpu().numpy()
+    assert np.isfinite(got).all()
+    xq, xs = oracle_mod.quant_wire(synth.bf16_to_f32_np(x_bits))
+    tensors = synth.layer_np(SEED, np.unique(ids))
+    good = oracle_mod.ffn_layer(tensors, xq, xs, ids, w)
+    assert rel_l2(got, good["partial"]) <= 1e-3
+    swap = lambda a: ((a >> 4) | (a << 4)).astype(np.uint8)
+    naive = {k: (swap(v) if k.endswith("_w") else v) for k, v in tensors.items()}     # payload tensors end in _w
+    bad = oracle_mod.ffn_layer(naive, xq, xs, ids, w)
+    assert bad["rc"] == 0 and rel_l2(got, bad["partial"]) > 0.5
+
+
+def test_exchange_sum_is_rank_ordered_in_all_24_arrival_orders(dev, oracle_mod):
+    """Four ranks' windows in this process; the planes are written and published in every one of the 24 orders (the
+    reference's coordinator test walks the same 24 arrival orders, crates/mimo26-wire/tests/r8_rank_order.rs); the sum
+    must be the rank-ordered one every time. The planes are chosen so that every other order of additions differs."""
+    import itertools
+
+    import torch
+
+    import mimo26f_afd_b200 as M
+
+    n = 4096
+    vals = np.array([2.0 ** 24, 1.0, -(2.0 ** 24), 1.0], np.float32)       # rank order: ((2^24 + 1) - 2^24) + 1 = 1
+    planes = np.repeat((vals.view(np.uint32) >> 16).astype(np.uint16)[:, None], n, axis=1)
+    rng = np.random.default_rng(5)
+    planes[:, 1:] = (rng.standard_normal((4, n - 1)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    want = oracle_mod.rank_sum(planes)
+    assert want[0] == 1.0
+    ex = [M.Exchange(n * 2, r, 4, export=False) for r in range(4)]
+    for e in ex:
+        e.connect_local(ex)
+    out = torch.empty(n, dtype=torch.float32, device=dev)
+    for order in itertools.permutations(range(4)):
+        for r in order:
+            torch.as_tensor(_DevView(ex[r].plane(), n, "<i2"), device=dev).copy_(to_dev(planes[r], dev))
+            if r != 0:
+                ex[0].publish_as(r)
+        ex[0].sum(n, out)
+        ex[0].status()
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32)), order
+        for r in range(1, 4):                               # the other ranks take the same step (their sums are not read)
+            for q in range(4):
+                if q != r:
+                    ex[r].publish_as(q)
+            ex[r].sum(n, torch.empty(n, dtype=torch.float32, device=dev))
+            ex[r].status()
+    for e in ex:
+        e.close()
+
+
 def test_tp4_from_canonical_image_matches_reference_slices(weights, dev, oracle_mod):
     """m26b_layer_new on the reference's canonical-v2 TP4 rank images: each rank's partial equals the oracle's
     rank slice, and the rank-ordered sum of the four BF16 planes equals the oracle's wire result bit for bit
