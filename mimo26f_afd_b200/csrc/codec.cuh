@@ -100,7 +100,8 @@ __device__ __forceinline__ uint32_t wire_scale_byte(uint32_t amax_bits) {
     const int s = k + 127;
     return uint32_t(s < 0 ? 0 : s > 254 ? 254 : s);
 }
-__device__ __forceinline__ uint32_t wire_payload(uint32_t bits, uint32_t scale_byte) {
+// Integer form, valid for every scale byte.
+__device__ __forceinline__ uint32_t wire_payload_exact(uint32_t bits, uint32_t scale_byte) {
     const uint32_t mag = bits & 0x7fffffffu;
     if (!mag || mag > 0x7f800000u) return 0u;          // +-0 and NaN encode to code 0, sign clear
     const uint32_t sign = (bits >> 24) & 0x80u;
@@ -108,6 +109,25 @@ __device__ __forceinline__ uint32_t wire_payload(uint32_t bits, uint32_t scale_b
     uint32_t sig; int exp;
     split_f32(mag, sig, exp);
     return sign | e4m3_mag_code<false>(sig, exp + 127 - int(scale_byte));
+}
+// The same code through the FP32 pipeline, for scale bytes 1..253 (every block with a finite nonzero maximum):
+// |x| * 2^(127 - s) is a power-of-two scaling, exact unless it underflows, which only happens far below the 2^-10
+// rounding threshold. At or above 2^-6 the grid keeps four significant bits: adding half of the dropped field to the
+// bit pattern and truncating is round-half-away, and the carry walks into the exponent by itself. Below, the grid is the
+// fixed quantum 2^-9: floor(512 a + 1/2), with the add rounded toward zero so that a sum just under an integer is not
+// rounded up to it.
+__device__ __forceinline__ uint32_t wire_payload(uint32_t bits, uint32_t scale_byte) {
+    if (scale_byte - 1u > 252u) return wire_payload_exact(bits, scale_byte);
+    const uint32_t mag = bits & 0x7fffffffu;
+    if (!mag || mag > 0x7f800000u) return 0u;
+    const uint32_t sign = (bits >> 24) & 0x80u;
+    if (mag == 0x7f800000u) return sign | 0x7eu;
+    const float a = __fmul_rn(__uint_as_float(mag), __uint_as_float((254u - scale_byte) << 23));
+    const uint32_t sub = __float2uint_rz(__fadd_rz(__fmul_rn(a, 512.0f), 0.5f));      // 0..8; 8 is the smallest normal's code
+    const uint32_t ab = __float_as_uint(a);
+    uint32_t nrm = ((ab + 0x80000u) >> 20) - 960u;
+    nrm = nrm > 0x7eu ? 0x7eu : nrm;
+    return sign | (a < 0.015625f ? sub : nrm);
 }
 
 // ---- BF16 ---------------------------------------------------------------------

@@ -11,8 +11,8 @@
 namespace m26b {
 
 // ---------------------------------------------------------------- quantisers
-// One K32 block = four threads of eight elements (16-byte loads for BF16,
-// 2 x 16 bytes for FP32); the block maximum crosses the four lanes by shuffle.
+// One K32 block = two threads of sixteen elements (2 x 16-byte loads for BF16, 4 x 16 bytes for FP32, one 16-byte
+// store); the block maximum crosses the two lanes by shuffle.
 // CODEC 0: wire codec (scale byte 0 for a zero block, ties away from zero).
 // CODEC 1: quant_v1 (floor 1e-4, ties to even, faults instead of clipping; a
 // faulting block writes nothing), crates/mimo26-expert/kernels/b1/quant_v1.cu:34-59.
@@ -21,44 +21,46 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const IN* __restrict
                                                             uint8_t* __restrict__ payload,
                                                             uint8_t* __restrict__ scales,
                                                             uint32_t* __restrict__ fault) {
-    const uint64_t n8 = n_elems / 8;
+    const uint64_t n16 = n_elems / 16;
     uint32_t bad = 0;
     // the bound is rounded up to a whole warp so every lane reaches the shuffles
-    for (uint64_t g = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < ((n8 + 31) & ~uint64_t(31));
+    for (uint64_t g = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < ((n16 + 31) & ~uint64_t(31));
          g += uint64_t(gridDim.x) * blockDim.x) {
-        uint32_t bits[8];
-        const bool live = g < n8;
+        uint32_t bits[16];
+        const bool live = g < n16;
         if (live) {
             if constexpr (sizeof(IN) == 2) {
-                const uint4 v = reinterpret_cast<const uint4*>(x)[g];
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) { bits[2 * i] = w[i] << 16; bits[2 * i + 1] = w[i] & 0xffff0000u; }
-            } else {
                 const uint4 a = reinterpret_cast<const uint4*>(x)[2 * g], b = reinterpret_cast<const uint4*>(x)[2 * g + 1];
-                bits[0] = a.x; bits[1] = a.y; bits[2] = a.z; bits[3] = a.w;
-                bits[4] = b.x; bits[5] = b.y; bits[6] = b.z; bits[7] = b.w;
+                const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { bits[2 * i] = w[i] << 16; bits[2 * i + 1] = w[i] & 0xffff0000u; }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 a = reinterpret_cast<const uint4*>(x)[4 * g + i];
+                    bits[4 * i] = a.x; bits[4 * i + 1] = a.y; bits[4 * i + 2] = a.z; bits[4 * i + 3] = a.w;
+                }
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) bits[i] = 0;
+            for (int i = 0; i < 16; ++i) bits[i] = 0;
         }
         uint32_t amax = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 16; ++i) {
             uint32_t m = bits[i] & 0x7fffffffu;
             if (CODEC == 0 && m > 0x7f800000u) m = 0;   // the wire codec's maximum skips NaN
             amax = m > amax ? m : amax;
         }
-        uint32_t o = __shfl_xor_sync(0xffffffffu, amax, 1); amax = o > amax ? o : amax;
-        o = __shfl_xor_sync(0xffffffffu, amax, 2); amax = o > amax ? o : amax;
-        uint32_t code[8];
+        const uint32_t o = __shfl_xor_sync(0xffffffffu, amax, 1);
+        amax = o > amax ? o : amax;
+        uint32_t code[16];
         uint32_t sbyte;
         bool write = live;
         if constexpr (CODEC == 0) {
             sbyte = wire_scale_byte(amax);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) code[i] = wire_payload(bits[i], sbyte);
+            for (int i = 0; i < 16; ++i) code[i] = wire_payload(bits[i], sbyte);
         } else {
             bool over = false;
             if (amax >= 0x7f800000u) {
@@ -66,24 +68,25 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const IN* __restrict
                 write = false;
                 sbyte = 0;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) code[i] = 0;
+                for (int i = 0; i < 16; ++i) code[i] = 0;
             } else {
                 const int k = quant_v1_scale_exp(amax);
                 sbyte = uint32_t(k + 127);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { code[i] = quant_v1_payload(bits[i], k); over |= !quant_v1_finite(code[i], k); }
+                for (int i = 0; i < 16; ++i) { code[i] = quant_v1_payload(bits[i], k); over |= !quant_v1_finite(code[i], k); }
             }
             uint32_t ov = over ? 1u : 0u;
             ov |= __shfl_xor_sync(0xffffffffu, ov, 1);
-            ov |= __shfl_xor_sync(0xffffffffu, ov, 2);
             if (ov) { if (live) bad |= kFaultQuantOverflow; write = false; }
         }
         if (write) {
-            uint2 out;
+            uint4 out;
             out.x = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
             out.y = code[4] | (code[5] << 8) | (code[6] << 16) | (code[7] << 24);
-            reinterpret_cast<uint2*>(payload)[g] = out;
-            if ((g & 3) == 0) scales[g >> 2] = uint8_t(sbyte);
+            out.z = code[8] | (code[9] << 8) | (code[10] << 16) | (code[11] << 24);
+            out.w = code[12] | (code[13] << 8) | (code[14] << 16) | (code[15] << 24);
+            reinterpret_cast<uint4*>(payload)[g] = out;
+            if ((g & 1) == 0) scales[g >> 1] = uint8_t(sbyte);
         }
     }
     if (bad) atomicOr(fault, bad);

@@ -738,7 +738,7 @@ int m26b_quantize_dev(const void* x, int x_dtype, uint64_t n_elems, int codec, u
     }
     if (!n_elems) return 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const uint64_t threads = n_elems / 8;
+    const uint64_t threads = n_elems / 16;
     const uint32_t blocks = uint32_t((threads + 255) / 256 < 148 * 64 ? (threads + 255) / 256 : 148 * 64);
     if (x_dtype == 0 && codec == 0) quantize_rows_kernel<0, uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);
     else if (x_dtype == 0) quantize_rows_kernel<1, uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);

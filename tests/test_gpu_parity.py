@@ -123,6 +123,41 @@ def test_quantisers_bf16_input_and_ragged_sizes(dev, oracle_mod, codec):
         assert np.array_equal(p.cpu().numpy(), wp.reshape(-1)) and np.array_equal(s.cpu().numpy(), ws.reshape(-1))
 
 
+def test_wire_quantiser_wide_dynamic_range_and_ties(dev, oracle_mod):
+    """The wire codec over the whole FP32 range: block maxima from 2^-140 to 2^120, elements down to 2^-60 of their
+    block's maximum, exact ties and their neighbours at every grid point, signed zeros, infinities and NaN."""
+    import torch
+
+    from mimo26f_afd_b200 import expert
+
+    rng = np.random.default_rng(17)
+    n_blocks = 8192
+    exp = rng.integers(-140, 121, size=(n_blocks, 1)).astype(np.float64)
+    rel = rng.integers(-60, 1, size=(n_blocks, 32)).astype(np.float64)
+    mant = 1.0 + rng.integers(0, 1 << 23, size=(n_blocks, 32)) / float(1 << 23)
+    sign = np.where(rng.integers(0, 2, size=(n_blocks, 32)) == 1, -1.0, 1.0)
+    with np.errstate(over="ignore", under="ignore"):
+        x = (sign * mant * np.exp2(exp + rel)).astype(np.float32)
+    # ties: (m + 1/2) quanta of the E4M3 grid, and one FP32 ulp either side, scaled into each block
+    grid = np.array([(8 + m + 0.5) / 8.0 * 2.0 ** e for e in range(-6, 9) for m in range(8)] + [(m + 0.5) * 2.0 ** -9 for m in range(8)])
+    for b in range(0, 2048):
+        s = 2.0 ** int(exp[b, 0])
+        t = np.float32(grid[b % grid.size] * s / 256.0)
+        x[b, 1:4] = [np.nextafter(t, np.float32(0)), t, np.nextafter(t, np.float32(np.inf))]
+        x[b, 0] = np.float32(256.0 * s / 256.0 * 1.75)
+    x[4000, 5], x[4001, 6], x[4002, 7], x[4003, :] = np.inf, -np.inf, np.nan, 0.0
+    x[4004, 3] = -0.0
+    want_p, want_s = oracle_mod.quant_wire(x)
+    xd = torch.from_numpy(x).to(dev)
+    p = torch.empty(x.size, dtype=torch.uint8, device=dev)
+    s_ = torch.empty(x.size // 32, dtype=torch.uint8, device=dev)
+    fault = torch.zeros(1, dtype=torch.int32, device=dev)
+    expert.quantize_dev(xd, expert.X_F32, x.size, expert.CODEC_WIRE, p, s_, fault)
+    torch.cuda.synchronize()
+    assert np.array_equal(s_.cpu().numpy(), want_s.reshape(-1))
+    assert np.array_equal(p.cpu().numpy(), want_p.reshape(-1))
+
+
 def test_quant_v1_faults_write_nothing(dev):
     import torch
 
