@@ -141,6 +141,17 @@ int m26b_route_reduce_dev(const float* y, const float* weights, uint32_t rows, f
 int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
                       size_t errlen);
 
+/* The caller's producer step, on device pointers: the router's selection from FP32 logits
+ * (crates/mimo26-coordinator/src/router.rs:42-80 router_from_logits, kernels/glue.cu:72-126 router_topk_kernel:
+ * FP64 sigmoid, top 8 of 256 by score + bias with ties to the lower id, weights = unbiased scores normalised in
+ * selection order) and, when x is not NULL, the activation quantiser of m26b_quantize_dev on x [rows,4096], both in
+ * ONE launch. logits [rows,256] FP32; bias [256] FP32 or NULL; ids_out / weights_out [rows,8] are what m26b_ffn_dev
+ * takes. Indices equal the reference's; a weight may differ from a host libm evaluation in its last FP32 bit (the
+ * device's FP64 exp is not correctly rounded). */
+int m26b_produce_dev(const float* logits, const float* bias, uint32_t rows, int32_t* ids_out, float* weights_out, const void* x,
+                     int x_dtype, int codec, uint8_t* payload, uint8_t* scales, uint32_t* fault_dev, void* stream, char* err,
+                     size_t errlen);
+
 /* Plane exchange between the GPUs of one NVLink box, one process per GPU: replaces the return path + coordinator
  * sum of the reference (crates/mimo26-wire/src/l4.rs:169-244 collects the four ranks' BF16 planes over RDMA,
  * crates/mimo26-coordinator/kernels/glue.cu:202-213 adds them in rank order) when the ranks are GPUs that can map

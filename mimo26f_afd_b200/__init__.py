@@ -17,6 +17,7 @@ from .expert import (  # noqa: F401
     ffn_dev,
     ffn_strided,
     plan_static,
+    produce_dev,
     quantize_dev,
     rank_sum_dev,
     route_reduce_dev,

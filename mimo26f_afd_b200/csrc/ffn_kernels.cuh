@@ -17,15 +17,13 @@ namespace m26b {
 // CODEC 1: quant_v1 (floor 1e-4, ties to even, faults instead of clipping; a
 // faulting block writes nothing), crates/mimo26-expert/kernels/b1/quant_v1.cu:34-59.
 template <int CODEC, typename IN>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const IN* __restrict__ x, uint64_t n_elems,
-                                                            uint8_t* __restrict__ payload,
-                                                            uint8_t* __restrict__ scales,
-                                                            uint32_t* __restrict__ fault) {
+__device__ __forceinline__ void quantize_span(const IN* __restrict__ x, uint64_t n_elems, uint8_t* __restrict__ payload,
+                                              uint8_t* __restrict__ scales, uint32_t* __restrict__ fault, uint64_t first,
+                                              uint64_t stride) {
     const uint64_t n16 = n_elems / 16;
     uint32_t bad = 0;
     // the bound is rounded up to a whole warp so every lane reaches the shuffles
-    for (uint64_t g = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < ((n16 + 31) & ~uint64_t(31));
-         g += uint64_t(gridDim.x) * blockDim.x) {
+    for (uint64_t g = first; g < ((n16 + 31) & ~uint64_t(31)); g += stride) {
         uint32_t bits[16];
         const bool live = g < n16;
         if (live) {
@@ -90,6 +88,82 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const IN* __restrict
         }
     }
     if (bad) atomicOr(fault, bad);
+}
+template <int CODEC, typename IN>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const IN* __restrict__ x, uint64_t n_elems,
+                                                            uint8_t* __restrict__ payload,
+                                                            uint8_t* __restrict__ scales,
+                                                            uint32_t* __restrict__ fault) {
+    quantize_span<CODEC, IN>(x, n_elems, payload, scales, fault, uint64_t(blockIdx.x) * blockDim.x + threadIdx.x,
+                             uint64_t(gridDim.x) * blockDim.x);
+}
+
+// ---------------------------------------------------------------- router (the caller's step before the plan)
+// crates/mimo26-coordinator/src/router.rs:42-80 and kernels/glue.cu:72-126: FP64 sigmoid of the FP32 logits, the
+// top 8 of 256 experts by score + bias (descending, a tie to the lower expert id), weights = unbiased scores over
+// their sum taken in selection order, all in FP64, stored as FP32. One warp per token: lane l holds experts
+// l, l + 32, ..., l + 224, so a lane's candidates are in ascending id order and a strict comparison keeps the lower id.
+__device__ __forceinline__ void router_topk_warp(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                 uint32_t lane, int32_t* __restrict__ ids_out, float* __restrict__ w_out) {
+    double score[8], sel[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = int(lane) + 32 * i;
+        score[i] = 1.0 / (1.0 + exp(-double(logits[e])));
+        sel[i] = score[i] + (bias ? double(bias[e]) : 0.0);
+    }
+    uint32_t taken = 0;
+    double wsum = 0.0, mine_score = 0.0;
+    int32_t mine_id = 0;
+#pragma unroll 1
+    for (int k = 0; k < kTopK; ++k) {
+        double bv = 0.0;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (!((taken >> i) & 1u) && (bi == 0x7fffffff || sel[i] > bv)) { bv = sel[i]; bi = int(lane) + 32 * i; }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const double ov = __shfl_xor_sync(0xffffffffu, bv, d);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        double sc = 0.0;
+        if ((uint32_t(bi) & 31u) == lane) {
+            const int slot = bi >> 5;
+            taken |= 1u << slot;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (i == slot) sc = score[i];
+        }
+        sc = __shfl_sync(0xffffffffu, sc, bi & 31);
+        wsum += sc;
+        if (int(lane) == k) { mine_id = bi; mine_score = sc; }
+    }
+    if (lane < uint32_t(kTopK)) {
+        ids_out[lane] = mine_id;
+        w_out[lane] = float(mine_score / wsum);
+    }
+}
+
+// The caller's two steps in front of the path in one launch: the first `router_ctas` CTAs route (8 tokens each, one
+// warp per token), the others quantise the hidden rows. n_elems = 0: routing only.
+template <int CODEC, typename IN>
+__global__ void __launch_bounds__(256) produce_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                      uint32_t rows, uint32_t router_ctas, int32_t* __restrict__ ids_out,
+                                                      float* __restrict__ w_out, const IN* __restrict__ x, uint64_t n_elems,
+                                                      uint8_t* __restrict__ payload, uint8_t* __restrict__ scales,
+                                                      uint32_t* __restrict__ fault) {
+    if (blockIdx.x < router_ctas) {
+        const uint32_t token = blockIdx.x * 8u + (threadIdx.x >> 5);
+        if (token < rows)
+            router_topk_warp(logits + size_t(token) * kExperts, bias, threadIdx.x & 31u, ids_out + size_t(token) * kTopK,
+                             w_out + size_t(token) * kTopK);
+        return;
+    }
+    if (n_elems)
+        quantize_span<CODEC, IN>(x, n_elems, payload, scales, fault, uint64_t(blockIdx.x - router_ctas) * blockDim.x + threadIdx.x,
+                                 uint64_t(gridDim.x - router_ctas) * blockDim.x);
 }
 
 // ---------------------------------------------------------------- route plan

@@ -749,6 +749,39 @@ int m26b_quantize_dev(const void* x, int x_dtype, uint64_t n_elems, int codec, u
     return 0;
 }
 
+// Router top-8 and (optionally) the activation quantiser in one launch.
+int m26b_produce_dev(const float* logits, const float* bias, uint32_t rows, int32_t* ids_out, float* weights_out, const void* x,
+                     int x_dtype, int codec, uint8_t* payload, uint8_t* scales, uint32_t* fault_dev, void* stream, char* err,
+                     size_t errlen) {
+    const bool quant = x != nullptr;
+    if (!logits || !ids_out || !weights_out || !rows ||
+        (quant && (!payload || !scales || !fault_dev || x_dtype < 0 || x_dtype > 1 || codec < 0 || codec > 1))) {
+        set_msg(err, errlen, "m26b produce: bad arguments");
+        return 1;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t router_ctas = (rows + 7u) / 8u;
+    const uint64_t n_elems = quant ? uint64_t(rows) * kHidden : 0;
+    const uint64_t threads = n_elems / 16;
+    const uint32_t qctas = quant ? uint32_t((threads + 255) / 256 < 148 * 64 ? (threads + 255) / 256 : 148 * 64) : 0u;
+    const uint32_t grid = router_ctas + qctas;
+    if (!quant || (x_dtype == 0 && codec == 0))
+        produce_kernel<0, uint16_t><<<grid, 256, 0, st>>>(logits, bias, rows, router_ctas, ids_out, weights_out,
+                                                           static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);
+    else if (x_dtype == 0)
+        produce_kernel<1, uint16_t><<<grid, 256, 0, st>>>(logits, bias, rows, router_ctas, ids_out, weights_out,
+                                                           static_cast<const uint16_t*>(x), n_elems, payload, scales, fault_dev);
+    else if (codec == 0)
+        produce_kernel<0, float><<<grid, 256, 0, st>>>(logits, bias, rows, router_ctas, ids_out, weights_out,
+                                                        static_cast<const float*>(x), n_elems, payload, scales, fault_dev);
+    else
+        produce_kernel<1, float><<<grid, 256, 0, st>>>(logits, bias, rows, router_ctas, ids_out, weights_out,
+                                                        static_cast<const float*>(x), n_elems, payload, scales, fault_dev);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, errlen, "m26b produce launch", e); return 2; }
+    return 0;
+}
+
 int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtype, const uint8_t* x_scales, int codec,
                  const int32_t* ids, const float* weights, uint32_t rows, uint16_t* bf16_out, float* partial_out,
                  void* stream, char* err, size_t errlen) {

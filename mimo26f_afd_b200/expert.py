@@ -220,6 +220,15 @@ def quantize_dev(x, x_dtype: int, n_elems: int, codec: int, payload, scales, fau
                                            _ptr(stream), err, 256), err)
 
 
+def produce_dev(logits, bias, rows: int, ids_out, weights_out, x=None, x_dtype: int = X_BF16, codec: int = CODEC_WIRE,
+                payload=None, scales=None, fault=None, stream=None) -> None:
+    """Router top-8 from FP32 logits [rows, 256] (router.rs:42-80) and, when ``x`` is given, the activation quantiser,
+    in one launch. Outputs are what ``ffn_dev`` takes."""
+    err = C.create_string_buffer(256)
+    _check(_native.lib().m26b_produce_dev(_ptr(logits), _ptr(bias), rows, _ptr(ids_out), _ptr(weights_out), _ptr(x), x_dtype,
+                                          codec, _ptr(payload), _ptr(scales), _ptr(fault), _ptr(stream), err, 256), err)
+
+
 def route_reduce_dev(y, weights, rows: int, partial, bf16, fault, stream=None) -> None:
     err = C.create_string_buffer(256)
     _check(_native.lib().m26b_route_reduce_dev(_ptr(y), _ptr(weights), rows, _ptr(partial), _ptr(bf16), _ptr(fault),

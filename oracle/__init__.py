@@ -51,6 +51,8 @@ def lib() -> C.CDLL:
         L.orc_route_reduce_h.argtypes = [p, p, C.c_uint32, C.c_uint32, p, p]
         L.orc_rank_sum.argtypes = [p, C.c_uint32, C.c_uint64, p]
         L.orc_rank_sum.restype = None
+        L.orc_router_from_logits.argtypes = [p, p, C.c_uint32, C.c_uint32, C.c_uint32, p, p]
+        L.orc_router_from_logits.restype = None
         L.orc_ffn_layer.argtypes = [p] * 6 + [C.c_uint32, C.c_uint32, p, p, p, p, C.c_uint32, p, p, p, p, p, p]
         L.orc_cpu_path.argtypes = [p] * 10 + [C.c_uint32, C.c_uint32, C.c_uint32, p, p]
         L.orc_cpu_path.restype = C.c_uint32
@@ -165,6 +167,17 @@ def rank_sum(planes):
     out = np.empty(planes.shape[1:], np.float32)
     lib().orc_rank_sum(_p(planes), g, n, _p(out))
     return out
+
+
+def router_from_logits(logits, bias, top_k=8):
+    """crates/mimo26-coordinator/src/router.rs:42-80: (indices int32 [T, top_k], weights float32 [T, top_k])."""
+    logits = _a(logits, np.float32)
+    t, e = logits.shape
+    b = None if bias is None else _a(bias, np.float32)
+    idx = np.empty((t, top_k), np.int32)
+    w = np.empty((t, top_k), np.float32)
+    lib().orc_router_from_logits(_p(logits), None if b is None else _p(b), t, e, top_k, _p(idx), _p(w))
+    return idx, w
 
 
 def ffn_layer(tensors, xq, xs, ids, weights, tp_rank=0, tp_size=1, stages=False):

@@ -350,6 +350,40 @@ void orc_rank_sum(const uint16_t* planes, uint32_t n_ranks, uint64_t n, float* o
     }
 }
 
+/* ---- router (the caller's step before the path) ---------------------------------------------
+ * crates/mimo26-coordinator/src/router.rs:42-80 (router_from_logits), Python twin
+ * oracle/mimo26/nn/layers.py::router: FP64 sigmoid of the FP32 logits; the top_k experts by
+ * score + bias, descending, a tie going to the lower expert id (stable sort over ascending ids);
+ * weights = unbiased scores over their sum, the sum taken in selection order, in FP64, then FP32. */
+void orc_router_from_logits(const float* logits, const float* bias, uint32_t rows, uint32_t n_experts, uint32_t top_k,
+                            int32_t* idx_out, float* w_out) {
+    double* score = (double*)malloc(sizeof(double) * n_experts);
+    double* sel = (double*)malloc(sizeof(double) * n_experts);
+    for (uint32_t r = 0; r < rows; ++r) {
+        for (uint32_t e = 0; e < n_experts; ++e) {
+            const double s = (double)logits[(size_t)r * n_experts + e];
+            score[e] = 1.0 / (1.0 + exp(-s));
+            sel[e] = score[e] + (bias ? (double)bias[e] : 0.0);
+        }
+        double wsum = 0.0;
+        for (uint32_t k = 0; k < top_k; ++k) {          /* k-th pass of a stable descending selection */
+            uint32_t best = 0;
+            int have = 0;
+            for (uint32_t e = 0; e < n_experts; ++e) {
+                if (isnan(sel[e])) continue;             /* taken */
+                if (!have || sel[e] > sel[best]) { best = e; have = 1; }
+            }
+            idx_out[(size_t)r * top_k + k] = (int32_t)best;
+            wsum += score[best];
+            sel[best] = NAN;
+        }
+        for (uint32_t k = 0; k < top_k; ++k)
+            w_out[(size_t)r * top_k + k] = (float)(score[idx_out[(size_t)r * top_k + k]] / wsum);
+    }
+    free(score);
+    free(sel);
+}
+
 /* ---- one layer on one rank ------------------------------------------------------------------
  * The reference's rank FFN (crates/mimo26-spark/kernels/b1_serve.cu:312-572) on
  * the lattice above: plan, per-expert FFN on the expert's rows in stable

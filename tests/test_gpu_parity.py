@@ -158,6 +158,49 @@ def test_wire_quantiser_wide_dynamic_range_and_ties(dev, oracle_mod):
     assert np.array_equal(p.cpu().numpy(), want_p.reshape(-1))
 
 
+def test_producer_router_and_quantiser_in_one_launch(dev, oracle_mod):
+    """Router top-8 from FP32 logits against the oracle (indices exact, weights within one FP32 ulp: the device's FP64
+    exp is not correctly rounded) on the reference-generated fixture and on a larger seeded batch with ties; the
+    quantiser half of the same launch writes the bytes the stand-alone quantiser writes."""
+    import os
+
+    import torch
+
+    from mimo26f_afd_b200 import expert, synth
+
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "router_vectors.npz"))
+    cases = [(g["logits_bits"].view(np.float32), g["bias_bits"].view(np.float32), g["idx"], g["weight_bits"].view(np.float32))]
+    rng = np.random.default_rng(23)
+    big = (rng.standard_normal((1000, 256)) * 1.5).astype(np.float32)
+    big[5] = 0.0                                              # a 256-way tie
+    big[6, 10:20] = big[6, 30]                                # ties inside a row
+    bias = (rng.standard_normal(256) * 0.05).astype(np.float32)
+    cases.append((big, bias, *oracle_mod.router_from_logits(big, bias)))
+    cases.append((big, None, *oracle_mod.router_from_logits(big, None)))
+    for logits, b, want_idx, want_w in cases:
+        t = logits.shape[0]
+        x_bits = synth.activations_bf16(SEED + 11, t)
+        ids = torch.empty((t, TOPK), dtype=torch.int32, device=dev)
+        w = torch.empty((t, TOPK), dtype=torch.float32, device=dev)
+        p = torch.empty((t, H), dtype=torch.uint8, device=dev)
+        s_ = torch.empty((t, H // 32), dtype=torch.uint8, device=dev)
+        fault = torch.zeros(1, dtype=torch.int32, device=dev)
+        expert.produce_dev(to_dev(logits, dev), None if b is None else to_dev(b, dev), t, ids, w, x=to_dev(x_bits, dev),
+                           payload=p, scales=s_, fault=fault)
+        torch.cuda.synchronize()
+        assert np.array_equal(ids.cpu().numpy(), want_idx)
+        got_w = w.cpu().numpy()
+        ulp = np.abs(got_w.view(np.int32).astype(np.int64) - np.ascontiguousarray(want_w).view(np.int32).astype(np.int64))
+        assert ulp.max() <= 1, ulp.max()
+        oq, os_ = oracle_mod.quant_wire(synth.bf16_to_f32_np(x_bits))
+        assert np.array_equal(p.cpu().numpy(), oq) and np.array_equal(s_.cpu().numpy(), os_) and int(fault.item()) == 0
+        # routing only
+        ids2 = torch.empty_like(ids); w2 = torch.empty_like(w)
+        expert.produce_dev(to_dev(logits, dev), None if b is None else to_dev(b, dev), t, ids2, w2)
+        torch.cuda.synchronize()
+        assert torch.equal(ids2, ids) and torch.equal(w2, w)
+
+
 def test_quant_v1_faults_write_nothing(dev):
     import torch
 
