@@ -140,6 +140,11 @@ int m26b_route_reduce_dev(const float* y, const float* weights, uint32_t rows, f
  * planes[r] BF16 [n], r < n_ranks <= 8 -> out FP32 [n]. `planes` is a HOST array of device pointers. */
 int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
                       size_t errlen);
+/* The same with the coordinator's next step folded in (crates/mimo26-coordinator/src/dforward.rs:2294-2297: rank sum,
+ * then h += f, kernels/glue.cu:55-59): out = residual + sum, one FP32 add after the rank-ordered sum, so the result
+ * is bit-identical to the two launches. residual may be NULL (plain sum) and may alias out (in-place h += f). */
+int m26b_rank_sum_residual_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, const float* residual, float* out,
+                               void* stream, char* err, size_t errlen);
 
 /* The caller's producer step, on device pointers: the router's selection from FP32 logits
  * (crates/mimo26-coordinator/src/router.rs:42-80 router_from_logits, kernels/glue.cu:72-126 router_topk_kernel:
@@ -177,6 +182,9 @@ void* m26b_exchange_plane(m26b_exchange* x);
 int m26b_exchange_set_wait_ms(m26b_exchange* x, uint32_t ms);
 int m26b_exchange_publish_as(m26b_exchange* x, uint32_t peer_rank, void* stream, char* err, size_t errlen);
 int m26b_exchange_sum_dev(m26b_exchange* x, uint64_t n_elems, float* out_f32, void* stream, char* err, size_t errlen);
+/* sum_dev with the residual add folded in, as m26b_rank_sum_residual_dev: out = residual + rank-ordered sum. */
+int m26b_exchange_sum_residual_dev(m26b_exchange* x, uint64_t n_elems, const float* residual, float* out_f32, void* stream,
+                                   char* err, size_t errlen);
 int m26b_exchange_status(m26b_exchange* x, void* stream, char* err, size_t errlen);
 void m26b_exchange_free(m26b_exchange* x);
 

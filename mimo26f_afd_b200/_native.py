@@ -19,6 +19,7 @@ SYMBOLS = (
     "m26b_layer_new_from_checkpoint_ep", "m26b_ep_new", "m26b_ep_connect", "m26b_ep_connect_local", "m26b_ep_rows",
     "m26b_ep_set_wait_ms", "m26b_ep_publish_as", "m26b_ep_begin_dev", "m26b_ep_compute_dev", "m26b_ep_finish_dev",
     "m26b_ep_status", "m26b_ep_free", "m26b_produce_dev",
+    "m26b_rank_sum_residual_dev", "m26b_exchange_sum_residual_dev",
 )
 
 _lib = None
@@ -82,6 +83,8 @@ def lib() -> C.CDLL:
     L.m26b_ep_status.argtypes = [vp, vp, *err]
     L.m26b_ep_free.argtypes = [vp]
     L.m26b_ep_free.restype = None
+    L.m26b_rank_sum_residual_dev.argtypes = [C.POINTER(vp), C.c_int, C.c_uint64, f32p, f32p, vp, *err]
+    L.m26b_exchange_sum_residual_dev.argtypes = [vp, C.c_uint64, f32p, f32p, vp, *err]
     L.m26b_produce_dev.argtypes = [f32p, f32p, C.c_uint32, i32p, f32p, vp, C.c_int, C.c_int, u8p, u8p, u32p, vp, *err]
     for name in SYMBOLS:
         if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version", "m26b_exchange_plane", "m26b_exchange_free",

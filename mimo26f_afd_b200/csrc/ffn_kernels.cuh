@@ -583,7 +583,10 @@ __global__ void __launch_bounds__(256) route_reduce_kernel(const float* __restri
 struct RankPlanes {
     const uint16_t* p[8];
 };
-__global__ void __launch_bounds__(256) rank_sum_kernel(RankPlanes planes, int n_ranks, uint64_t n, float* __restrict__ out) {
+// `residual` (may alias `out`): out = residual + s, the coordinator's next step (h += f,
+// crates/mimo26-coordinator/kernels/glue.cu:55-59, src/dforward.rs:2294-2297) folded into the same pass.
+__global__ void __launch_bounds__(256) rank_sum_kernel(RankPlanes planes, int n_ranks, uint64_t n, float* out,
+                                                       const float* residual) {
     const uint64_t n8 = n / 8;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += uint64_t(gridDim.x) * blockDim.x) {
         float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -596,13 +599,18 @@ __global__ void __launch_bounds__(256) rank_sum_kernel(RankPlanes planes, int n_
                 s[2 * k + 1] = __fadd_rn(s[2 * k + 1], __uint_as_float(wv[k] & 0xffff0000u));
             }
         }
+        if (residual) {
+            const float4 a = reinterpret_cast<const float4*>(residual)[2 * i], b = reinterpret_cast<const float4*>(residual)[2 * i + 1];
+            s[0] = __fadd_rn(a.x, s[0]); s[1] = __fadd_rn(a.y, s[1]); s[2] = __fadd_rn(a.z, s[2]); s[3] = __fadd_rn(a.w, s[3]);
+            s[4] = __fadd_rn(b.x, s[4]); s[5] = __fadd_rn(b.y, s[5]); s[6] = __fadd_rn(b.z, s[6]); s[7] = __fadd_rn(b.w, s[7]);
+        }
         reinterpret_cast<float4*>(out)[2 * i] = make_float4(s[0], s[1], s[2], s[3]);
         reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(s[4], s[5], s[6], s[7]);
     }
     for (uint64_t i = n8 * 8 + uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) {
         float s = 0.f;
         for (int r = 0; r < n_ranks; ++r) s = __fadd_rn(s, __uint_as_float(uint32_t(planes.p[r][i]) << 16));
-        out[i] = s;
+        out[i] = residual ? __fadd_rn(residual[i], s) : s;
     }
 }
 
@@ -639,7 +647,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 __global__ void __launch_bounds__(256) exchange_sum_kernel(ExchangePeers peers, int rank, int world, uint32_t step,
                                                            uint64_t plane_offset, uint64_t n, long long wait_cycles,
-                                                           float* __restrict__ out) {
+                                                           float* out, const float* residual) {
     __shared__ uint32_t late;
     ExchangeWindow* mine = reinterpret_cast<ExchangeWindow*>(peers.window[rank]);
     grid_dep_wait();             // the local plane comes from the combine kernel before this one
@@ -676,6 +684,11 @@ __global__ void __launch_bounds__(256) exchange_sum_kernel(ExchangePeers peers, 
                 s[2 * k] = __fadd_rn(s[2 * k], __uint_as_float(wv[k] << 16));
                 s[2 * k + 1] = __fadd_rn(s[2 * k + 1], __uint_as_float(wv[k] & 0xffff0000u));
             }
+        }
+        if (residual) {      // h += f of the coordinator, in the same pass (may alias out)
+            const float4 a = reinterpret_cast<const float4*>(residual)[2 * i], b = reinterpret_cast<const float4*>(residual)[2 * i + 1];
+            s[0] = __fadd_rn(a.x, s[0]); s[1] = __fadd_rn(a.y, s[1]); s[2] = __fadd_rn(a.z, s[2]); s[3] = __fadd_rn(a.w, s[3]);
+            s[4] = __fadd_rn(b.x, s[4]); s[5] = __fadd_rn(b.y, s[5]); s[6] = __fadd_rn(b.z, s[6]); s[7] = __fadd_rn(b.w, s[7]);
         }
         reinterpret_cast<float4*>(out)[2 * i] = make_float4(s[0], s[1], s[2], s[3]);
         reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(s[4], s[5], s[6], s[7]);

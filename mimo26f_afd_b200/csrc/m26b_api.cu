@@ -843,8 +843,8 @@ int m26b_route_reduce_dev(const float* y, const float* weights, uint32_t rows, f
     return 0;
 }
 
-int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
-                      size_t errlen) {
+int m26b_rank_sum_residual_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, const float* residual, float* out,
+                               void* stream, char* err, size_t errlen) {
     if (!planes || n_ranks < 1 || n_ranks > 8 || !out) { set_msg(err, errlen, "m26b rank sum: bad arguments"); return 1; }
     RankPlanes rp{};
     for (int r = 0; r < n_ranks; ++r) {
@@ -853,10 +853,15 @@ int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, fl
     }
     if (!n) return 0;
     const uint64_t t = (n / 8 + 255) / 256 + 1;
-    rank_sum_kernel<<<uint32_t(t < 148 * 16 ? t : 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(rp, n_ranks, n, out);
+    rank_sum_kernel<<<uint32_t(t < 148 * 16 ? t : 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(rp, n_ranks, n, out, residual);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, errlen, "m26b rank sum launch", e); return 2; }
     return 0;
+}
+
+int m26b_rank_sum_dev(const uint16_t* const* planes, int n_ranks, uint64_t n, float* out, void* stream, char* err,
+                      size_t errlen) {
+    return m26b_rank_sum_residual_dev(planes, n_ranks, n, nullptr, out, stream, err, errlen);
 }
 
 // ---- plane exchange between the GPUs of one box ----------------------------------------------
@@ -945,6 +950,11 @@ int m26b_exchange_publish_as(m26b_exchange* X, uint32_t peer_rank, void* stream,
 }
 
 int m26b_exchange_sum_dev(m26b_exchange* X, uint64_t n_elems, float* out_f32, void* stream, char* err, size_t errlen) {
+    return m26b_exchange_sum_residual_dev(X, n_elems, nullptr, out_f32, stream, err, errlen);
+}
+
+int m26b_exchange_sum_residual_dev(m26b_exchange* X, uint64_t n_elems, const float* residual, float* out_f32, void* stream,
+                                   char* err, size_t errlen) {
     if (!X || !out_f32 || !n_elems || n_elems % 8 || n_elems * 2 > X->plane_bytes) {
         set_msg(err, errlen, "m26b exchange sum: bad extent (a multiple of 8 elements that fits the plane)");
         return 1;
@@ -957,7 +967,7 @@ int m26b_exchange_sum_dev(m26b_exchange* X, uint64_t n_elems, float* out_f32, vo
     const uint64_t t = (n_elems / 8 + 255) / 256;
     const unsigned blocks = unsigned(t < 148 * 8 ? (t ? t : 1) : 148 * 8);
     const cudaError_t e = launch_dependent(exchange_sum_kernel, blocks, 256u, size_t(0), static_cast<cudaStream_t>(stream), X->peers,
-                                           X->rank, X->world, X->step, off, n_elems, X->wait_cycles, out_f32);
+                                           X->rank, X->world, X->step, off, n_elems, X->wait_cycles, out_f32, residual);
     if (e != cudaSuccess) { set_err(err, errlen, "m26b exchange sum launch", e); return 2; }
     return 0;
 }

@@ -235,11 +235,12 @@ def route_reduce_dev(y, weights, rows: int, partial, bf16, fault, stream=None) -
                                                _ptr(stream), err, 256), err)
 
 
-def rank_sum_dev(planes, n: int, out, stream=None) -> None:
-    """FP32 sum of BF16 planes in rank order; ``planes`` is a sequence of device buffers."""
+def rank_sum_dev(planes, n: int, out, stream=None, residual=None) -> None:
+    """FP32 sum of BF16 planes in rank order; ``planes`` is a sequence of device buffers. With ``residual`` the
+    coordinator's ``h += f`` is folded in: out = residual + sum (``residual`` may be ``out`` itself)."""
     arr = (C.c_void_p * len(planes))(*[_ptr(p) for p in planes])
     err = C.create_string_buffer(256)
-    _check(_native.lib().m26b_rank_sum_dev(arr, len(planes), n, _ptr(out), _ptr(stream), err, 256), err)
+    _check(_native.lib().m26b_rank_sum_residual_dev(arr, len(planes), n, _ptr(residual), _ptr(out), _ptr(stream), err, 256), err)
 
 
 class Exchange:
@@ -285,9 +286,10 @@ class Exchange:
         err = C.create_string_buffer(256)
         _check(_native.lib().m26b_exchange_publish_as(self._h, peer_rank, _ptr(stream), err, 256), err)
 
-    def sum(self, n_elems: int, out_f32, stream=None) -> None:
+    def sum(self, n_elems: int, out_f32, stream=None, residual=None) -> None:
+        """out = rank-ordered sum of every rank's plane (+ ``residual``, which may be ``out_f32`` itself)."""
         err = C.create_string_buffer(256)
-        _check(_native.lib().m26b_exchange_sum_dev(self._h, n_elems, _ptr(out_f32), _ptr(stream), err, 256), err)
+        _check(_native.lib().m26b_exchange_sum_residual_dev(self._h, n_elems, _ptr(residual), _ptr(out_f32), _ptr(stream), err, 256), err)
 
     def status(self, stream=None) -> None:
         err = C.create_string_buffer(256)

@@ -260,6 +260,16 @@ def test_rank_sum_order(dev, oracle_mod):
         expert.rank_sum_dev([to_dev(planes[r], dev) for r in range(g)], n, out)
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy().view(np.uint32), oracle_mod.rank_sum(planes[:g]).view(np.uint32))
+    # the coordinator's h += f folded in: identical to summing first and adding afterwards, also in place
+    h = rng.standard_normal(n).astype(np.float32)
+    want = (h + oracle_mod.rank_sum(planes[:4])).astype(np.float32)
+    hd = to_dev(h, dev)
+    out = torch.empty(n, dtype=torch.float32, device=dev)
+    expert.rank_sum_dev([to_dev(planes[r], dev) for r in range(4)], n, out, residual=hd)
+    expert.rank_sum_dev([to_dev(planes[r], dev) for r in range(4)], n, hd, residual=hd)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(hd.cpu().numpy().view(np.uint32), want.view(np.uint32))
     out = torch.empty(n, dtype=torch.float32, device=dev)
     expert.rank_sum_dev([to_dev(planes[r], dev) for r in (0, 2, 1, 3)], n, out)
     torch.cuda.synchronize()
@@ -299,6 +309,17 @@ def test_plane_exchange_two_windows_one_process(dev, oracle_mod):
         want = oracle_mod.rank_sum(planes)
         for r in range(2):
             assert np.array_equal(out[r].cpu().numpy().view(np.uint32), want.view(np.uint32)), (step, r)
+        if step == 1:                                           # the same step's planes again, with h += f folded in
+            h = rng.standard_normal(n).astype(np.float32)
+            for r in range(2):
+                torch.as_tensor(_DevView(ex[r].plane(), n, "<i2"), device=dev).copy_(to_dev(planes[r], dev))
+            torch.cuda.synchronize()
+            for r in range(2):
+                hd = to_dev(h, dev)
+                ex[r].publish_as(1 - r)
+                ex[r].sum(n, hd, residual=hd)
+                ex[r].status()
+                assert np.array_equal(hd.cpu().numpy().view(np.uint32), (h + want).astype(np.float32).view(np.uint32))
     # a peer that never publishes: the wait runs out, the status says so, and the window works again afterwards
     ex[0].set_wait_ms(20)
     ex[0].sum(n, out[0])
