@@ -221,6 +221,33 @@ int m26b_ep_finish_dev(m26b_ep* e, uint16_t* bf16_out, float* partial_out, void*
 int m26b_ep_status(m26b_ep* e, void* stream, char* err, size_t errlen);
 void m26b_ep_free(m26b_ep* e);
 
+/* DS41RTE3 v3 frames (host memory): the request a rank receives and the compact return it sends
+ * (crates/mimo26-wire/src/layout.rs:64-115 field offsets, src/frame.rs:311-455, 868-955, 987-1041; checksum CRC32C over the
+ * frame with its own field zero, src/crc32c.rs). Return code 6 = frame rejected, with the reference's reason in `err`.
+ *   request_bytes / return_bytes: frame sizes for `rows` tokens with 8 routes each (128 + rows x 4360, 128 + rows x 8192).
+ *   encode_request: the frame of encode_request_meta_into (frame.rs:569-652: decode-kind rows, row t = id and position t,
+ *     routes t*8.., placement version 1) with the hidden rows copied in and, if `seal`, the checksum written.
+ *   serve_frame: what the expert daemon does per request (crates/mimo26-spark/src/serve.rs:206-246 + main.rs:386-413):
+ *     validate the request in place, run m26b_ffn on its rows at the frame's stride, write the return frame (BF16 rows
+ *     straight behind the header, flags = pre-summed + compact BF16, ids copied from the request) and seal it.
+ *     `check_crc` = verify the request's checksum and seal the reply (0 = the reference's MIMO26_WIRE_NOCRC=1 mode).
+ *   parse_return: the coordinator's checks on a return frame; rows_offset = where the BF16 rows start. */
+uint64_t m26b_frame_request_bytes(uint32_t rows);
+uint64_t m26b_frame_return_bytes(uint32_t rows);
+uint32_t m26b_frame_crc32c(const uint8_t* bytes, uint64_t n);
+int m26b_frame_encode_request(uint8_t* out, uint64_t cap, uint64_t request_id, uint32_t layer_id, uint64_t executor_id, uint64_t seq,
+                              const uint8_t* payload, size_t payload_pitch, const uint8_t* scales, size_t scales_pitch,
+                              const int32_t* ids, const float* weights, uint32_t rows, int seal, uint64_t* len_out, char* err,
+                              size_t errlen);
+/* serve_frame's checks on a request frame without running it (no GPU needed). */
+int m26b_frame_check_request(const uint8_t* request, uint64_t request_len, int check_crc, uint32_t* rows, uint64_t* request_id,
+                             uint32_t* layer_id, char* err, size_t errlen);
+int m26b_serve_frame(const m26b_layer* l, m26b_scratch* s, const uint8_t* request, uint64_t request_len, uint8_t* reply,
+                     uint64_t reply_cap, uint64_t* reply_len, int check_crc, uint64_t reply_seq, float* ms, char* err,
+                     size_t errlen);
+int m26b_frame_parse_return(const uint8_t* frame, uint64_t len, int check_crc, uint64_t* request_id, uint32_t* layer_id,
+                            uint32_t* rows, uint32_t* status, uint64_t* seq, uint64_t* rows_offset, char* err, size_t errlen);
+
 /* Route plan without any allocation. No counterpart in the reference.
  * For callers that must not allocate device memory while they run: a serving loop that gave every free byte of the
  * GPU to resident expert weights at start-up, a request handler that has to stay clear of cudaMalloc's device-wide

@@ -16,6 +16,7 @@
 #include "gemm_mx_pair.cuh"
 #include "prologue_small.cuh"
 #include "ep_kernels.cuh"
+#include "frame.inl"
 
 using namespace m26b;
 
@@ -1215,6 +1216,176 @@ void m26b_ep_free(m26b_ep* E) {
     if (E->fault) cudaFree(E->fault);
     if (E->hfault) cudaFreeHost(E->hfault);
     delete E;
+}
+
+// ---- DS41RTE3 v3 frames ----------------------------------------------------------------------
+uint64_t m26b_frame_request_bytes(uint32_t rows) {
+    return m26b_frame::kHeaderLen + uint64_t(rows) * (m26b_frame::kDescLen + kTopK * m26b_frame::kRouteLen + m26b_frame::kHiddenRow);
+}
+uint64_t m26b_frame_return_bytes(uint32_t rows) { return m26b_frame::kHeaderLen + uint64_t(rows) * m26b_frame::kReturnRow; }
+uint32_t m26b_frame_crc32c(const uint8_t* bytes, uint64_t n) { return m26b_frame::crc32c(bytes, size_t(n)); }
+
+int m26b_frame_encode_request(uint8_t* out, uint64_t cap, uint64_t request_id, uint32_t layer_id, uint64_t executor_id, uint64_t seq,
+                              const uint8_t* payload, size_t payload_pitch, const uint8_t* scales, size_t scales_pitch,
+                              const int32_t* ids, const float* weights, uint32_t rows, int seal, uint64_t* len_out, char* err,
+                              size_t errlen) {
+    using namespace m26b_frame;
+    if (!out || !payload || !scales || !ids || !weights || !rows || payload_pitch < kHidden || scales_pitch < kHidden / kBlockK) {
+        set_msg(err, errlen, "m26b frame: bad arguments");
+        return 1;
+    }
+    const uint64_t need = m26b_frame_request_bytes(rows);
+    if (cap < need) {
+        if (err && errlen) std::snprintf(err, errlen, "m26b frame: buffer too short: need %llu bytes, got %llu", (unsigned long long)need, (unsigned long long)cap);
+        return 1;
+    }
+    const uint64_t routes = uint64_t(rows) * kTopK;
+    Header h{};
+    h.kind = kKindRequest; h.request_id = request_id; h.placement_version = 1; h.layer_id = layer_id; h.row_count = rows;
+    h.dim = kHidden; h.dtype = kDtypeUe8m0K32; h.source_kind = 1; h.route_count = uint32_t(routes);
+    h.desc_bytes = uint32_t(rows * kDescLen); h.route_bytes = uint32_t(routes * kRouteLen); h.payload_bytes = uint64_t(rows) * kHiddenRow;
+    h.logical_bytes = uint64_t(rows) * (kDescLen + kTopK * kRouteLen + kHiddenRow); h.wire_bytes = need; h.flags = 0;
+    h.row_stride = uint32_t(kHiddenRow); h.status = 0; h.executor_id = executor_id; h.token_position = 0; h.seq = seq;
+    write_header(out, h);
+    uint8_t* desc = out + kHeaderLen;
+    uint8_t* route = desc + size_t(rows) * kDescLen;
+    uint8_t* hidden = route + routes * kRouteLen;
+    for (uint32_t t = 0; t < rows; ++t) {
+        uint8_t* d = desc + size_t(t) * kDescLen;
+        std::memset(d, 0, kDescLen);
+        put64(d, 0, t); put16(d, 8, 1); put64(d, 12, request_id); put64(d, 20, t); put32(d, 28, t * kTopK); put32(d, 32, kTopK);
+        for (uint32_t k = 0; k < uint32_t(kTopK); ++k) {
+            uint8_t* r = route + (size_t(t) * kTopK + k) * kRouteLen;
+            uint32_t wbits;
+            std::memcpy(&wbits, &weights[size_t(t) * kTopK + k], 4);
+            put32(r, 0, t); put32(r, 4, uint32_t(ids[size_t(t) * kTopK + k])); put32(r, 8, wbits);
+        }
+        std::memcpy(hidden + size_t(t) * kHiddenRow, payload + size_t(t) * payload_pitch, kHidden);
+        std::memcpy(hidden + size_t(t) * kHiddenRow + kHidden, scales + size_t(t) * scales_pitch, kHidden / kBlockK);
+    }
+    if (seal) put32(out, oCrc, frame_crc(out, size_t(need)));
+    if (len_out) *len_out = need;
+    return 0;
+}
+
+// The checks serve_frame makes on a request, without running it (RequestView::parse + serve_b1_view's shape rules).
+int m26b_frame_check_request(const uint8_t* request, uint64_t request_len, int check_crc, uint32_t* rows, uint64_t* request_id,
+                             uint32_t* layer_id, char* err, size_t errlen) {
+    using namespace m26b_frame;
+    if (!request) { set_msg(err, errlen, "m26b frame: null frame"); return 1; }
+    RequestView v{};
+    char msg[160];
+    if (const char* e = parse_request(request, size_t(request_len), check_crc != 0, v, msg, sizeof msg)) {
+        if (err && errlen) std::snprintf(err, errlen, "m26b frame: %s", e);
+        return 6;
+    }
+    if (v.h.row_stride != kHiddenRow) {
+        if (err && errlen) std::snprintf(err, errlen, "serve b1: hidden row stride %u is not 4,096 E4M3 + 128 scales", v.h.row_stride);
+        return 6;
+    }
+    for (uint32_t i = 0; i < v.h.row_count; ++i) {
+        const uint8_t* d = v.desc + size_t(i) * kDescLen;
+        if (get32(d, 32) != uint32_t(kTopK)) {
+            if (err && errlen) std::snprintf(err, errlen, "serve b1: row %u has %u routes, want 8", i, get32(d, 32));
+            return 6;
+        }
+        for (uint32_t j = 0; j < uint32_t(kTopK); ++j)
+            if (get32(v.routes + size_t(get32(d, 28) + j) * kRouteLen, 0) != i) {
+                if (err && errlen) std::snprintf(err, errlen, "serve b1: route row %u under row %u", get32(v.routes + size_t(get32(d, 28) + j) * kRouteLen, 0), i);
+                return 6;
+            }
+    }
+    if (rows) *rows = v.h.row_count;
+    if (request_id) *request_id = v.h.request_id;
+    if (layer_id) *layer_id = v.h.layer_id;
+    return 0;
+}
+
+// One request frame in, one return frame out: the rank's whole job for a request
+// (crates/mimo26-spark/src/serve.rs:206-246 serve_b1_view, then the return header of
+// crates/mimo26-wire/src/frame.rs:987-1030 and the seal). The hidden rows are read in place at the frame's stride.
+int m26b_serve_frame(const m26b_layer* L, m26b_scratch* S, const uint8_t* request, uint64_t request_len, uint8_t* reply,
+                     uint64_t reply_cap, uint64_t* reply_len, int check_crc, uint64_t reply_seq, float* ms, char* err,
+                     size_t errlen) {
+    using namespace m26b_frame;
+    if (!L || !S || !request || !reply) { set_msg(err, errlen, "m26b serve: null handle or buffer"); return 1; }
+    RequestView v{};
+    char msg[160];
+    if (const char* e = parse_request(request, size_t(request_len), check_crc != 0, v, msg, sizeof msg)) {
+        if (err && errlen) std::snprintf(err, errlen, "m26b serve: %s", e);
+        return 6;
+    }
+    const uint32_t rows = v.h.row_count;
+    if (v.h.row_stride != kHiddenRow) {
+        if (err && errlen) std::snprintf(err, errlen, "serve b1: hidden row stride %u is not 4,096 E4M3 + 128 scales", v.h.row_stride);
+        return 6;
+    }
+    const uint64_t need = m26b_frame_return_bytes(rows);
+    if (reply_cap < need) {
+        if (err && errlen) std::snprintf(err, errlen, "m26b serve: reply buffer too short: need %llu bytes, got %llu", (unsigned long long)need, (unsigned long long)reply_cap);
+        return 1;
+    }
+    std::vector<int32_t> ids(size_t(rows) * kTopK);
+    std::vector<float> weights(size_t(rows) * kTopK);
+    for (uint32_t i = 0; i < rows; ++i) {
+        const uint8_t* d = v.desc + size_t(i) * kDescLen;
+        if (get32(d, 32) != uint32_t(kTopK)) {
+            if (err && errlen) std::snprintf(err, errlen, "serve b1: row %u has %u routes, want 8", i, get32(d, 32));
+            return 6;
+        }
+        const uint32_t off = get32(d, 28);
+        for (uint32_t j = 0; j < uint32_t(kTopK); ++j) {
+            const uint8_t* r = v.routes + size_t(off + j) * kRouteLen;
+            if (get32(r, 0) != i) {
+                if (err && errlen) std::snprintf(err, errlen, "serve b1: route row %u under row %u", get32(r, 0), i);
+                return 6;
+            }
+            ids[size_t(i) * kTopK + j] = int32_t(get32(r, 4));
+            const uint32_t wbits = get32(r, 8);
+            std::memcpy(&weights[size_t(i) * kTopK + j], &wbits, 4);
+        }
+    }
+    uint16_t* rows_out = reinterpret_cast<uint16_t*>(reply + kHeaderLen);   // 128 bytes in: 2-byte aligned if `reply` is
+    const int rc = m26b_ffn(L, S, v.hidden, kHiddenRow, v.hidden + kHidden, kHiddenRow, ids.data(), weights.data(), rows, rows_out, ms,
+                            err, errlen);
+    if (rc) return rc;
+    Header h{};
+    h.kind = kKindReturn; h.request_id = v.h.request_id; h.placement_version = v.h.placement_version; h.layer_id = v.h.layer_id;
+    h.row_count = rows; h.dim = kHidden; h.dtype = kDtypeBf16; h.source_kind = 1; h.route_count = kTopK; h.desc_bytes = 0; h.route_bytes = 0;
+    h.payload_bytes = uint64_t(rows) * kReturnRow; h.logical_bytes = h.payload_bytes; h.wire_bytes = need; h.flags = kFlagReturnRequired;
+    h.row_stride = uint32_t(kReturnRow); h.status = 0; h.executor_id = v.h.executor_id; h.token_position = v.h.token_position; h.seq = reply_seq;
+    write_header(reply, h);
+    if (check_crc) put32(reply, oCrc, frame_crc(reply, size_t(need)));
+    if (reply_len) *reply_len = need;
+    return 0;
+}
+
+// Coordinator side of a return frame: header checks (kind, status, the two flags an Ok return must carry, BF16 rows of
+// 8,192 bytes) and the offset of the rows (crates/mimo26-wire/src/frame.rs:1127-1180 decode_return).
+int m26b_frame_parse_return(const uint8_t* frame, uint64_t len, int check_crc, uint64_t* request_id, uint32_t* layer_id,
+                            uint32_t* rows, uint32_t* status, uint64_t* seq, uint64_t* rows_offset, char* err, size_t errlen) {
+    using namespace m26b_frame;
+    if (!frame) { set_msg(err, errlen, "m26b frame: null frame"); return 1; }
+    Header h{};
+    char msg[160];
+    if (const char* e = parse_header(frame, size_t(len), h, msg, sizeof msg)) {
+        if (err && errlen) std::snprintf(err, errlen, "m26b frame: %s", e);
+        return 6;
+    }
+    auto bad = [&](const char* what) { if (err && errlen) std::snprintf(err, errlen, "m26b frame: %s", what); return 6; };
+    if (check_crc && frame_crc(frame, size_t(len)) != get32(frame, oCrc)) return bad("corrupt frame: CRC32C mismatch");
+    if (h.kind != kKindReturn) return bad("not a return frame");
+    if (h.status == 0 && (h.flags & kFlagReturnRequired) != kFlagReturnRequired) return bad("return frame is not a pre-summed compact BF16 return");
+    if (h.row_count == 0 || h.dim != uint32_t(kHidden) || h.dtype != kDtypeBf16 || h.row_stride != kReturnRow ||
+        h.payload_bytes != uint64_t(h.row_count) * kReturnRow || len != kHeaderLen + h.payload_bytes)
+        return bad("return frame geometry is not rows x 8,192 bytes of BF16");
+    if (request_id) *request_id = h.request_id;
+    if (layer_id) *layer_id = h.layer_id;
+    if (rows) *rows = h.row_count;
+    if (status) *status = h.status;
+    if (seq) *seq = h.seq;
+    if (rows_offset) *rows_offset = kHeaderLen;
+    return 0;
 }
 
 int m26b_scratch_timings(m26b_scratch* S, float* ms6, char* err, size_t errlen) {
