@@ -234,7 +234,8 @@ void m26b_ep_free(m26b_ep* e);
  *   parse_return: the coordinator's checks on a return frame; rows_offset = where the BF16 rows start. */
 uint64_t m26b_frame_request_bytes(uint32_t rows);
 uint64_t m26b_frame_return_bytes(uint32_t rows);
-uint32_t m26b_frame_crc32c(const uint8_t* bytes, uint64_t n);
+uint32_t m26b_frame_crc32c(const uint8_t* bytes, uint64_t n);        /* the CPU's CRC32C instruction where it exists */
+uint32_t m26b_frame_crc32c_table(const uint8_t* bytes, uint64_t n);  /* table path only: the cross-check of the former */
 int m26b_frame_encode_request(uint8_t* out, uint64_t cap, uint64_t request_id, uint32_t layer_id, uint64_t executor_id, uint64_t seq,
                               const uint8_t* payload, size_t payload_pitch, const uint8_t* scales, size_t scales_pitch,
                               const int32_t* ids, const float* weights, uint32_t rows, int seal, uint64_t* len_out, char* err,

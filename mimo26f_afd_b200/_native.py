@@ -20,7 +20,7 @@ SYMBOLS = (
     "m26b_ep_set_wait_ms", "m26b_ep_publish_as", "m26b_ep_begin_dev", "m26b_ep_compute_dev", "m26b_ep_finish_dev",
     "m26b_ep_status", "m26b_ep_free", "m26b_produce_dev",
     "m26b_rank_sum_residual_dev", "m26b_exchange_sum_residual_dev",
-    "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c", "m26b_frame_encode_request",
+    "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c", "m26b_frame_crc32c_table", "m26b_frame_encode_request",
     "m26b_serve_frame", "m26b_frame_parse_return", "m26b_frame_check_request",
 )
 
@@ -93,6 +93,8 @@ def lib() -> C.CDLL:
     L.m26b_frame_return_bytes.restype = C.c_uint64
     L.m26b_frame_crc32c.argtypes = [u8p, C.c_uint64]
     L.m26b_frame_crc32c.restype = C.c_uint32
+    L.m26b_frame_crc32c_table.argtypes = [u8p, C.c_uint64]
+    L.m26b_frame_crc32c_table.restype = C.c_uint32
     L.m26b_frame_encode_request.argtypes = [u8p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64, u8p, C.c_size_t, u8p,
                                             C.c_size_t, i32p, f32p, C.c_uint32, C.c_int, C.POINTER(C.c_uint64), *err]
     L.m26b_serve_frame.argtypes = [vp, vp, u8p, C.c_uint64, u8p, C.c_uint64, C.POINTER(C.c_uint64), C.c_int, C.c_uint64, f32p, *err]
@@ -103,7 +105,8 @@ def lib() -> C.CDLL:
     L.m26b_produce_dev.argtypes = [f32p, f32p, C.c_uint32, i32p, f32p, vp, C.c_int, C.c_int, u8p, u8p, u32p, vp, *err]
     for name in SYMBOLS:
         if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version", "m26b_exchange_plane", "m26b_exchange_free",
-                        "m26b_ep_free", "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c"):
+                        "m26b_ep_free", "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c",
+                        "m26b_frame_crc32c_table"):
             getattr(L, name).restype = C.c_int
     _lib = L
     return L

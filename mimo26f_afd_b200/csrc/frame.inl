@@ -10,6 +10,9 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#if defined(__x86_64__)
+#include <nmmintrin.h>
+#endif
 
 namespace m26b_frame {
 
@@ -42,7 +45,30 @@ struct CrcTable {
             for (int s = 1; s < 8; ++s) t[s][i] = (t[s - 1][i] >> 8) ^ t[0][t[s - 1][i] & 0xffu];
     }
 };
+#if defined(__x86_64__)
+// The CPU's own CRC32C instruction where it exists (checked once at run time); the table path is its reference.
+__attribute__((target("sse4.2"))) inline uint32_t crc_update_hw(uint32_t crc, const uint8_t* p, size_t n) {
+    uint64_t c = crc;
+    while (n && (reinterpret_cast<uintptr_t>(p) & 7u)) { c = _mm_crc32_u8(uint32_t(c), *p++); --n; }
+    while (n >= 8) {
+        uint64_t w;
+        std::memcpy(&w, p, 8);
+        c = _mm_crc32_u64(c, w);
+        p += 8; n -= 8;
+    }
+    while (n--) c = _mm_crc32_u8(uint32_t(c), *p++);
+    return uint32_t(c);
+}
+#endif
+inline uint32_t crc_update_table(uint32_t crc, const uint8_t* p, size_t n);
 inline uint32_t crc_update(uint32_t crc, const uint8_t* p, size_t n) {
+#if defined(__x86_64__)
+    static const bool hw = __builtin_cpu_supports("sse4.2");
+    if (hw) return crc_update_hw(crc, p, n);
+#endif
+    return crc_update_table(crc, p, n);
+}
+inline uint32_t crc_update_table(uint32_t crc, const uint8_t* p, size_t n) {
     static const CrcTable T;
     while (n && (reinterpret_cast<uintptr_t>(p) & 7u)) { crc = (crc >> 8) ^ T.t[0][(crc ^ *p++) & 0xffu]; --n; }
     while (n >= 8) {                                        // slicing by eight
@@ -57,6 +83,7 @@ inline uint32_t crc_update(uint32_t crc, const uint8_t* p, size_t n) {
     return crc;
 }
 inline uint32_t crc32c(const uint8_t* p, size_t n) { return ~crc_update(~0u, p, n); }
+inline uint32_t crc32c_table(const uint8_t* p, size_t n) { return ~crc_update_table(~0u, p, n); }
 // CRC32C of a frame with the header's checksum field taken as zero.
 inline uint32_t frame_crc(const uint8_t* f, size_t n) {
     static const uint8_t zero[4] = {0, 0, 0, 0};

@@ -1224,6 +1224,7 @@ uint64_t m26b_frame_request_bytes(uint32_t rows) {
 }
 uint64_t m26b_frame_return_bytes(uint32_t rows) { return m26b_frame::kHeaderLen + uint64_t(rows) * m26b_frame::kReturnRow; }
 uint32_t m26b_frame_crc32c(const uint8_t* bytes, uint64_t n) { return m26b_frame::crc32c(bytes, size_t(n)); }
+uint32_t m26b_frame_crc32c_table(const uint8_t* bytes, uint64_t n) { return m26b_frame::crc32c_table(bytes, size_t(n)); }
 
 int m26b_frame_encode_request(uint8_t* out, uint64_t cap, uint64_t request_id, uint32_t layer_id, uint64_t executor_id, uint64_t seq,
                               const uint8_t* payload, size_t payload_pitch, const uint8_t* scales, size_t scales_pitch,

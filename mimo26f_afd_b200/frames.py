@@ -23,6 +23,12 @@ def crc32c(data: bytes) -> int:
     return int(_native.lib().m26b_frame_crc32c(C.addressof(buf) if buf is not None else None, len(data)))
 
 
+def crc32c_table(data: bytes) -> int:
+    """The table path only (the cross-check of the instruction path ``crc32c`` may take)."""
+    buf = (C.c_uint8 * len(data)).from_buffer_copy(data) if data else None
+    return int(_native.lib().m26b_frame_crc32c_table(C.addressof(buf) if buf is not None else None, len(data)))
+
+
 def request_bytes(rows: int) -> int:
     return int(_native.lib().m26b_frame_request_bytes(rows))
 

@@ -40,7 +40,7 @@ def test_crc32c_known_answers_and_bitwise_cross_check():
         x = (x * 1664525 + 1013904223) & 0xFFFFFFFF
         long.append(x >> 24)
     for sample in (b"a", b"123456789", bytes(300), bytes(long), bytes(long[3:517])):
-        assert frames.crc32c(sample) == crc32c_bitwise(sample)
+        assert frames.crc32c(sample) == crc32c_bitwise(sample) == frames.crc32c_table(sample)
     assert frames.crc32c(b"123456789") != 0xCBF43926            # that is CRC-32 (IEEE), the wrong family
 
 
