@@ -744,3 +744,45 @@ def test_prefill_8192_tokens_properties_and_sampled_oracle(layer, dev, oracle_mo
         ref = oracle_mod.expert_ffn(xq, xs, *t)
         assert ref["rc"] == 0
         assert rel_l2(y[routes], ref["y"]) <= 1e-3
+
+
+def test_config4_65536_tokens_zipf_through_the_host_entry_point(layer, dev, oracle_mod):
+    """BASELINE config 4's batch (65,536 tokens, Zipf 1.0: one expert receives about 62,000 rows) on one GPU through
+    m26b_ffn, which cuts it into passes of 16,384 tokens. Properties: the bytes do not depend on the cut (four
+    quarter-size calls and a shifted cut give the same rows), and sampled tokens match the oracle end to end."""
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import synth
+
+    tokens = 65536
+    s = M.Scratch()
+    ids, w = synth.routing(SEED + 4, tokens, 1.0)
+    counts = np.bincount(ids.reshape(-1), minlength=256)
+    assert counts.max() > 40000 and (counts > 0).all()
+    sample = np.array([0, 1, 16383, 16384, 40000, 65535])
+    # quantised rows: seeded bytes directly (valid E4M3 codes, scale bytes 118..125), the host entry point's own input form
+    rng = np.random.default_rng(99)
+    xq = rng.integers(0, 256, (tokens, H), dtype=np.uint8)
+    xq[(xq & 0x7F) == 0x7F] ^= 1
+    xs = rng.integers(118, 126, (tokens, H // 32), dtype=np.uint8)
+    bf = np.empty((tokens, H), np.uint16)
+    st = M.ffn(layer, s, xq.reshape(-1), xs.reshape(-1), ids.reshape(-1), w.reshape(-1), tokens, bf.reshape(-1))
+    assert st.groups > 0
+    # another cut: 10,000 tokens first, then the rest (passes start at other tokens)
+    cut = 10000
+    bf_a = np.empty((cut, H), np.uint16)
+    bf_b = np.empty((tokens - cut, H), np.uint16)
+    M.ffn(layer, s, xq[:cut].reshape(-1), xs[:cut].reshape(-1), ids[:cut].reshape(-1), w[:cut].reshape(-1), cut, bf_a.reshape(-1))
+    M.ffn(layer, s, xq[cut:].reshape(-1), xs[cut:].reshape(-1), ids[cut:].reshape(-1), w[cut:].reshape(-1), tokens - cut, bf_b.reshape(-1))
+    assert np.array_equal(bf[:cut], bf_a) and np.array_equal(bf[cut:], bf_b)
+    # sampled tokens against the oracle (their experts' weights only)
+    tensors = synth.layer_np(SEED, np.unique(ids[sample]))
+    ref = oracle_mod.ffn_layer(tensors, xq[sample], xs[sample], ids[sample], w[sample])
+    assert ref["rc"] == 0
+    dec = lambda b: (b.astype(np.uint32) << 16).view(np.float32)
+    got = dec(bf[sample])
+    assert rel_l2(got, ref["partial"]) <= 1e-3 + 2.0 ** -8          # BF16 output against the FP32 plane: half a BF16 ulp on top
+    # elementwise: one BF16 ulp, except where an E4M3 bin crossing of the intermediate moved an output (counted, rare)
+    # (these seeded bytes give outputs of magnitude ~1000, so the absolute part of the bound scales with the row)
+    rms = np.sqrt((ref["partial"].astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    beyond = np.abs(got - dec(ref["bf16"])) > 2.0 ** -7 * np.abs(ref["partial"]) + 1e-3 * rms
+    assert beyond.mean() < 2e-3, beyond.mean()
