@@ -1,0 +1,54 @@
+"""Step-histogram workloads (CPU): file checks of step_hist.h, the seeded expert assignment, and batches that realise a
+histogram with distinct experts per token."""
+import numpy as np
+import pytest
+
+from mimo26f_afd_b200 import step_hist as SH
+
+
+def test_parse_checks_follow_the_reference():
+    good = {"C16-w8": {"steps": [{"layer": 3, "hist": {"8": 100, "16": 14}}]}}
+    w = SH.parse(good, "C16-w8")
+    assert w["seed"] == 20260924 and w["steps"][0]["experts"] == 114 and w["steps"][0]["routes"] == 1024
+
+    def refused(doc, word, name="C16-w8"):
+        with pytest.raises(SH.StepHistError) as e:
+            SH.parse(doc, name)
+        assert word in str(e.value), str(e.value)
+
+    refused({"C16-w8": {"hist": {"1": 2}}}, "per-layer-step histograms required")
+    refused({"C16-w8": {"steps": []}}, "step count")
+    refused({"C16-w8": {"steps": [{"layer": 0, "hist": {"8": 128}}]}}, "MoE layer")
+    refused({"C16-w8": {"steps": [{"layer": 1, "hist": {}}]}}, "empty")
+    refused({"C16-w8": {"steps": [{"layer": 1, "hist": {"08": 128}}]}}, "noncanonical")
+    refused({"C16-w8": {"steps": [{"layer": 1, "hist": {"129": 1}}]}}, "M must be")
+    refused({"C16-w8": {"steps": [{"layer": 1, "hist": {"1": 257}}]}}, "active count")
+    refused({"C16-w8": {"steps": [{"layer": 1, "hist": {"1": 200, "2": 100}}]}}, "more than 256")
+    refused({"C1-w8": {"steps": [{"layer": 1, "hist": {"9": 1}}]}}, "exceeds workload token count", "C1-w8")
+    refused({"C16-w8": {"steps": [{"layer": 1, "hist": {"8": 100}}]}}, "route count differs")
+
+
+def test_expert_assignment_is_a_seeded_permutation_dealt_in_bin_order():
+    step = SH.parse({"X": {"steps": [{"layer": 1, "hist": {"1": 3, "5": 2, "2": 4}}]}}, "X")["steps"][0]
+    a = SH.assign_experts(step, 77)
+    assert [m for m, _ in a] == [1, 2, 5] and [len(e) for _, e in a] == [3, 4, 2]
+    flat = [e for _, es in a for e in es]
+    assert len(set(flat)) == 9 and all(0 <= e < 256 for e in flat)
+    assert SH.assign_experts(step, 77) == a and SH.assign_experts(step, 78) != a
+    assert SH.sample_seed(1, 0, 0) != SH.sample_seed(1, 0, 1) != SH.sample_seed(1, 1, 0)
+
+
+@pytest.mark.parametrize("name", ["C1-w8", "C4-w8", "C16-w8"])
+def test_batches_realise_their_histograms(name):
+    doc = SH.synthetic_workload(name, 6, zipf=1.2)
+    w = SH.parse(doc, name)
+    for i, step in enumerate(w["steps"]):
+        ids, wts = SH.step_batch(step, SH.sample_seed(w["seed"], i, 0))
+        assert ids.shape == (SH.WORKLOAD_TOKENS[name], 8)
+        assert all(len(set(r)) == 8 for r in ids.tolist())
+        assert SH.histogram_of(ids) == step["hist"]
+        assert np.allclose(wts.sum(axis=1), 1.0, atol=1e-6) and (wts > 0).all()
+    # the extreme step: one expert takes a row of every token
+    step = SH.parse({name: {"steps": [{"layer": 1, "hist": {str(SH.WORKLOAD_TOKENS[name]): 8}}]}}, name)["steps"][0]
+    ids, _ = SH.step_batch(step, 5)
+    assert SH.histogram_of(ids) == {SH.WORKLOAD_TOKENS[name]: 8}
