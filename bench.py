@@ -498,6 +498,16 @@ def main():
         sub = argparse.Namespace(**vars(args))
         sub.steps, sub.warmup = max(3, min(args.steps, 10)), max(3, min(args.warmup, 5))
         extra = run_workload("prefill8k", layer, scratch, dev, stream, sub, rank, world, peaks)
+        extra["parallelism"] = f"tp{world}" if world > 1 else "single"
+    prefill_ep = None
+    if extra is not None and world > 1:
+        # Prefill under tensor parallelism repeats the per-token work on every rank and stops scaling at two GPUs; the
+        # scheme for prefill on several GPUs is expert parallelism, so the same segment is also reported that way.
+        layer.close()
+        del layer
+        torch.cuda.empty_cache()
+        prefill_ep = run_expert_parallel("prefill8k", dev, stream, sub, rank, world)
+        prefill_ep["parallelism"] = f"ep{world}"
     if rank == 0:
         cpu = cpu_baseline_for(args.workload) if world == 1 else None
         line = dict(metric="moe_expert_ffn_tokens_per_s_per_layer", value=main_r["value"], unit="tokens/s", n_gpus=world,
@@ -516,10 +526,14 @@ def main():
             line["prefill"] = {k: extra[k] for k in ("workload", "tokens", "value", "ms_per_step", "ms_per_step_with_kernel_events", "e2e", "roofline", "whole_step",
                                                      "kernels_ms", "clocks")}
             line["prefill"]["unit"] = "tokens/s"
+            line["prefill"]["parallelism"] = extra["parallelism"]
+        if prefill_ep:
+            line["prefill_expert_parallel"] = {k: prefill_ep[k] for k in ("workload", "tokens", "value", "ms_per_step", "e2e", "roofline",
+                                                                           "whole_step", "clocks", "parallelism")}
+            line["prefill_expert_parallel"]["unit"] = "tokens/s"
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
         dist.destroy_process_group()
 
 

@@ -792,6 +792,10 @@ int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtyp
         return 1;
     }
     if (!device_ok(L->device, err, errlen) || !device_ok(S->device, err, errlen)) return 1;
+    if (reinterpret_cast<uintptr_t>(x) & 15u) {
+        set_msg(err, errlen, "m26b ffn: the activation pointer must be 16-byte aligned");
+        return 1;
+    }
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : S->st;
     int rc = ensure_pass(S, rows, L->i_local, x_dtype != 2, err, errlen);
     if (rc) return rc;
