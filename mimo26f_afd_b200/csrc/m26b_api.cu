@@ -141,6 +141,11 @@ int pair_resident_ctas(int sms) {
     return ctas < (sms & ~1) ? ctas : (sms & ~1);
 }
 
+// Requests of at most this many tokens go up from the host in one copy (rows, scales, ids, weights packed into a
+// pinned staging block) instead of three: a copy operation costs more than copying 70 KB on the host.
+constexpr uint32_t kStageRows = 64;
+constexpr size_t kStageBytes = size_t(kStageRows) * (kHidden + kHidden / kBlockK + kTopK * 8);
+
 // Requests above this many tokens run the CTA-pair kernels (prefill); below, the single-CTA kernels (decode).
 constexpr uint32_t kPairMinRows = 129;
 
@@ -204,7 +209,7 @@ struct m26b_scratch {
     int device = 0, sms = 0;
     int pair_ctas = 0;          // resident CTAs of the pair kernels (0: the device cannot run them)
     uint32_t debug = 0;
-    Dev xq, xs, iw, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
+    Dev xq, xs, iw, dstage, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
         partial, bf16, status, gather, plan_cnt;
     TokenMaps map_x, map_mid;
     PairMaps pair_x, pair_mid;
@@ -212,6 +217,7 @@ struct m26b_scratch {
     void* map_x_base = nullptr; void* map_mid_base = nullptr;
     uint64_t map_x_rows = 0, map_mid_rows = 0; int map_mid_cols = 0;
     std::vector<uint8_t> hiw;
+    uint8_t* hstage = nullptr;       // pinned: rows, scales, ids and weights of a small request, uploaded in one copy
     Status* hstatus = nullptr;       // pinned
     // last pass
     uint32_t last_rows = 0; int last_i_local = 0; bool pending = false; uint32_t n_status = 0;
@@ -630,6 +636,7 @@ int m26b_scratch_new(m26b_scratch** out, char* err, size_t errlen) {
         (e = cudaEventCreate(&S->e0)) != cudaSuccess || (e = cudaEventCreate(&S->e1)) != cudaSuccess ||
         (e = cudaEventCreate(&S->ea)) != cudaSuccess || (e = cudaEventCreate(&S->ec)) != cudaSuccess ||
         (e = cudaMallocHost(reinterpret_cast<void**>(&S->hstatus), sizeof(Status) * 64)) != cudaSuccess ||
+        (e = cudaMallocHost(reinterpret_cast<void**>(&S->hstage), kStageBytes)) != cudaSuccess ||
         (e = [&] { cudaError_t r = cudaSuccess; for (auto& ev : S->kev) if (r == cudaSuccess) r = cudaEventCreate(&ev); return r; }()) != cudaSuccess) {
         set_err(err, errlen, "m26b scratch stream/events", e);
         m26b_scratch_free(S);
@@ -648,6 +655,7 @@ void m26b_scratch_free(m26b_scratch* S) {
     for (auto& ev : S->kev) if (ev) cudaEventDestroy(ev);
     if (S->st) cudaStreamDestroy(S->st);
     if (S->hstatus) cudaFreeHost(S->hstatus);
+    if (S->hstage) cudaFreeHost(S->hstage);
     delete S;
 }
 
@@ -672,35 +680,53 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     const uint32_t pass_rows = rows < kMaxPassRows ? rows : kMaxPassRows;
     const uint32_t passes = (rows + kMaxPassRows - 1) / kMaxPassRows;
     if (passes > 64) { set_msg(err, errlen, "m26b ffn: bad rows/handles/pitch"); return 1; }
-    M26B_CK(S->xq.ensure(size_t(rows) * kHidden), "m26b x alloc");
-    M26B_CK(S->xs.ensure(size_t(rows) * (kHidden / kBlockK)), "m26b xs alloc");
-    M26B_CK(S->iw.ensure(routes * 8), "m26b ids/w alloc");
     M26B_CK(S->gather.ensure(size_t(rows) * kHidden * 2), "m26b out alloc");
     int rc = ensure_pass(S, pass_rows, L->i_local, false, err, errlen);
     if (rc) return rc;
-    int32_t* const ids_d = S->iw.as<int32_t>();
-    float* const w_d = reinterpret_cast<float*>(S->iw.as<uint8_t>() + routes * 4);
-    // contiguous rows go up as one linear copy (a pitched copy of the same bytes takes a slower path)
-    if (payload_pitch == kHidden)
-        M26B_CK(cudaMemcpyAsync(S->xq.p, payload, size_t(rows) * kHidden, cudaMemcpyHostToDevice, S->st), "m26b x upload");
-    else
-        M26B_CK(cudaMemcpy2DAsync(S->xq.p, kHidden, payload, payload_pitch, kHidden, rows, cudaMemcpyHostToDevice, S->st),
-                "m26b x upload");
-    if (scales_pitch == kHidden / kBlockK)
-        M26B_CK(cudaMemcpyAsync(S->xs.p, scales, size_t(rows) * (kHidden / kBlockK), cudaMemcpyHostToDevice, S->st), "m26b xs upload");
-    else
-        M26B_CK(cudaMemcpy2DAsync(S->xs.p, kHidden / kBlockK, scales, scales_pitch, kHidden / kBlockK, rows,
-                                  cudaMemcpyHostToDevice, S->st), "m26b xs upload");
-    S->hiw.resize(routes * 8);
-    std::memcpy(S->hiw.data(), ids, routes * 4);
-    std::memcpy(S->hiw.data() + routes * 4, weights, routes * 4);
-    M26B_CK(cudaMemcpyAsync(S->iw.p, S->hiw.data(), routes * 8, cudaMemcpyHostToDevice, S->st), "m26b ids/w upload");
+    const uint8_t* xq_d;
+    const uint8_t* xs_d;
+    const int32_t* ids_d;
+    const float* w_d;
+    if (rows <= kStageRows) {
+        M26B_CK(S->dstage.ensure(kStageBytes), "m26b staging alloc");
+        const size_t o_s = size_t(rows) * kHidden, o_i = o_s + size_t(rows) * (kHidden / kBlockK), o_w = o_i + routes * 4;
+        for (uint32_t r = 0; r < rows; ++r) {
+            std::memcpy(S->hstage + size_t(r) * kHidden, payload + size_t(r) * payload_pitch, kHidden);
+            std::memcpy(S->hstage + o_s + size_t(r) * (kHidden / kBlockK), scales + size_t(r) * scales_pitch, kHidden / kBlockK);
+        }
+        std::memcpy(S->hstage + o_i, ids, routes * 4);
+        std::memcpy(S->hstage + o_w, weights, routes * 4);
+        M26B_CK(cudaMemcpyAsync(S->dstage.p, S->hstage, o_w + routes * 4, cudaMemcpyHostToDevice, S->st), "m26b request upload");
+        xq_d = S->dstage.as<uint8_t>(); xs_d = xq_d + o_s;
+        ids_d = reinterpret_cast<const int32_t*>(xq_d + o_i); w_d = reinterpret_cast<const float*>(xq_d + o_w);
+    } else {
+        M26B_CK(S->xq.ensure(size_t(rows) * kHidden), "m26b x alloc");
+        M26B_CK(S->xs.ensure(size_t(rows) * (kHidden / kBlockK)), "m26b xs alloc");
+        M26B_CK(S->iw.ensure(routes * 8), "m26b ids/w alloc");
+        // contiguous rows go up as one linear copy (a pitched copy of the same bytes takes a slower path)
+        if (payload_pitch == kHidden)
+            M26B_CK(cudaMemcpyAsync(S->xq.p, payload, size_t(rows) * kHidden, cudaMemcpyHostToDevice, S->st), "m26b x upload");
+        else
+            M26B_CK(cudaMemcpy2DAsync(S->xq.p, kHidden, payload, payload_pitch, kHidden, rows, cudaMemcpyHostToDevice, S->st),
+                    "m26b x upload");
+        if (scales_pitch == kHidden / kBlockK)
+            M26B_CK(cudaMemcpyAsync(S->xs.p, scales, size_t(rows) * (kHidden / kBlockK), cudaMemcpyHostToDevice, S->st), "m26b xs upload");
+        else
+            M26B_CK(cudaMemcpy2DAsync(S->xs.p, kHidden / kBlockK, scales, scales_pitch, kHidden / kBlockK, rows,
+                                      cudaMemcpyHostToDevice, S->st), "m26b xs upload");
+        S->hiw.resize(routes * 8);
+        std::memcpy(S->hiw.data(), ids, routes * 4);
+        std::memcpy(S->hiw.data() + routes * 4, weights, routes * 4);
+        M26B_CK(cudaMemcpyAsync(S->iw.p, S->hiw.data(), routes * 8, cudaMemcpyHostToDevice, S->st), "m26b ids/w upload");
+        xq_d = S->xq.as<uint8_t>(); xs_d = S->xs.as<uint8_t>();
+        ids_d = S->iw.as<int32_t>(); w_d = reinterpret_cast<const float*>(S->iw.as<uint8_t>() + routes * 4);
+    }
     uint16_t* const out_d = S->gather.as<uint16_t>();
     // stage timings cost four events between the kernels (and the overlap of dependent launches): only when asked for
     const bool timed = ms != nullptr && passes == 1;
     for (uint32_t ps = 0; ps < passes; ++ps) {
         const uint32_t r0 = ps * kMaxPassRows, n = rows - r0 < kMaxPassRows ? rows - r0 : kMaxPassRows;
-        rc = enqueue_pass(L, S, S->xq.as<uint8_t>() + size_t(r0) * kHidden, S->xs.as<uint8_t>() + size_t(r0) * (kHidden / kBlockK),
+        rc = enqueue_pass(L, S, xq_d + size_t(r0) * kHidden, xs_d + size_t(r0) * (kHidden / kBlockK),
                           ids_d + size_t(r0) * kTopK, w_d + size_t(r0) * kTopK, n, out_d + size_t(r0) * kHidden,
                           S->partial.as<float>(), S->status.as<Status>() + ps, S->st, timed, err, errlen);
         if (rc) return rc;
