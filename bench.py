@@ -44,7 +44,7 @@ MXF8F6F4_RANDOM_BURST_TFLOPS = 3694.0       # same probe on random operands, fir
 MXF8F6F4_RANDOM_SUSTAINED_TFLOPS = 3193.0   # same, after three seconds (1.32 GHz under the 1000 W limit)
 # dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch at N = 1, from the ncu captures summarised in
 # profiles/gemm_mx_decode16.md and profiles/gemm_mx_prefill8k.md (the seeded workloads are the same every run)
-FC1_TRAFFIC_BYTES = {"decode16": 915384064, "prefill8k": 3002103808}
+FC1_TRAFFIC_BYTES = {"decode16": 915809536, "prefill8k": 2762296320}
 WORKLOADS = {
     "decode16": dict(tokens=16, zipf=0.0, desc="16-token decode batch, uniform routing (BASELINE configs[1])"),
     "prefill8k": dict(tokens=8192, zipf=0.0, desc="8192-token prefill segment, uniform routing (BASELINE configs[3])"),
