@@ -104,6 +104,8 @@ def cpu_reference_arm(args, rank):
     """The reference's CPU expert path on the host cores, bounded sample of the headline workload."""
     if rank != 0:
         return
+    # the launcher for several ranks pins every process to one OpenMP thread; this arm runs on rank 0 alone and takes all cores
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import oracle
     from mimo26f_afd_b200 import synth
 
