@@ -297,7 +297,7 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
     roof["kernel_ms"] = fc1_ms
     whole = dict(hbm_gbs=(active * EXPERT_BYTES / world + tokens * H * 4 + routes * 8) / (total_ms / args.steps * 1e-3) / 1e9,
                  tflops=FLOP_PER_TOKEN * tokens / world / (total_ms / args.steps * 1e-3) / 1e12)
-    launches = (4 if tokens <= 32 else 6 if routes <= 4096 else 8) + (1 if world > 1 else 0)
+    launches = (4 if tokens <= 128 else 6 if routes <= 4096 else 8) + (1 if world > 1 else 0)
     return dict(workload=name, tokens=tokens, active_experts=active, value=value, ms_per_step=total_ms / args.steps,
                 ms_per_step_with_kernel_events=ms_instrumented,
                 e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),

@@ -360,7 +360,7 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
     return 0;
 }
 
-// Activations that are not quantised yet (requests of at most kSmallRows tokens quantise inside the fused prologue).
+// Activations that are not quantised yet (requests of at most kMediumRows tokens quantise inside the fused prologue).
 struct RawInput {
     const void* x;
     int dtype, codec;          // 0 BF16 / 1 FP32; 0 wire / 1 quant_v1
@@ -368,9 +368,15 @@ struct RawInput {
 };
 
 template <int CODEC, int IN>
-void launch_small_prologue(uint32_t grid, cudaStream_t st, const SmallIo& io, const int32_t* ids, const float* w, uint32_t rows,
+void launch_small_prologue(uint32_t sms, cudaStream_t st, const SmallIo& io, const int32_t* ids, const float* w, uint32_t rows,
                            const uint8_t* resident, int max_n, int mt1, int mt2, const PlanOut& po) {
-    small_prologue_kernel<CODEC, IN><<<grid, 256, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
+    const uint32_t routes = rows * kTopK;
+    if (rows <= kSmallRows) {
+        small_prologue_kernel<CODEC, IN, 256><<<routes < sms ? routes : sms, 256, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
+    } else {
+        const uint32_t need = (routes + 3u) / 4u;          // four rows side by side per CTA
+        small_prologue_kernel<CODEC, IN, 1024><<<need < sms ? need : sms, 1024, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
+    }
 }
 
 // A pass of an expert-parallel step: where the pass's token rows live and where its FC2 rows go.
@@ -380,7 +386,7 @@ struct EpPass {
 };
 
 // Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine. `raw` (only with at most
-// kSmallRows rows) names activations still to be quantised into xq / xs; `status_cleared`: the caller has already
+// kMediumRows rows) names activations still to be quantised into xq / xs; `status_cleared`: the caller has already
 // zeroed the status block on the stream.
 int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const uint8_t* xs, const int32_t* ids,
                  const float* w, uint32_t rows, uint16_t* bf16_out, float* partial_out, Status* status,
@@ -404,7 +410,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
     const int skip_foreign = ep ? 1 : 0;
     const TokenSources src = ep ? ep->src : TokenSources{};
-    if (rows <= kSmallRows && !ep) {
+    if (rows <= kMediumRows && !ep) {
         // one launch: plan + (quantise) + gate + permutation; timed as the permutation, the plan slot reads zero
         if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
         SmallIo io{};
@@ -412,7 +418,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         io.xq_out = raw ? const_cast<uint8_t*>(xq) : nullptr; io.xs_out = raw ? const_cast<uint8_t*>(xs) : nullptr;
         io.x_perm = S->x_perm.as<uint8_t>(); io.sfb = S->sfb1.as<uint8_t>();
         io.fault_input = &status->fault_input; io.fault_quant = raw ? raw->fault_quant : nullptr;
-        const uint32_t grid = routes < uint32_t(S->sms) ? routes : uint32_t(S->sms);
+        const uint32_t grid = uint32_t(S->sms);
         const int sel = raw ? raw->codec * 2 + raw->dtype : 4;
         switch (sel) {
             case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
@@ -829,7 +835,7 @@ int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtyp
     const uint8_t* xq = static_cast<const uint8_t*>(x);
     const uint8_t* xs = x_scales;
     RawInput raw{x, x_dtype, codec, &status[1].fault_input};
-    const bool fused = rows <= kSmallRows;
+    const bool fused = rows <= kMediumRows;
     if (x_dtype != 2) {
         // the quantiser's fault word (second status block) is cleared together with the pass's own block
         cudaError_t e;

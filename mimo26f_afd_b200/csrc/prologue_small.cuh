@@ -1,8 +1,9 @@
-// Everything in front of the first GEMM in one launch, for requests of at most 32 tokens (decode).
+// Everything in front of the first GEMM in one launch, for requests of at most 128 tokens (decode, verify rounds).
 //
 // The separate quantiser, route planner and permutation are each a few microseconds of launch latency around
 // almost no work at this size, so here every CTA recomputes the whole route plan in shared memory (one thread per
-// route, 256 routes at most) and then produces its share of the grouped rows straight from the caller's activations:
+// route: 256 threads for up to 32 tokens, 1024 for up to 128) and then produces its share of the grouped rows straight
+// from the caller's activations, one row per 256 threads:
 // quantise (or take the caller's E4M3 bytes), gate, and write the row and its scale bytes where the FC1 kernel's
 // loads expect them. The plan tables themselves are written by CTAs 0..3, one table group each.
 //
@@ -13,7 +14,8 @@
 
 namespace m26b {
 
-constexpr uint32_t kSmallRows = 32;
+constexpr uint32_t kSmallRows = 32;      // one thread per route with 256 threads
+constexpr uint32_t kMediumRows = 128;    // ... with 1024 threads
 
 struct SmallIo {
     const void* x;           // IN 0: BF16 [rows][4096]; IN 1: FP32; IN 2: E4M3 payload
@@ -26,21 +28,23 @@ struct SmallIo {
     uint32_t* fault_quant;   // IN 0/1 with quant_v1: nonfinite / overflow
 };
 
-template <int CODEC, int IN>
-__global__ void __launch_bounds__(256) small_prologue_kernel(SmallIo io, const int32_t* __restrict__ ids,
+template <int CODEC, int IN, int THREADS>
+__global__ void __launch_bounds__(THREADS) small_prologue_kernel(SmallIo io, const int32_t* __restrict__ ids,
                                                              const float* __restrict__ w, uint32_t rows,
                                                              const uint8_t* __restrict__ resident, int max_n, int mt_fc1,
                                                              int mt_fc2, PlanOut o) {
-    __shared__ uint32_t wcnt[8][kExperts];
+    constexpr int kWarps = THREADS / 32;
+    constexpr uint32_t kRowsAtOnce = THREADS / 256;      // grouped rows a CTA produces side by side
+    __shared__ uint32_t wcnt[kWarps][kExperts];
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
     __shared__ uint32_t i1base[kExperts], i2base[kExperts];
     __shared__ uint32_t wsum[4][8];
     __shared__ uint32_t max_count;
-    __shared__ uint16_t row_tile[256];
-    __shared__ uint8_t row_token[256], row_lr[256], row_first[256];
+    __shared__ uint16_t row_tile[THREADS];
+    __shared__ uint8_t row_token[THREADS], row_lr[THREADS], row_first[THREADS];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, routes = rows * kTopK;
     grid_dep_launch();           // the FC1 kernel may set itself up meanwhile; it waits for this grid before it reads
-    for (uint32_t i = tid; i < 8 * kExperts; i += 256) (&wcnt[0][0])[i] = 0;
+    for (uint32_t i = tid; i < kWarps * kExperts; i += THREADS) (&wcnt[0][0])[i] = 0;
     if (tid == 0) max_count = 0;
     // ---- validate (the rules of plan_kernel) and count per (warp, expert)
     const bool live = tid < routes;
@@ -62,19 +66,22 @@ __global__ void __launch_bounds__(256) small_prologue_kernel(SmallIo io, const i
     const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
     if (live && rank == 0) wcnt[warp][e] = __popc(peers);
     __syncthreads();
-    // ---- thread = expert: totals, tile cuts, exclusive scans
-    uint32_t c = 0;
-    for (int wi = 0; wi < 8; ++wi) { const uint32_t t = wcnt[wi][tid]; wcnt[wi][tid] = c; c += t; }
-    const uint32_t n = c ? (c + max_n - 1) / max_n : 0;
-    const uint32_t per = n ? (c + n - 1) / n : 0;
-    cnt[tid] = c; ntl[tid] = n; width[tid] = (per + 15u) & ~15u;
-    atomicMax(&max_count, c);
-    const uint32_t v[4] = {c, n, n * uint32_t(mt_fc1), n * uint32_t(mt_fc2)};
-    uint32_t inc[4];
+    // ---- thread = expert (the first 256 threads): totals, tile cuts, exclusive scans
+    const bool is_expert = tid < uint32_t(kExperts);
+    uint32_t c = 0, n = 0;
+    uint32_t v[4] = {0, 0, 0, 0}, inc[4] = {0, 0, 0, 0};
+    if (is_expert) {
+        for (int wi = 0; wi < kWarps; ++wi) { const uint32_t t = wcnt[wi][tid]; wcnt[wi][tid] = c; c += t; }
+        n = c ? (c + max_n - 1) / max_n : 0;
+        const uint32_t per = n ? (c + n - 1) / n : 0;
+        cnt[tid] = c; ntl[tid] = n; width[tid] = (per + 15u) & ~15u;
+        atomicMax(&max_count, c);
+        v[0] = c; v[1] = n; v[2] = n * uint32_t(mt_fc1); v[3] = n * uint32_t(mt_fc2);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) { inc[k] = warp_inclusive_scan(v[k], lane); if (lane == 31) wsum[k][warp] = inc[k]; }
-    const uint32_t active = __syncthreads_count(c > 0);
-    {
+        for (int k = 0; k < 4; ++k) { inc[k] = warp_inclusive_scan(v[k], lane); if (lane == 31) wsum[k][warp] = inc[k]; }
+    }
+    const uint32_t active = __syncthreads_count(is_expert && c > 0);
+    if (is_expert) {
         uint32_t add[4] = {0, 0, 0, 0};
         for (uint32_t wi = 0; wi < warp; ++wi)
 #pragma unroll
@@ -103,41 +110,43 @@ __global__ void __launch_bounds__(256) small_prologue_kernel(SmallIo io, const i
         }
     }
     // ---- plan tables, one group per CTA (thread = expert)
-    if (blockIdx.x == 1u % gridDim.x) {
+    if (is_expert && blockIdx.x == 1u % gridDim.x) {
         o.experts[tid] = ExpertPlan{int32_t(c), int32_t(rbase[tid]), int32_t(tstart[tid]), int32_t(width[tid])};
         for (uint32_t j = 0; j < n; ++j) {
             const uint32_t wd = width[tid], nv = c - j * wd < wd ? c - j * wd : wd;
             o.tiles[tstart[tid] + j] = TokenTile{int32_t(tid), int32_t(rbase[tid] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
     }
-    if (blockIdx.x == 2u % gridDim.x)
+    if (is_expert && blockIdx.x == 2u % gridDim.x)
         for (uint32_t i = 0; i < n * uint32_t(mt_fc1); ++i)
             o.items_fc1[i1base[tid] + i] = WorkItem{int32_t(tstart[tid] + i % n), int32_t(i / n)};
-    if (blockIdx.x == 3u % gridDim.x)
+    if (is_expert && blockIdx.x == 3u % gridDim.x)
         for (uint32_t i = 0; i < n * uint32_t(mt_fc2); ++i)
             o.items_fc2[i2base[tid] + i] = WorkItem{int32_t(tstart[tid] + i % n), int32_t(i / n)};
     __syncthreads();
-    // ---- grouped rows: thread t holds elements [16 t, 16 t + 16), a K32 block is a pair of threads
+    // ---- grouped rows, kRowsAtOnce side by side: thread t of a row's 256 holds elements [16 t, 16 t + 16), a K32 block is
+    // a pair of threads. The bound is the same for every thread of a warp (a warp never straddles two rows).
     uint32_t bad_in = 0, bad_q = 0;
-    for (uint32_t g = blockIdx.x; g < routes; g += gridDim.x) {
+    const uint32_t sub = tid >> 8, rt = tid & 255u;
+    for (uint32_t g = blockIdx.x * kRowsAtOnce + sub; g < routes; g += gridDim.x * kRowsAtOnce) {
         const uint32_t token = row_token[g];
         uint32_t code[16];
         uint32_t sbyte = 0;
         bool write = true;
         if constexpr (IN == 2) {
-            const uint4 q = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(io.x) + size_t(token) * kHidden)[tid];
+            const uint4 q = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(io.x) + size_t(token) * kHidden)[rt];
             code[0] = q.x; code[1] = q.y; code[2] = q.z; code[3] = q.w;
-            sbyte = io.xs_in[size_t(token) * (kHidden / kBlockK) + (tid >> 1)];
+            sbyte = io.xs_in[size_t(token) * (kHidden / kBlockK) + (rt >> 1)];
         } else {
             uint32_t bits[16];
             if constexpr (IN == 0) {
-                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(io.x) + size_t(token) * kHidden) + 2 * tid;
+                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(io.x) + size_t(token) * kHidden) + 2 * rt;
                 const uint4 a = src[0], b = src[1];
                 const uint32_t wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) { bits[2 * i] = wv[i] << 16; bits[2 * i + 1] = wv[i] & 0xffff0000u; }
             } else {
-                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(io.x) + size_t(token) * kHidden) + 4 * tid;
+                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(io.x) + size_t(token) * kHidden) + 4 * rt;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint4 a = src[i];
@@ -185,14 +194,14 @@ __global__ void __launch_bounds__(256) small_prologue_kernel(SmallIo io, const i
             if ((((code[i] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) != 0u) bad_in = kFaultInputScale;
         if (sbyte < 105u || sbyte > 247u) bad_in = kFaultInputScale;
         const uint4 q = make_uint4(code[0], code[1], code[2], code[3]);
-        reinterpret_cast<uint4*>(io.x_perm + size_t(g) * kHidden)[tid] = q;
-        const uint32_t blk = tid >> 1;
-        if ((tid & 1u) == 0u)
+        reinterpret_cast<uint4*>(io.x_perm + size_t(g) * kHidden)[rt] = q;
+        const uint32_t blk = rt >> 1;
+        if ((rt & 1u) == 0u)
             io.sfb[(size_t(row_tile[g]) * (kHidden / kChunkK) + (blk >> 2)) * kScaleBlockBytes +
                    scale_block_offset(int(row_lr[g]), int(blk & 3u))] = uint8_t(sbyte);
         if (IN != 2 && io.xq_out && row_first[g]) {
-            reinterpret_cast<uint4*>(io.xq_out + size_t(token) * kHidden)[tid] = q;
-            if ((tid & 1u) == 0u) io.xs_out[size_t(token) * (kHidden / kBlockK) + blk] = uint8_t(sbyte);
+            reinterpret_cast<uint4*>(io.xq_out + size_t(token) * kHidden)[rt] = q;
+            if ((rt & 1u) == 0u) io.xs_out[size_t(token) * (kHidden / kBlockK) + blk] = uint8_t(sbyte);
         }
     }
     if (bad_in) atomicOr(io.fault_input, bad_in);

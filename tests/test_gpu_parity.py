@@ -479,9 +479,10 @@ def test_ffn_ragged_token_counts(layer, scratch, dev, oracle_mod, tokens):
     check_ffn(layer, scratch, dev, oracle_mod, tokens, 0.7, codec=0, seed=SEED + tokens)
 
 
-@pytest.mark.parametrize("tokens", [7, 32])
+@pytest.mark.parametrize("tokens", [7, 32, 33, 128])
 def test_small_request_prologue_input_forms_agree(layer, scratch, dev, oracle_mod, tokens):
-    """Requests of at most 32 tokens quantise, plan and permute in one launch. BF16 and FP32 activations (both codecs)
+    """Requests of at most 128 tokens quantise, plan and permute in one launch (256 threads per CTA up to 32 tokens,
+    1024 above). BF16 and FP32 activations (both codecs)
     and caller-quantised E4M3 rows must give the same bytes at every stage, and the quant_v1 faults must surface."""
     from mimo26f_afd_b200 import synth
     import mimo26f_afd_b200 as M
