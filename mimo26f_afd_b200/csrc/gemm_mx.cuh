@@ -141,12 +141,15 @@ __device__ long long g_gemm_timing[148 * 16];
 
 // E-ACT-CR32 activation: e = exp(-|g|) (never a positive exponential), s = g / (1 + e) or g e / (1 + e),
 // h = s u. The exponential and the reciprocal of 1 + e (which lies in [1, 2]) use the hardware
-// approximations: together under 1e-6 relative, inside the 1e-5 stage tolerance, at a fifth of the
-// instructions of expf and an IEEE divide. That matters: this runs once per intermediate element and the
-// epilogue must stay cheaper than the main loop it overlaps.
+// approximations (ex2.approx, rcp.approx: one instruction each, about one ulp): together under 1e-6 relative, inside
+// the 1e-5 stage tolerance, at a fifth of the instructions of expf and an IEEE divide. Measured against the oracle the
+// intermediate's relative L2 error is 1.3e-7 either way and the count of E4M3 bin crossings does not move; the
+// correctly rounded reciprocal cost FC1 3 % at prefill. This runs once per intermediate element and the kernel is at
+// the power limit, so every instruction here is clock.
 __device__ __forceinline__ float silu_mul(float g, float u) {
     const float e = __expf(-fabsf(g));
-    const float r = __frcp_rn(__fadd_rn(1.0f, e));
+    float r;
+    asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(__fadd_rn(1.0f, e)));
     const float num = g >= 0.0f ? g : __fmul_rn(g, e);
     return __fmul_rn(__fmul_rn(num, r), u);
 }
