@@ -479,6 +479,25 @@ def test_ffn_ragged_token_counts(layer, scratch, dev, oracle_mod, tokens):
     check_ffn(layer, scratch, dev, oracle_mod, tokens, 0.7, codec=0, seed=SEED + tokens)
 
 
+@pytest.mark.parametrize("tokens,cut,zipf", [(129, 1, 1.5), (130, 111, 0.5), (145, 61, 1.5), (513, 325, 0.0), (1025, 350, 1.5), (2469, 1206, 0.0)])
+def test_bytes_do_not_depend_on_the_batch_cut(layer, scratch, dev, oracle_mod, tokens, cut, zipf):
+    """A token's output bytes depend on its own row and routes only: the same tokens served as one batch or as two
+    give identical FP32 planes and BF16 rows, although the two forms take different paths (fused or general prologue,
+    one-CTA tiles of 16..128 rows or CTA-pair tiles of 256, different positions inside an expert's group). The sizes sit
+    on the edges of those classes. Plan indices are checked against the oracle at each size."""
+    from mimo26f_afd_b200 import synth
+
+    x_bits = synth.activations_bf16(SEED + tokens, tokens)
+    ids, w = synth.routing(SEED + tokens, tokens, zipf)
+    bf, part = run_dev(layer, scratch, dev, x_bits, ids, w)
+    st, oinv, _, _, _ = oracle_mod.plan(ids, w)
+    assert st == 0 and np.array_equal(scratch.peek("inverse", np.int32, (tokens * TOPK,)), oinv)
+    bf_a, part_a = run_dev(layer, scratch, dev, x_bits[:cut], ids[:cut], w[:cut])
+    bf_b, part_b = run_dev(layer, scratch, dev, x_bits[cut:], ids[cut:], w[cut:])
+    assert np.array_equal(np.concatenate([bf_a, bf_b]), bf)
+    assert np.array_equal(np.concatenate([part_a, part_b]).view(np.uint32), part.view(np.uint32))
+
+
 @pytest.mark.parametrize("tokens", [7, 32, 33, 128])
 def test_small_request_prologue_input_forms_agree(layer, scratch, dev, oracle_mod, tokens):
     """Requests of at most 128 tokens quantise, plan and permute in one launch (256 threads per CTA up to 32 tokens,
