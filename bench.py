@@ -62,14 +62,54 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """SM clock and throttle reasons while the timed region runs: read through NVML every 2 ms (read-only queries), or,
+    where NVML cannot be loaded, from `nvidia-smi -lms 200`."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index):
-        self.rows, self.proc, self.index = [], None, index
+        self.rows, self.proc, self.index, self.nvml, self.stop = [], None, index, None, threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            import torch
+
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        return pynvml, handle
+
+    def _poll(self):
+        nv, h = self.nvml
+        bits = (nv.nvmlClocksThrottleReasonHwSlowdown, nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                nv.nvmlClocksThrottleReasonSwThermalSlowdown, nv.nvmlClocksThrottleReasonSwPowerCap)
+        top = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        while not self.stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                why = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.rows.append([str(mhz), str(top), "0"] + ["Active" if why & b else "Not Active" for b in bits])
+            except Exception:
+                break
+            self.stop.wait(0.002)
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
 
     def __enter__(self):
+        try:
+            self.nvml = self._nvml_handle()
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return self
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "200"],
@@ -80,12 +120,11 @@ class ClockSampler:
             self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
     def __exit__(self, *a):
-        if self.proc:
+        if self.nvml:
+            self.stop.set()
+            self.t.join(1.0)
+        elif self.proc:
             time.sleep(0.25)
             self.proc.terminate()
             self.proc.wait(5)
@@ -94,10 +133,9 @@ class ClockSampler:
         ok = [r for r in self.rows if len(r) >= 7 and r[0].isdigit()]
         if not ok:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in ok)]
+        reasons = [n for i, n in enumerate(self.NAMES) if any(r[3 + i].lower().startswith("active") for r in ok)]
         return dict(sm_mhz=float(np.median([int(r[0]) for r in ok])), sm_max_mhz=float(ok[0][1]), reasons=reasons,
-                    samples=len(ok))
+                    samples=len(ok), source="nvml" if self.nvml else "nvidia-smi")
 
 
 def cpu_reference_arm(args, rank):
@@ -259,11 +297,13 @@ def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
     for _ in range(max(args.warmup, 10) if tokens <= 128 else min(args.warmup, 3)):   # short calls: let clocks and the driver settle
         e2e_step()
     sync_all()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    with ClockSampler(dev.index or 0) as clocks_e2e:           # the end-to-end region is timed too: its samples join the record
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+    clocks.rows += clocks_e2e.rows
     t = torch.tensor([e2e_s], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -32,3 +32,23 @@ def test_gpu_arm_refuses_to_run_without_a_gpu():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--steps", "1", "--warmup", "3"], cwd=ROOT,
                        capture_output=True, text=True, timeout=600)
     assert r.returncode != 0 and "no CPU path" in (r.stderr + r.stdout)
+
+
+def test_clock_record_summary_from_fake_samples():
+    """The clock record of the JSON line: median SM clock, the maximum, and every throttle reason seen in any sample."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    argv, sys.argv = sys.argv, ["bench.py"]
+    try:
+        spec.loader.exec_module(bench)
+    finally:
+        sys.argv = argv
+    c = bench.ClockSampler(0)
+    assert c.summary()["samples"] == 0 and c.summary()["sm_mhz"] is None
+    quiet = ["Not Active"] * 4
+    c.rows = [["1965", "1965", "0"] + quiet, ["1410", "1965", "0"] + quiet[:3] + ["Active"], ["1350", "1965", "0"] + quiet,
+              ["garbage"]]
+    s = c.summary()
+    assert s["samples"] == 3 and s["sm_mhz"] == 1410.0 and s["sm_max_mhz"] == 1965.0 and s["reasons"] == ["sw_power_cap"]
