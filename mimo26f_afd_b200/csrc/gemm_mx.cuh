@@ -179,8 +179,12 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    grid_dep_wait();             // the plan and the token rows come from the kernels before this one
-    grid_dep_launch();
+    // The plan and the token rows come from the kernels before this one. FC2's producer warp waits later: the route plan
+    // is older than the FC1 launch in front of it (FC1 let this grid start only after its own wait on the plan's
+    // kernels), and the weights are static, so the weight half of its first stages is requested while FC1 still runs
+    // on other SMs; only the intermediate rows and their scales need FC1 to be complete.
+    constexpr bool kEarlyWeights = MODE == kModeFc2;
+    if (!(kEarlyWeights && warp == 0)) { grid_dep_wait(); grid_dep_launch(); }
     const uint32_t tb = s.tmem_base;
     const uint32_t n_items = *p.n_items;
     M26B_TDECL;
@@ -195,6 +199,23 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int i = 0; i < 4; ++i) tma_prefetch_desc(&maps_x.box[i]);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            int early = 0;       // chunks of the first item whose weight boxes and weight scales are already in flight
+            if constexpr (kEarlyWeights) {
+                if (blockIdx.x < n_items) {
+                    const ItemInfo cur = load_item(p, blockIdx.x, n_items);
+                    const int slot = (cur.tt.expert - p.expert_base) * p.m_tiles + cur.wi.m_tile;
+                    const uint8_t* sfa_g = p.sfa + size_t(slot) * p.k_chunks * 2 * kScaleBlockBytes;
+                    const uint32_t tx = kPairM * 64 + cur.tt.n_mma * 128 + 3 * kScaleBlockBytes;
+                    early = p.k_chunks < STAGES ? p.k_chunks : STAGES;       // every stage is free at the start
+                    for (int c = 0; c < early; ++c) {
+                        mbar_expect_tx(&s.full[c], tx);                       // the whole stage: the token half follows below
+                        tma_load_2d(s.a[c], &map_w, c * kChunkK, slot * kPairM, &s.full[c]);
+                        bulk_load(s.sfa[c], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[c]);
+                    }
+                }
+                grid_dep_wait();
+                grid_dep_launch();
+            }
                         for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
                 const ItemInfo cur = load_item(p, it, n_items);
                 const WorkItem wi = cur.wi;
@@ -204,11 +225,15 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
                 const uint32_t tx = kPairM * 64 + tt.n_mma * 128 + 3 * kScaleBlockBytes;
                 for (int c = 0; c < p.k_chunks; ++c) {
-                    M26B_T0(tw);
-                    if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-                    M26B_ACC(0, tw);
-                    mbar_expect_tx(&s.full[stage], tx);
-                    tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
+                    const bool weights_in_flight = kEarlyWeights && it == blockIdx.x && c < early;
+                    if (!weights_in_flight) {
+                        M26B_T0(tw);
+                        if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                        M26B_ACC(0, tw);
+                        mbar_expect_tx(&s.full[stage], tx);
+                        tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
+                        bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
+                    }
                     int r = 0;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -218,7 +243,6 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             r += rows;
                         }
                     }
-                    bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
                     bulk_load(s.sfb[stage], sfb_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
