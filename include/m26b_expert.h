@@ -36,7 +36,8 @@ typedef struct m26b_scratch m26b_scratch;
 /* Replaces m26s_b1_layer_new (b1_serve.cu:218-265): prepare one layer from the
  * reference's canonical-v2 rank image in device memory, 256 experts x 3,342,336
  * bytes, rank 0..3 of TP4 (crates/mimo26-repack/src/geom.rs:36-50). The image
- * may be freed after the call returns. */
+ * may be freed after the call returns. Every m26b_layer_new* call first waits for all work queued on the current
+ * device (cudaDeviceSynchronize), so source tensors produced on any stream are complete before they are repacked. */
 int m26b_layer_new(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t rank, m26b_layer** out,
                    char* err, size_t errlen);
 
@@ -118,6 +119,13 @@ enum {
     M26B_PEEK_PARTIAL = 9,         /* f32 [rows,4096] */
     M26B_PEEK_MID_SCALES = 10      /* u8 [routes,I_local/32] grouped order, row-major (gathered from the scale blocks) */
 };
+/* Route outputs (the FC2 rows the ordered combine reads) as FP32 (dtype 0, the default: the reference's lattice,
+ * bit-exact combine inputs) or BF16 (dtype 1): the reference's opt-in MIMO26_B1_Y=bf16
+ * (crates/mimo26-spark/kernels/b1_serve.cu:98-143 reduce_bf16y, 400-406): FC2 rounds each row to BF16 (nearest even),
+ * the combine widens them exactly and runs the same ordered multiply / add, fault rules and BF16 rounding. Halves
+ * FC2's write and the combine's read; not bit-identical to the FP32 mode. A scratch created while the environment
+ * holds MIMO26_B1_Y=bf16 starts in BF16 mode, as the reference's does. M26B_PEEK_Y then returns u16 [routes,4096]. */
+int m26b_scratch_set_route_output(m26b_scratch* scratch, int dtype);
 /* Per-kernel GPU time of the last pass in milliseconds, from CUDA events recorded on the launching stream
  * around each kernel when debug flag bit 1 (value 2) is set (the reference times its phases the same way,
  * b1_serve.cu:545-550): [0] input quantiser, [1] route plan, [2] permutation, [3] FC1 GEMM, [4] FC2 GEMM,
@@ -169,7 +177,10 @@ int m26b_produce_dev(const float* logits, const float* bias, uint32_t rows, int3
  *   connect_local: the same for windows of one process (`all` = world handles in rank order).
  *   plane:    device address the NEXT step's BF16 plane must be written to (alternates between the two slots).
  *   sum_dev:  n_elems a multiple of 8; out_f32 [n_elems] on this rank. Every rank must call it once per step.
- *   status:   0, or 5 when a wait ran out (the message names the ranks); the window stays usable.
+ *   status:   0, or 5 when a wait ran out (the message names the ranks). After code 5 the ranks are out of step: before
+ *             the next step every rank must reach a host-side barrier with its stream synchronised (the two-slot
+ *             scheme only protects a slot while every step's wait succeeds; a rank that keeps going after a lost
+ *             step can overwrite a plane a slow peer is still reading). The same holds for the m26b_ep_* rendezvous.
  *   set_wait_ms: the bound of the wait (default 2000 ms).
  *   publish_as: marks the next step as published by `peer_rank` from the host; for single-process tests and for a
  *             coordinator that stands in for a rank it knows to be idle. */
@@ -213,6 +224,9 @@ int m26b_ep_connect(m26b_ep* e, const uint8_t* handles, char* err, size_t errlen
 int m26b_ep_connect_local(m26b_ep* e, m26b_ep* const* all, char* err, size_t errlen);
 int m26b_ep_rows(const m26b_ep* e, uint32_t rank);
 int m26b_ep_set_wait_ms(m26b_ep* e, uint32_t ms);
+/* Result rows cross NVLink and are combined as FP32 (0, default) or BF16 (1), as m26b_scratch_set_route_output; every
+ * rank of a step must use the same setting. */
+int m26b_ep_set_route_output(m26b_ep* e, int dtype);
 int m26b_ep_publish_as(m26b_ep* e, uint32_t peer_rank, uint32_t which, void* stream, char* err, size_t errlen);
 int m26b_ep_begin_dev(m26b_ep* e, const void* x, int x_dtype, const uint8_t* x_scales, int codec, const int32_t* ids,
                       const float* weights, uint32_t rows, void* stream, char* err, size_t errlen);

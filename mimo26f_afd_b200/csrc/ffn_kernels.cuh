@@ -16,6 +16,68 @@ namespace m26b {
 // CODEC 0: wire codec (scale byte 0 for a zero block, ties away from zero).
 // CODEC 1: quant_v1 (floor 1e-4, ties to even, faults instead of clipping; a
 // faulting block writes nothing), crates/mimo26-expert/kernels/b1/quant_v1.cu:34-59.
+// Sixteen consecutive elements starting at element 16 g (half a K32 block; the other half is lane ^ 1's): the packed
+// payload, the block's scale byte and whether the block may be written; faults are ORed into `bad`. Every lane of the
+// warp must call it (the halves meet by shuffle); `live` = this lane's elements exist.
+template <int CODEC, typename IN>
+__device__ __forceinline__ bool quant16(const IN* __restrict__ x, uint64_t g, bool live, uint4& out, uint32_t& sbyte, uint32_t& bad) {
+    uint32_t bits[16];
+    if (live) {
+        if constexpr (sizeof(IN) == 2) {
+            const uint4 a = reinterpret_cast<const uint4*>(x)[2 * g], b = reinterpret_cast<const uint4*>(x)[2 * g + 1];
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { bits[2 * i] = w[i] << 16; bits[2 * i + 1] = w[i] & 0xffff0000u; }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 a = reinterpret_cast<const uint4*>(x)[4 * g + i];
+                bits[4 * i] = a.x; bits[4 * i + 1] = a.y; bits[4 * i + 2] = a.z; bits[4 * i + 3] = a.w;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) bits[i] = 0;
+    }
+    uint32_t amax = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        uint32_t m = bits[i] & 0x7fffffffu;
+        if (CODEC == 0 && m > 0x7f800000u) m = 0;   // the wire codec's maximum skips NaN
+        amax = m > amax ? m : amax;
+    }
+    const uint32_t o = __shfl_xor_sync(0xffffffffu, amax, 1);
+    amax = o > amax ? o : amax;
+    uint32_t code[16];
+    bool write = live;
+    if constexpr (CODEC == 0) {
+        sbyte = wire_scale_byte(amax);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) code[i] = wire_payload(bits[i], sbyte);
+    } else {
+        bool over = false;
+        if (amax >= 0x7f800000u) {
+            if (live) bad |= kFaultQuantNonfinite;
+            write = false;
+            sbyte = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) code[i] = 0;
+        } else {
+            const int k = quant_v1_scale_exp(amax);
+            sbyte = uint32_t(k + 127);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { code[i] = quant_v1_payload(bits[i], k); over |= !quant_v1_finite(code[i], k); }
+        }
+        uint32_t ov = over ? 1u : 0u;
+        ov |= __shfl_xor_sync(0xffffffffu, ov, 1);
+        if (ov) { if (live) bad |= kFaultQuantOverflow; write = false; }
+    }
+    out.x = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
+    out.y = code[4] | (code[5] << 8) | (code[6] << 16) | (code[7] << 24);
+    out.z = code[8] | (code[9] << 8) | (code[10] << 16) | (code[11] << 24);
+    out.w = code[12] | (code[13] << 8) | (code[14] << 16) | (code[15] << 24);
+    return write;
+}
 template <int CODEC, typename IN>
 __device__ __forceinline__ void quantize_span(const IN* __restrict__ x, uint64_t n_elems, uint8_t* __restrict__ payload,
                                               uint8_t* __restrict__ scales, uint32_t* __restrict__ fault, uint64_t first,
@@ -24,65 +86,9 @@ __device__ __forceinline__ void quantize_span(const IN* __restrict__ x, uint64_t
     uint32_t bad = 0;
     // the bound is rounded up to a whole warp so every lane reaches the shuffles
     for (uint64_t g = first; g < ((n16 + 31) & ~uint64_t(31)); g += stride) {
-        uint32_t bits[16];
-        const bool live = g < n16;
-        if (live) {
-            if constexpr (sizeof(IN) == 2) {
-                const uint4 a = reinterpret_cast<const uint4*>(x)[2 * g], b = reinterpret_cast<const uint4*>(x)[2 * g + 1];
-                const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { bits[2 * i] = w[i] << 16; bits[2 * i + 1] = w[i] & 0xffff0000u; }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint4 a = reinterpret_cast<const uint4*>(x)[4 * g + i];
-                    bits[4 * i] = a.x; bits[4 * i + 1] = a.y; bits[4 * i + 2] = a.z; bits[4 * i + 3] = a.w;
-                }
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) bits[i] = 0;
-        }
-        uint32_t amax = 0;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            uint32_t m = bits[i] & 0x7fffffffu;
-            if (CODEC == 0 && m > 0x7f800000u) m = 0;   // the wire codec's maximum skips NaN
-            amax = m > amax ? m : amax;
-        }
-        const uint32_t o = __shfl_xor_sync(0xffffffffu, amax, 1);
-        amax = o > amax ? o : amax;
-        uint32_t code[16];
+        uint4 out;
         uint32_t sbyte;
-        bool write = live;
-        if constexpr (CODEC == 0) {
-            sbyte = wire_scale_byte(amax);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) code[i] = wire_payload(bits[i], sbyte);
-        } else {
-            bool over = false;
-            if (amax >= 0x7f800000u) {
-                if (live) bad |= kFaultQuantNonfinite;
-                write = false;
-                sbyte = 0;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) code[i] = 0;
-            } else {
-                const int k = quant_v1_scale_exp(amax);
-                sbyte = uint32_t(k + 127);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) { code[i] = quant_v1_payload(bits[i], k); over |= !quant_v1_finite(code[i], k); }
-            }
-            uint32_t ov = over ? 1u : 0u;
-            ov |= __shfl_xor_sync(0xffffffffu, ov, 1);
-            if (ov) { if (live) bad |= kFaultQuantOverflow; write = false; }
-        }
-        if (write) {
-            uint4 out;
-            out.x = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
-            out.y = code[4] | (code[5] << 8) | (code[6] << 16) | (code[7] << 24);
-            out.z = code[8] | (code[9] << 8) | (code[10] << 16) | (code[11] << 24);
-            out.w = code[12] | (code[13] << 8) | (code[14] << 16) | (code[15] << 24);
+        if (quant16<CODEC, IN>(x, g, g < n16, out, sbyte, bad)) {
             reinterpret_cast<uint4*>(payload)[g] = out;
             if ((g & 1) == 0) scales[g >> 1] = uint8_t(sbyte);
         }
@@ -380,6 +386,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
     __shared__ uint32_t i1base[kExperts], i2base[kExperts];
     __shared__ uint32_t wsum[4][8];
+    __shared__ uint32_t part_sum[4][kExperts];
     __shared__ uint32_t max_count;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     if (o.meta->fault) {   // uniform: written by the previous launch
@@ -388,9 +395,28 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_
     }
     if (tid == 0) max_count = 0;
     __syncthreads();
+    // per-(CTA, expert) counts -> exclusive offsets over the CTAs: thread (expert, quarter) scans a quarter of the CTAs
+    // from registers (all its loads in flight at once), the quarters meet in shared memory
+    {
+        const uint32_t e = tid & (kExperts - 1u), part = tid >> 8;
+        const uint32_t per = (n_cta + 3u) / 4u, k0 = part * per;
+        uint32_t v[32];
+#pragma unroll
+        for (uint32_t i = 0; i < 32; ++i) v[i] = (i < per && k0 + i < n_cta) ? cta_cnt[(k0 + i) * kExperts + e] : 0u;
+        uint32_t sum = 0;
+#pragma unroll
+        for (uint32_t i = 0; i < 32; ++i) sum += v[i];
+        part_sum[part][e] = sum;
+        __syncthreads();
+        uint32_t run = 0;
+        for (uint32_t q = 0; q < part; ++q) run += part_sum[q][e];
+#pragma unroll
+        for (uint32_t i = 0; i < 32; ++i)
+            if (i < per && k0 + i < n_cta) { cta_cnt[(k0 + i) * kExperts + e] = run; run += v[i]; }
+    }
     uint32_t c = 0, n = 0;
     if (tid < kExperts) {
-        for (uint32_t k = 0; k < n_cta; ++k) { const uint32_t t = cta_cnt[k * kExperts + tid]; cta_cnt[k * kExperts + tid] = c; c += t; }
+        c = part_sum[0][tid] + part_sum[1][tid] + part_sum[2][tid] + part_sum[3][tid];
         n = c ? (c + max_n - 1) / max_n : 0;
         const uint32_t per = n ? (c + n - 1) / n : 0;
         cnt[tid] = c; ntl[tid] = n; width[tid] = (per + 15u) & ~15u;
@@ -533,6 +559,63 @@ __global__ void __launch_bounds__(256) permute_kernel(const uint8_t* __restrict_
     if (bad) atomicOr(fault, bad);
 }
 
+// Quantiser and permutation in one pass, for requests that arrive as BF16 / FP32 rows and are too large for the fused
+// small prologue: one CTA per token row quantises it once in registers (thread t holds elements 16 t .. 16 t + 15), writes
+// the quantised row and its scales in request order (what the stage dumps and the parity tests read), and copies both into
+// the row's eight places of the expert-sorted operand (x_perm rows, token-tile scale blocks). Against the two separate
+// passes this saves one write and one read of the quantised rows and one launch. The input gate of the permutation
+// applies to what the quantiser produced: a zero block under the wire codec (scale byte 0) raises kFaultInputScale.
+template <int CODEC, typename IN>
+__global__ void __launch_bounds__(256) quantize_permute_kernel(const IN* __restrict__ x, uint32_t rows, const int32_t* __restrict__ ids,
+                                                               const int32_t* __restrict__ inverse,
+                                                               const ExpertPlan* __restrict__ experts,
+                                                               const PlanMeta* __restrict__ meta, uint8_t* __restrict__ xq,
+                                                               uint8_t* __restrict__ xs, uint8_t* __restrict__ x_perm,
+                                                               uint8_t* __restrict__ sfb, uint32_t* __restrict__ fault_quant,
+                                                               uint32_t* __restrict__ fault_input) {
+    __shared__ uint32_t dst_row[kTopK], dst_tile[kTopK], dst_lr[kTopK];
+    const bool planned = meta->fault == 0;     // a rejected plan leaves no valid route tables: quantise only
+    uint32_t bad_q = 0, bad_in = 0;
+    for (uint32_t token = blockIdx.x; token < rows; token += gridDim.x) {
+        if (planned && threadIdx.x < uint32_t(kTopK)) {
+            const uint32_t route = token * kTopK + threadIdx.x;
+            const uint32_t p = uint32_t(inverse[route]);
+            const ExpertPlan ep = experts[ids[route]];
+            const uint32_t local = p - uint32_t(ep.rbase);
+            dst_row[threadIdx.x] = p;
+            dst_tile[threadIdx.x] = uint32_t(ep.tile_start) + local / uint32_t(ep.width);
+            dst_lr[threadIdx.x] = local % uint32_t(ep.width);
+        }
+        uint4 out;
+        uint32_t sbyte;
+        const uint64_t g = uint64_t(token) * (kHidden / 16) + threadIdx.x;
+        const bool write = quant16<CODEC, IN>(x, g, true, out, sbyte, bad_q);
+        __syncthreads();
+        if (write) {
+            const uint32_t wv[4] = {out.x, out.y, out.z, out.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if ((((wv[i] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) != 0u) bad_in = kFaultInputScale;
+            if (sbyte < 105 || sbyte > 247) bad_in = kFaultInputScale;
+            reinterpret_cast<uint4*>(xq)[g] = out;
+            const uint32_t blk = threadIdx.x >> 1;                  // K32 block of the row; the even thread stores its scale
+            if ((threadIdx.x & 1u) == 0) xs[size_t(token) * (kHidden / kBlockK) + blk] = uint8_t(sbyte);
+            if (planned) {
+#pragma unroll
+                for (int j = 0; j < kTopK; ++j) {
+                    reinterpret_cast<uint4*>(x_perm + size_t(dst_row[j]) * kHidden)[threadIdx.x] = out;
+                    if ((threadIdx.x & 1u) == 0)
+                        sfb[(size_t(dst_tile[j]) * (kHidden / kChunkK) + (blk >> 2)) * kScaleBlockBytes +
+                            scale_block_offset(int(dst_lr[j]), int(blk & 3u))] = uint8_t(sbyte);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (bad_q) atomicOr(fault_quant, bad_q);
+    if (bad_in) atomicOr(fault_input, bad_in);
+}
+
 // ---------------------------------------------------------------- combine
 // Per (token, column): v = 0; v = add(v, mul(w_j, y_j)) for slot j = 0..7 with
 // separate round-to-nearest multiply and add, then BF16 round-to-nearest-even
@@ -574,6 +657,54 @@ __global__ void __launch_bounds__(256) route_reduce_kernel(const float* __restri
         }
         if (partial) reinterpret_cast<float4*>(partial)[i] = make_float4(v[0], v[1], v[2], v[3]);
         reinterpret_cast<uint2*>(bf16)[i] = make_uint2(code[0] | (code[1] << 16), code[2] | (code[3] << 16));
+    }
+    if (__syncthreads_or(failed) && threadIdx.x == 0) atomicOr(fault, uint32_t(kFaultReduce));
+}
+
+// The same combine over BF16 route outputs (the route-output option; the reference's opt-in reduce_bf16y,
+// crates/mimo26-spark/kernels/b1_serve.cu:98-143): each y is a BF16 value widened exactly to FP32, then the same
+// ordered multiply / add, fault rules and BF16 rounding. Eight columns per thread (16-byte loads).
+__global__ void __launch_bounds__(256) route_reduce_y16_kernel(const uint16_t* __restrict__ y, const float* __restrict__ w,
+                                                               uint32_t rows, float* __restrict__ partial,
+                                                               uint16_t* __restrict__ bf16, uint32_t* __restrict__ fault) {
+    const float kMax = 3.402823466e+38f;
+    const uint64_t n8 = uint64_t(rows) * (kHidden / 8);
+    bool failed = false;
+    grid_dep_wait();             // y comes from the FC2 kernel
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint64_t row = i / (kHidden / 8), c8 = i % (kHidden / 8);
+        uint4 z[kTopK];
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) z[j] = reinterpret_cast<const uint4*>(y)[(row * kTopK + j) * (kHidden / 8) + c8];
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) {
+            const float wt = w[row * kTopK + j];
+            ok = ok && wt >= 0.0f && wt <= kMax;
+            const uint32_t words[4] = {z[j].x, z[j].y, z[j].z, z[j].w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float zv = __uint_as_float((k & 1) ? (words[k / 2] & 0xffff0000u) : (words[k / 2] << 16));
+                ok = ok && zv >= -kMax && zv <= kMax;
+                v[k] = __fadd_rn(v[k], __fmul_rn(wt, zv));
+                ok = ok && v[k] >= -kMax && v[k] <= kMax;
+            }
+        }
+        uint32_t code[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { code[k] = bf16_rne_bits(v[k]); ok = ok && (code[k] & 0x7f80u) != 0x7f80u; }
+        if (!ok) {
+            failed = true;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { code[k] = 0; v[k] = __int_as_float(0x7fc00000); }
+        }
+        if (partial) {
+            reinterpret_cast<float4*>(partial)[2 * i] = make_float4(v[0], v[1], v[2], v[3]);
+            reinterpret_cast<float4*>(partial)[2 * i + 1] = make_float4(v[4], v[5], v[6], v[7]);
+        }
+        reinterpret_cast<uint4*>(bf16)[i] = make_uint4(code[0] | (code[1] << 16), code[2] | (code[3] << 16),
+                                                       code[4] | (code[5] << 16), code[6] | (code[7] << 16));
     }
     if (__syncthreads_or(failed) && threadIdx.x == 0) atomicOr(fault, uint32_t(kFaultReduce));
 }

@@ -73,10 +73,10 @@ struct GemmArgs {
     // FC1 epilogue
     uint8_t* mid_q;             // [grouped rows][i_local] E4M3
     uint8_t* mid_sf;            // scale blocks for FC2 [tile][i_local/128][512]
-    float* mid_f32;             // optional FP32 copy of silu(gate)*up, same indexing as mid_q
+    float* mid_f32;             // FP32 copy of silu(gate)*up, same indexing as mid_q (stage-dump instantiations only)
     int i_local;
     // FC2 epilogue
-    float* y;                   // [routes][4096] FP32, original route order
+    float* y;                   // [routes][4096] FP32 (BF16 with the route-output option), original route order
     const int32_t* original_routes;
     int expert_base;            // first expert of the weight image (a layer may hold a contiguous subset of the experts)
     RouteSinks sinks;
@@ -94,15 +94,24 @@ __device__ __forceinline__ ItemInfo load_item(const GemmArgs& p, uint32_t it, ui
     return r;
 }
 
-// Row of the FC2 output for a route of the pass.
-__device__ __forceinline__ float* y_row(const GemmArgs& p, int32_t route) {
-    if (p.sinks.n == 0) return p.y + size_t(route) * kHidden;
+// Row of the FC2 output for a route of the pass. Rows are FP32, or BF16 with the route-output option (Y16): the
+// reference's MIMO26_B1_Y=bf16 mode, crates/mimo26-spark/kernels/b1_serve.cu:400-406.
+template <bool Y16>
+__device__ __forceinline__ uint8_t* y_row(const GemmArgs& p, int32_t route) {
+    constexpr size_t kRowBytes = size_t(kHidden) * (Y16 ? 2 : 4);
+    if (p.sinks.n == 0) return reinterpret_cast<uint8_t*>(p.y) + size_t(route) * kRowBytes;
     const uint32_t token = p.sinks.token_base + uint32_t(route) / kTopK, slot = uint32_t(route) % kTopK;
     uint32_t k = 0;
 #pragma unroll
     for (uint32_t i = 1; i < 8; ++i)
         if (i < p.sinks.n && token >= p.sinks.lo[i]) k = i;
-    return p.sinks.y[k] + (size_t(token - p.sinks.lo[k]) * kTopK + slot) * kHidden;
+    return reinterpret_cast<uint8_t*>(p.sinks.y[k]) + (size_t(token - p.sinks.lo[k]) * kTopK + slot) * kRowBytes;
+}
+// One FC2 output element of column `col` into the row at `row`.
+template <bool Y16>
+__device__ __forceinline__ void y_store(unsigned long long row, uint32_t col, uint32_t f32_bits) {
+    if constexpr (Y16) reinterpret_cast<uint16_t*>(row)[col] = uint16_t(bf16_rne_bits(__uint_as_float(f32_bits)));
+    else reinterpret_cast<float*>(row)[col] = __uint_as_float(f32_bits);
 }
 
 // Token-operand tensor maps with boxes of 128, 64, 32 and 16 rows: a tile's rows are fetched with the fewest
@@ -123,22 +132,6 @@ struct GemmSmem {
     uint32_t abort_flag;
 };
 
-#ifdef M26B_GEMM_TIMING
-__device__ long long g_gemm_timing[148 * 16];
-#define M26B_TDECL long long m26b_tacc[16] = {}
-#define M26B_T0(v) const long long v = clock64()
-#define M26B_ACC(slot, v) m26b_tacc[slot] += clock64() - (v)
-#define M26B_TFLUSH                                                                                              \
-    _Pragma("unroll") for (int ts = 0; ts < 16; ++ts) if (m26b_tacc[ts])                                         \
-        atomicAdd(reinterpret_cast<unsigned long long*>(&g_gemm_timing[blockIdx.x * 16 + ts]),                  \
-                  static_cast<unsigned long long>(m26b_tacc[ts]))
-#else
-#define M26B_TDECL
-#define M26B_T0(v)
-#define M26B_ACC(slot, v)
-#define M26B_TFLUSH
-#endif
-
 // E-ACT-CR32 activation: e = exp(-|g|) (never a positive exponential), s = g / (1 + e) or g e / (1 + e),
 // h = s u. The exponential and the reciprocal of 1 + e (which lies in [1, 2]) use the hardware
 // approximations (ex2.approx, rcp.approx: one instruction each, about one ulp): together under 1e-6 relative, inside
@@ -157,7 +150,8 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 static_assert(sizeof(GemmSmem<32, 6>) + 1024 <= 232448 && sizeof(GemmSmem<kMaxN, 4>) + 1024 <= 232448,
               "a CTA has at most 227 KB of shared memory");
 
-template <int MODE, int B_ROWS, int STAGES>
+// DUMP: also store the FP32 intermediate (stage dumps of the parity tests). Y16: FC2 rows as BF16.
+template <int MODE, int B_ROWS, int STAGES, bool DUMP = false, bool Y16 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_x, const GemmArgs p) {
     using Smem = GemmSmem<B_ROWS, STAGES>;
@@ -186,9 +180,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     constexpr bool kEarlyWeights = MODE == kModeFc2;
     if (!(kEarlyWeights && warp == 0)) { grid_dep_wait(); grid_dep_launch(); }
     const uint32_t tb = s.tmem_base;
-    const uint32_t n_items = *p.n_items;
-    M26B_TDECL;
-    M26B_T0(t_all);
+    // FC2's producer warp has not waited for its predecessors yet: it reads the plan around L1 (the plan is older than
+    // the FC1 launch in front of this grid, but only the wait makes earlier grids' writes visible to cached loads).
+    const uint32_t n_items = (kEarlyWeights && warp == 0) ? __ldcv(p.n_items) : *p.n_items;
     volatile uint32_t* abort_flag = &s.abort_flag;
 
     if (warp == 0) {
@@ -202,7 +196,13 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int early = 0;       // chunks of the first item whose weight boxes and weight scales are already in flight
             if constexpr (kEarlyWeights) {
                 if (blockIdx.x < n_items) {
-                    const ItemInfo cur = load_item(p, blockIdx.x, n_items);
+                    ItemInfo cur{};
+                    {   // the same two records load_item() reads, around L1
+                        const int2 wi = __ldcv(reinterpret_cast<const int2*>(p.items) + blockIdx.x);
+                        const int4 tt = __ldcv(reinterpret_cast<const int4*>(p.tiles) + wi.x);
+                        cur.wi = WorkItem{wi.x, wi.y};
+                        cur.tt = TokenTile{tt.x, tt.y, tt.z, tt.w};
+                    }
                     const int slot = (cur.tt.expert - p.expert_base) * p.m_tiles + cur.wi.m_tile;
                     const uint8_t* sfa_g = p.sfa + size_t(slot) * p.k_chunks * 2 * kScaleBlockBytes;
                     const uint32_t tx = kPairM * 64 + cur.tt.n_mma * 128 + 3 * kScaleBlockBytes;
@@ -227,9 +227,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int c = 0; c < p.k_chunks; ++c) {
                     const bool weights_in_flight = kEarlyWeights && it == blockIdx.x && c < early;
                     if (!weights_in_flight) {
-                        M26B_T0(tw);
                         if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-                        M26B_ACC(0, tw);
                         mbar_expect_tx(&s.full[stage], tx);
                         tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
                         bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
@@ -265,16 +263,12 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const TokenTile tt = cur.tt;
                 const uint32_t idesc0 = idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), 0, 0);
                 // the accumulators are free once every epilogue warp has pulled its slice of the previous item
-                M26B_T0(ta);
                 const uint32_t aset = local % kAccSets, ause = local / kAccSets;
                 if (!mbar_wait(&s.acc_empty[aset], (ause & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-                M26B_ACC(2, ta);
                 tc_fence_after();
                 const uint32_t d0 = tb + aset * B_ROWS, d1 = d0 + kAcc1;
                 for (int c = 0; c < p.k_chunks; ++c) {
-                    M26B_T0(tf);
                     if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
-                    M26B_ACC(1, tf);
                     tc_fence_after();
                     // consecutive chunks alternate between two scale slots in tensor memory
                     const uint32_t t_sf = tb + kSfSlot0 + sf_slot * kSfSlotStride;
@@ -316,14 +310,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             unsigned long long row_lo = 0, row_hi = 0;
             if constexpr (MODE == kModeFc2) {
                 const int t = (int(wq >> 1) + 2 * (lane >> 3)) * 8 + (lane & 7);
-                if (t < tt.n_valid) row_lo = reinterpret_cast<unsigned long long>(y_row(p, p.original_routes[tt.row_base + t]));
-                if (t + 64 < tt.n_valid) row_hi = reinterpret_cast<unsigned long long>(y_row(p, p.original_routes[tt.row_base + t + 64]));
+                if (t < tt.n_valid) row_lo = reinterpret_cast<unsigned long long>(y_row<Y16>(p, p.original_routes[tt.row_base + t]));
+                if (t + 64 < tt.n_valid) row_hi = reinterpret_cast<unsigned long long>(y_row<Y16>(p, p.original_routes[tt.row_base + t + 64]));
             }
-            M26B_T0(te);
             const uint32_t aset = local % kAccSets, ause = local / kAccSets;
             if (!mbar_wait(&s.acc_full[aset], ause & 1u, abort_flag)) { ok = false; break; }
-            if (warp == 2 && lane == 0) { M26B_ACC(3, te); }
-            M26B_T0(tc);
             tc_fence_after();
             const uint32_t t_acc = tb + ((q * 32u) << 16) + aset * B_ROWS;
             if constexpr (MODE == kModeFc2) {
@@ -347,7 +338,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const unsigned long long row = __shfl_sync(0xffffffffu, g < 4 ? row_lo : row_hi, (g & 3) * 8 + j);
-                        if (row) reinterpret_cast<float*>(row)[ycol] = __uint_as_float(r[g][j]);
+                        if (row) y_store<Y16>(row, ycol, r[g][j]);
                     }
                 }
             } else {
@@ -369,7 +360,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int feat0 = wi.m_tile * kTileM + int(q) * 32;
                 uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + wi.m_tile) * kScaleBlockBytes;
                 uint8_t* mq = p.mid_q + size_t(tt.row_base) * p.i_local + feat0 + lane;
-                float* mf = p.mid_f32 ? p.mid_f32 + size_t(tt.row_base) * p.i_local + feat0 + lane : nullptr;
+                float* mf = DUMP ? p.mid_f32 + size_t(tt.row_base) * p.i_local + feat0 + lane : nullptr;
                 uint32_t fault = 0;
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
@@ -379,7 +370,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int t = c0 + j;
                         if (t >= tt.n_valid) continue;   // warp-uniform
                         const float h = silu_mul(__uint_as_float(gt[g][j]), __uint_as_float(up[g][j]));
-                        if (mf) mf[size_t(t) * p.i_local] = h;
+                        if constexpr (DUMP) mf[size_t(t) * p.i_local] = h;
                         const uint32_t bits = __float_as_uint(h);
                         const uint32_t amax = __reduce_max_sync(0xffffffffu, bits & 0x7fffffffu);
                         if (amax >= 0x7f800000u) { fault |= kFaultQuantNonfinite; continue; }
@@ -393,14 +384,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (fault && lane == 0) atomicOr(p.fault, fault);
             }
-            if (warp == 2 && lane == 0) { M26B_ACC(4, tc); }
         }
         if (!ok && lane == 0) atomicOr(p.fault, uint32_t(kFaultPipeline));
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) { M26B_ACC(5, t_all); }
-    M26B_TFLUSH;
     if (warp == 1) tmem_dealloc(tb, kTmemCols);
 }
 

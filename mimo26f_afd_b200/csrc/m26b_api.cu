@@ -86,13 +86,13 @@ cudaError_t launch_dependent(void (*kernel)(P...), unsigned grid, unsigned block
     return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
 }
 
-template <int MODE, int B_ROWS, int STAGES>
+template <int MODE, int B_ROWS, int STAGES, bool DUMP, bool Y16>
 cudaError_t launch_gemm(const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
     const int smem = int(sizeof(GemmSmem<B_ROWS, STAGES>)) + 1024;
-    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES>,
+    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return launch_dependent(gemm_mx_kernel<MODE, B_ROWS, STAGES>, unsigned(ctas), kGemmThreads, size_t(smem), st, mw, mx, a);
+    return launch_dependent(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16>, unsigned(ctas), kGemmThreads, size_t(smem), st, mw, mx, a);
 }
 // Scale blocks as a 2-D tensor of 128 x u32 rows (one 512-byte block per row), no swizzle.
 bool make_sf_map(CUtensorMap* m, const void* base, uint64_t blocks, uint32_t box_rows) {
@@ -106,12 +106,19 @@ bool make_sf_map(CUtensorMap* m, const void* base, uint64_t blocks, uint32_t box
              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MODE>
+template <int MODE, bool DUMP, bool Y16>
 cudaError_t launch_gemm_pair(const CUtensorMap& mw, const PairMaps& maps, const GemmArgs& a, int ctas, cudaStream_t st) {
     const int smem = int(sizeof(PairSmem)) + 1024;
-    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_pair_kernel<MODE, DUMP, Y16>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return launch_dependent(gemm_mx_pair_kernel<MODE>, unsigned(ctas & ~1), kGemmThreads, size_t(smem), st, mw, maps, a);
+    return launch_dependent(gemm_mx_pair_kernel<MODE, DUMP, Y16>, unsigned(ctas & ~1), kPairThreads, size_t(smem), st, mw, maps, a);
+}
+cudaError_t launch_fc1_pair(bool dump, const CUtensorMap& mw, const PairMaps& maps, const GemmArgs& a, int ctas, cudaStream_t st) {
+    return dump ? launch_gemm_pair<kModeFc1, true, false>(mw, maps, a, ctas, st) : launch_gemm_pair<kModeFc1, false, false>(mw, maps, a, ctas, st);
+}
+cudaError_t launch_fc2_pair(bool y16, const CUtensorMap& mw, const PairMaps& maps, const GemmArgs& a, int ctas, cudaStream_t st) {
+    return y16 ? launch_gemm_pair<kModeFc2, false, true>(mw, maps, a, ctas, st) : launch_gemm_pair<kModeFc2, false, false>(mw, maps, a, ctas, st);
 }
 
 // How many CTAs of the pair kernels can be resident at once (2 x the co-resident clusters, at most one per SM).
@@ -120,20 +127,20 @@ cudaError_t launch_gemm_pair(const CUtensorMap& mw, const PairMaps& maps, const 
 template <int MODE>
 int pair_resident_ctas(int sms) {
     const int smem = int(sizeof(PairSmem)) + 1024;
-    if (cudaFuncSetAttribute(gemm_mx_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_mx_pair_kernel<MODE, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(sms & ~1));
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(kPairThreads);
     cfg.dynamicSmemBytes = size_t(smem);
     cudaLaunchAttribute at{};
     at.id = cudaLaunchAttributeClusterDimension;
     at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
     cfg.attrs = &at; cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_mx_pair_kernel<MODE>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_mx_pair_kernel<MODE, false, false>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -149,11 +156,14 @@ constexpr size_t kStageBytes = size_t(kStageRows) * (kHidden + kHidden / kBlockK
 // Requests above this many tokens run the CTA-pair kernels (prefill); below, the single-CTA kernels (decode).
 constexpr uint32_t kPairMinRows = 129;
 
+// The single-CTA kernels by launch class; `variant` = the FP32 stage dump for FC1, BF16 route outputs for FC2.
 template <int MODE>
-cudaError_t launch_gemm_class(uint32_t rows, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas,
+cudaError_t launch_gemm_class(uint32_t rows, bool variant, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas,
                               cudaStream_t st) {
-    if (rows <= 32) return launch_gemm<MODE, 32, 6>(mw, mx, a, ctas, st);
-    return launch_gemm<MODE, kMaxN, 4>(mw, mx, a, ctas, st);
+    constexpr bool kFc1 = MODE == kModeFc1;
+    if (rows <= 32)
+        return variant ? launch_gemm<MODE, 32, 6, kFc1, !kFc1>(mw, mx, a, ctas, st) : launch_gemm<MODE, 32, 6, false, false>(mw, mx, a, ctas, st);
+    return variant ? launch_gemm<MODE, kMaxN, 4, kFc1, !kFc1>(mw, mx, a, ctas, st) : launch_gemm<MODE, kMaxN, 4, false, false>(mw, mx, a, ctas, st);
 }
 
 // Device status block of one pass: PlanMeta then four fault words.
@@ -195,6 +205,7 @@ struct m26b_ep {
     uint32_t tokens = 0;                 // tokens of a step, over all ranks
     uint32_t lo[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // token block of rank r: [lo[r], lo[r + 1])
     uint32_t step = 0;
+    bool y16 = false;                    // result rows travel and are combined as BF16
     long long wait_cycles = 0;
     Dev ids, w;                          // every rank's routes, request order
     uint32_t* fault = nullptr;           // device word: quantiser / combine faults of the step
@@ -209,6 +220,7 @@ struct m26b_scratch {
     int device = 0, sms = 0;
     int pair_ctas = 0;          // resident CTAs of the pair kernels (0: the device cannot run them)
     uint32_t debug = 0;
+    bool y16 = false;           // route outputs (FC2 rows) as BF16 instead of FP32
     Dev xq, xs, iw, dstage, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
         partial, bf16, status, gather, plan_cnt;
     TokenMaps map_x, map_mid;
@@ -220,7 +232,7 @@ struct m26b_scratch {
     uint8_t* hstage = nullptr;       // pinned: rows, scales, ids and weights of a small request, uploaded in one copy
     Status* hstatus = nullptr;       // pinned
     // last pass
-    uint32_t last_rows = 0; int last_i_local = 0; bool pending = false; uint32_t n_status = 0;
+    uint32_t last_rows = 0; int last_i_local = 0; bool pending = false; uint32_t n_status = 0; bool last_y16 = false;
     const int32_t* last_ids = nullptr; const uint8_t* last_xq = nullptr; const uint8_t* last_xs = nullptr;
 };
 
@@ -229,6 +241,12 @@ namespace {
 int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, uint32_t tp_rank, uint32_t tp_size,
                   m26b_layer** out, char* err, size_t errlen, int expert_lo = 0, int n_local = kExperts) {
     const int i_local = kInter / int(tp_size);
+    // The repack kernels below run on the default stream and take no stream argument: whatever produced the source
+    // tensors, on any stream of this device, is waited for here (this runs once per layer, off the serving path).
+    {
+        const cudaError_t se = cudaDeviceSynchronize();
+        if (se != cudaSuccess) { set_err(err, errlen, "m26b layer: waiting for the source tensors", se); return 2; }
+    }
     auto* L = new m26b_layer();
     L->i_local = i_local; L->tp_rank = tp_rank; L->tp_size = tp_size;
     L->expert_lo = expert_lo; L->n_local = n_local;
@@ -360,7 +378,8 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
     return 0;
 }
 
-// Activations that are not quantised yet (requests of at most kMediumRows tokens quantise inside the fused prologue).
+// Activations that are not quantised yet: requests of at most kMediumRows tokens quantise inside the fused prologue,
+// larger ones inside the permutation pass.
 struct RawInput {
     const void* x;
     int dtype, codec;          // 0 BF16 / 1 FP32; 0 wire / 1 quant_v1
@@ -383,11 +402,12 @@ void launch_small_prologue(uint32_t sms, cudaStream_t st, const SmallIo& io, con
 struct EpPass {
     TokenSources src;
     RouteSinks sinks;
+    bool y16;
 };
 
-// Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine. `raw` (only with at most
-// kMediumRows rows) names activations still to be quantised into xq / xs; `status_cleared`: the caller has already
-// zeroed the status block on the stream.
+// Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine. `raw` names activations still to be
+// quantised into xq / xs (not with expert parallelism); `status_cleared`: the caller has already zeroed the status
+// block on the stream.
 int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const uint8_t* xs, const int32_t* ids,
                  const float* w, uint32_t rows, uint16_t* bf16_out, float* partial_out, Status* status,
                  cudaStream_t st, bool events, char* err, size_t errlen, const RawInput* raw = nullptr,
@@ -400,11 +420,9 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (events) M26B_CK(cudaEventRecord(S->e0, st), "m26b event 0");
     PlanOut po{S->inverse.as<int32_t>(), S->original.as<int32_t>(), S->gweights.as<float>(), S->experts.as<ExpertPlan>(),
                S->tiles.as<TokenTile>(), S->items1.as<WorkItem>(), S->items2.as<WorkItem>(), &status->meta};
-#ifdef M26B_GEMM_TIMING
-    const bool pair = rows >= kPairMinRows && (mt1 % 2 == 0) && S->pair_ctas >= S->sms / 2 && !getenv("M26B_NO_PAIR");
-#else
     const bool pair = rows >= kPairMinRows && (mt1 % 2 == 0) && S->pair_ctas >= S->sms / 2;
-#endif
+    const bool dump = (S->debug & 1u) != 0;
+    const bool y16 = ep ? ep->y16 : S->y16;
     const int m_step = pair ? 2 : 1;
     const bool kt = (S->debug & 2u) != 0;
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
@@ -443,10 +461,27 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         }
         M26B_CK(cudaGetLastError(), "m26b plan launch");
         if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
-        permute_kernel<<<routes < 65535u * 8u ? routes : 65535u * 8u, 256, 0, st>>>(
-            xq, xs, ids, S->original.as<int32_t>(), S->experts.as<ExpertPlan>(), &status->meta, routes,
-            S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input, src);
-        M26B_CK(cudaGetLastError(), "m26b permute launch");
+        if (raw) {
+            // activations still to be quantised: quantiser and permutation in one pass over the rows
+            uint8_t* xq_w = const_cast<uint8_t*>(xq);
+            uint8_t* xs_w = const_cast<uint8_t*>(xs);
+            const int32_t* inv = S->inverse.as<int32_t>();
+            const ExpertPlan* ex = S->experts.as<ExpertPlan>();
+            uint8_t* xp = S->x_perm.as<uint8_t>();
+            uint8_t* sf = S->sfb1.as<uint8_t>();
+            switch (raw->codec * 2 + raw->dtype) {
+                case 0: quantize_permute_kernel<0, uint16_t><<<rows, 256, 0, st>>>(static_cast<const uint16_t*>(raw->x), rows, ids, inv, ex, &status->meta, xq_w, xs_w, xp, sf, raw->fault_quant, &status->fault_input); break;
+                case 1: quantize_permute_kernel<0, float><<<rows, 256, 0, st>>>(static_cast<const float*>(raw->x), rows, ids, inv, ex, &status->meta, xq_w, xs_w, xp, sf, raw->fault_quant, &status->fault_input); break;
+                case 2: quantize_permute_kernel<1, uint16_t><<<rows, 256, 0, st>>>(static_cast<const uint16_t*>(raw->x), rows, ids, inv, ex, &status->meta, xq_w, xs_w, xp, sf, raw->fault_quant, &status->fault_input); break;
+                default: quantize_permute_kernel<1, float><<<rows, 256, 0, st>>>(static_cast<const float*>(raw->x), rows, ids, inv, ex, &status->meta, xq_w, xs_w, xp, sf, raw->fault_quant, &status->fault_input); break;
+            }
+            M26B_CK(cudaGetLastError(), "m26b quantise+permute launch");
+        } else {
+            permute_kernel<<<routes < 65535u * 8u ? routes : 65535u * 8u, 256, 0, st>>>(
+                xq, xs, ids, S->original.as<int32_t>(), S->experts.as<ExpertPlan>(), &status->meta, routes,
+                S->x_perm.as<uint8_t>(), S->sfb1.as<uint8_t>(), &status->fault_input, src);
+            M26B_CK(cudaGetLastError(), "m26b permute launch");
+        }
     }
     if (kt) M26B_CK(cudaEventRecord(S->kev[3], st), "m26b event");
     GemmArgs a{};
@@ -454,7 +489,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     a.i_local = L->i_local;
     a.mid_q = S->mid_q.as<uint8_t>();
     a.mid_sf = S->mid_sf.as<uint8_t>();
-    a.mid_f32 = (S->debug & 1u) ? S->mid_f32.as<float>() : nullptr;
+    a.mid_f32 = dump ? S->mid_f32.as<float>() : nullptr;
     a.y = S->y.as<float>();
     a.original_routes = S->original.as<int32_t>();
     a.expert_base = L->expert_lo;
@@ -466,9 +501,9 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (pair) {
         PairMaps pm = S->pair_x;
         pm.sfa = L->map_s13;
-        M26B_CK(launch_gemm_pair<kModeFc1>(L->map_w13, pm, a, S->pair_ctas, st), "m26b fc1 launch");
+        M26B_CK(launch_fc1_pair(dump, L->map_w13, pm, a, S->pair_ctas, st), "m26b fc1 launch");
     } else {
-        M26B_CK(launch_gemm_class<kModeFc1>(rows, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
+        M26B_CK(launch_gemm_class<kModeFc1>(rows, dump, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
     }
     if (events) M26B_CK(cudaEventRecord(S->ea, st), "m26b event a");
     if (kt) M26B_CK(cudaEventRecord(S->kev[4], st), "m26b event");
@@ -479,19 +514,28 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (pair) {
         PairMaps pm = S->pair_mid;
         pm.sfa = L->map_s2;
-        M26B_CK(launch_gemm_pair<kModeFc2>(L->map_w2, pm, a, S->pair_ctas, st), "m26b fc2 launch");
+        M26B_CK(launch_fc2_pair(y16, L->map_w2, pm, a, S->pair_ctas, st), "m26b fc2 launch");
     } else {
-        M26B_CK(launch_gemm_class<kModeFc2>(rows, L->map_w2, S->map_mid, a, S->sms, st), "m26b fc2 launch");
+        M26B_CK(launch_gemm_class<kModeFc2>(rows, y16, L->map_w2, S->map_mid, a, S->sms, st), "m26b fc2 launch");
     }
     if (events) M26B_CK(cudaEventRecord(S->ec, st), "m26b event c");
     if (kt) M26B_CK(cudaEventRecord(S->kev[5], st), "m26b event");
-    const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
-    const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
-    if (!ep)   // an expert-parallel pass leaves its rows with the tokens' owners; they combine after the step's rendezvous
-        M26B_CK(launch_dependent(route_reduce_kernel, blocks, 256u, size_t(0), st, static_cast<const float*>(S->y.as<float>()), w,
-                                 rows, partial_out, bf16_out, &status->fault_reduce), "m26b reduce launch");
+    if (!ep) {   // an expert-parallel pass leaves its rows with the tokens' owners; they combine after the step's rendezvous
+        if (y16) {
+            const uint64_t n8 = uint64_t(rows) * (kHidden / 8);
+            const uint32_t blocks = uint32_t(n8 / 256 + 1 < 16384 ? n8 / 256 + 1 : 16384);
+            M26B_CK(launch_dependent(route_reduce_y16_kernel, blocks, 256u, size_t(0), st, static_cast<const uint16_t*>(S->y.as<uint16_t>()), w,
+                                     rows, partial_out, bf16_out, &status->fault_reduce), "m26b reduce launch");
+        } else {
+            const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
+            const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
+            M26B_CK(launch_dependent(route_reduce_kernel, blocks, 256u, size_t(0), st, static_cast<const float*>(S->y.as<float>()), w,
+                                     rows, partial_out, bf16_out, &status->fault_reduce), "m26b reduce launch");
+        }
+    }
     if (events) M26B_CK(cudaEventRecord(S->e1, st), "m26b event 1");
     if (kt) { M26B_CK(cudaEventRecord(S->kev[6], st), "m26b event"); S->kev_valid = true; }
+    S->last_y16 = y16;
     S->last_rows = rows; S->last_i_local = L->i_local; S->last_ids = ids; S->last_xq = xq; S->last_xs = xs;
     return 0;
 }
@@ -528,16 +572,6 @@ bool device_ok(int dev_of_handle, char* err, size_t errlen) {
 extern "C" {
 
 const char* m26b_version(void) { return "m26b-expert 0.1 sm_100a"; }
-
-#ifdef M26B_GEMM_TIMING
-// working-build only: read and clear the per-CTA cycle counters of the GEMM roles
-int m26b_debug_timing(long long* out, int clear) {
-    cudaDeviceSynchronize();
-    if (out) cudaMemcpyFromSymbol(out, m26b::g_gemm_timing, sizeof(long long) * 148 * 16);
-    if (clear) { static long long z[148 * 16] = {}; cudaMemcpyToSymbol(m26b::g_gemm_timing, z, sizeof z); }
-    return 0;
-}
-#endif
 
 int m26b_layer_new_tp(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t tp_rank, uint32_t tp_size,
                       m26b_layer** out, char* err, size_t errlen) {
@@ -632,11 +666,13 @@ int m26b_scratch_new(m26b_scratch** out, char* err, size_t errlen) {
     }
     S->sms = prop.multiProcessorCount;
     {
+        // the reference's opt-in for BF16 route outputs, read where it reads it (b1_serve.cu:402-405)
+        const char* v = std::getenv("MIMO26_B1_Y");
+        S->y16 = v && std::strcmp(v, "bf16") == 0;
+    }
+    {
         const int c1 = pair_resident_ctas<kModeFc1>(S->sms), c2 = pair_resident_ctas<kModeFc2>(S->sms);
         S->pair_ctas = c1 < c2 ? c1 : c2;
-#ifdef M26B_GEMM_TIMING
-        std::fprintf(stderr, "m26b: %d SMs, %d resident pair CTAs\n", S->sms, S->pair_ctas);
-#endif
     }
     if ((e = cudaStreamCreateWithFlags(&S->st, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaEventCreate(&S->e0)) != cudaSuccess || (e = cudaEventCreate(&S->e1)) != cudaSuccess ||
@@ -671,6 +707,12 @@ int m26b_scratch_set_debug(m26b_scratch* S, uint32_t flags) {
     return 0;
 }
 
+int m26b_scratch_set_route_output(m26b_scratch* S, int dtype) {
+    if (!S || dtype < 0 || dtype > 1) return 1;
+    S->y16 = dtype == 1;
+    return 0;
+}
+
 int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_t payload_pitch, const uint8_t* scales,
              size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows, uint16_t* bf16_out, float* ms,
              char* err, size_t errlen) {
@@ -682,6 +724,7 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     if (!device_ok(L->device, err, errlen) || !device_ok(S->device, err, errlen)) return 1;
     cudaError_t e;
     const auto t0 = std::chrono::steady_clock::now();
+    S->kev_quant = false;          // this entry point takes quantised rows: the quantiser slot of the timings reads zero
     const size_t routes = size_t(rows) * kTopK;
     const uint32_t pass_rows = rows < kMaxPassRows ? rows : kMaxPassRows;
     const uint32_t passes = (rows + kMaxPassRows - 1) / kMaxPassRows;
@@ -756,7 +799,9 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
         }
         ms[0] = std::chrono::duration<float, std::milli>(t1 - t0).count();
         ms[1] = gpu_ms;
-        ms[2] = std::chrono::duration<float, std::milli>(t2 - t1).count() - gpu_ms;
+        // what the host waited beyond the GPU's own time (the GPU starts before t1, so the difference can fall below zero)
+        const float tail = std::chrono::duration<float, std::milli>(t2 - t1).count() - gpu_ms;
+        ms[2] = tail > 0.f ? tail : 0.f;
         ms[3] = float(S->hstatus[0].meta.n_tiles);
         ms[4] = p1; ms[5] = 0.f; ms[6] = p2; ms[7] = p3;
     }
@@ -835,22 +880,17 @@ int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtyp
     const uint8_t* xq = static_cast<const uint8_t*>(x);
     const uint8_t* xs = x_scales;
     RawInput raw{x, x_dtype, codec, &status[1].fault_input};
-    const bool fused = rows <= kMediumRows;
     if (x_dtype != 2) {
-        // the quantiser's fault word (second status block) is cleared together with the pass's own block
+        // the quantiser's fault word (second status block) is cleared together with the pass's own block; the quantiser
+        // itself runs inside the pass (fused prologue, or the quantise-and-permute kernel)
         cudaError_t e;
         M26B_CK(cudaMemsetAsync(status, 0, 2 * sizeof(Status), st), "m26b status clear");
         if (S->debug & 2u) M26B_CK(cudaEventRecord(S->kev[0], st), "m26b event");
-        if (!fused) {
-            rc = m26b_quantize_dev(x, x_dtype, uint64_t(rows) * kHidden, codec, S->xq.as<uint8_t>(), S->xs.as<uint8_t>(),
-                                   &status[1].fault_input, st, err, errlen);
-            if (rc) return rc;
-        }
         xq = S->xq.as<uint8_t>(); xs = S->xs.as<uint8_t>();
     }
     S->kev_quant = x_dtype != 2;
     rc = enqueue_pass(L, S, xq, xs, ids, weights, rows, bf16_out, partial_out ? partial_out : nullptr, status, st, false,
-                      err, errlen, (x_dtype != 2 && fused) ? &raw : nullptr, x_dtype != 2);
+                      err, errlen, x_dtype != 2 ? &raw : nullptr, x_dtype != 2);
     if (rc) return rc;
     S->pending = true;
     S->n_status = x_dtype != 2 ? 2 : 1;
@@ -1114,6 +1154,12 @@ int m26b_ep_connect_local(m26b_ep* E, m26b_ep* const* all, char* err, size_t err
 
 int m26b_ep_rows(const m26b_ep* E, uint32_t rank) { return E && int(rank) < E->world ? int(E->lo[rank + 1] - E->lo[rank]) : -1; }
 
+int m26b_ep_set_route_output(m26b_ep* E, int dtype) {
+    if (!E || dtype < 0 || dtype > 1) return 1;
+    E->y16 = dtype == 1;
+    return 0;
+}
+
 int m26b_ep_set_wait_ms(m26b_ep* E, uint32_t ms) {
     if (!E || !ms) return 1;
     E->wait_cycles = (long long)ms * E->khz;
@@ -1177,6 +1223,7 @@ int m26b_ep_compute_dev(m26b_ep* E, const m26b_layer* L, m26b_scratch* S, void* 
     if (passes > 64) { set_msg(err, errlen, "m26b ep compute: too many tokens"); return 1; }
     int rc = ensure_pass(S, pass_rows, L->i_local, false, err, errlen);
     if (rc) return rc;
+    S->kev_quant = false;
     TokenSources shards{};
     shards.n = uint32_t(E->world);
     RouteSinks sinks{};
@@ -1193,7 +1240,7 @@ int m26b_ep_compute_dev(m26b_ep* E, const m26b_layer* L, m26b_scratch* S, void* 
     M26B_CK(cudaGetLastError(), "m26b ep gather launch");
     for (uint32_t ps = 0; ps < passes; ++ps) {
         const uint32_t r0 = ps * kMaxPassRows, n = E->tokens - r0 < kMaxPassRows ? E->tokens - r0 : kMaxPassRows;
-        EpPass pass{shards, sinks};
+        EpPass pass{shards, sinks, E->y16};
         pass.src.token_base = r0; pass.sinks.token_base = r0;
         rc = enqueue_pass(L, S, nullptr, nullptr, E->ids.as<int32_t>() + size_t(r0) * kTopK, E->w.as<float>() + size_t(r0) * kTopK, n,
                           nullptr, nullptr, S->status.as<Status>() + ps, st, false, err, errlen, nullptr, false, &pass);
@@ -1212,11 +1259,18 @@ int m26b_ep_finish_dev(m26b_ep* E, uint16_t* bf16_out, float* partial_out, void*
     if (!device_ok(E->device, err, errlen)) return 1;
     const uint32_t rows = E->lo[E->rank + 1] - E->lo[E->rank];
     if (!rows) return 0;
-    const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
-    const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
-    route_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const float*>(ep_ptr(E, E->rank, E->lay.y_off())), reinterpret_cast<const float*>(ep_ptr(E, E->rank, E->lay.w_off())),
-        rows, partial_out, bf16_out, E->fault);
+    const float* wts = reinterpret_cast<const float*>(ep_ptr(E, E->rank, E->lay.w_off()));
+    if (E->y16) {
+        const uint64_t n8 = uint64_t(rows) * (kHidden / 8);
+        const uint32_t blocks = uint32_t(n8 / 256 + 1 < 16384 ? n8 / 256 + 1 : 16384);
+        route_reduce_y16_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const uint16_t*>(ep_ptr(E, E->rank, E->lay.y_off())), wts, rows, partial_out, bf16_out, E->fault);
+    } else {
+        const uint64_t n4 = uint64_t(rows) * (kHidden / 4);
+        const uint32_t blocks = uint32_t(n4 / 256 + 1 < 16384 ? n4 / 256 + 1 : 16384);
+        route_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const float*>(ep_ptr(E, E->rank, E->lay.y_off())), wts, rows, partial_out, bf16_out, E->fault);
+    }
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, errlen, "m26b ep reduce launch", e); return 2; }
     return 0;
@@ -1513,7 +1567,7 @@ int m26b_scratch_peek(m26b_scratch* S, int what, void* host_dst, uint64_t bytes,
         case M26B_PEEK_X_SCALES: src = S->last_xs; have = rows * (kHidden / kBlockK); break;
         case M26B_PEEK_MID_PAYLOAD: src = S->mid_q.p; have = routes * il; break;
         case M26B_PEEK_MID_F32: src = (S->debug & 1u) ? S->mid_f32.p : nullptr; have = routes * il * 4; break;
-        case M26B_PEEK_Y: src = S->y.p; have = routes * kHidden * 4; break;
+        case M26B_PEEK_Y: src = S->y.p; have = routes * kHidden * (S->last_y16 ? 2 : 4); break;
         case M26B_PEEK_PARTIAL: src = S->partial.p; have = rows * kHidden * 4; break;
         case M26B_PEEK_MID_SCALES: {
             // gather the scale blocks back to row-major [routes][il/32] on the host

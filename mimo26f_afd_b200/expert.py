@@ -123,6 +123,12 @@ class Scratch:
     def set_debug(self, flags: int) -> None:
         _native.lib().m26b_scratch_set_debug(self._h, flags)
 
+    def set_route_output(self, bf16: bool) -> None:
+        """FC2 rows as BF16 instead of FP32 (the reference's opt-in ``MIMO26_B1_Y=bf16``, b1_serve.cu:400-406):
+        half the FC2 write and combine read, not bit-identical to the FP32 mode."""
+        if _native.lib().m26b_scratch_set_route_output(self._h, 1 if bf16 else 0):
+            raise ExpertError(1, "m26b scratch: bad route-output type")
+
     def status(self, stream=None) -> None:
         """Wait for the last ``ffn_dev`` on this scratch and raise on a plan or numerical fault."""
         err = C.create_string_buffer(256)
@@ -341,6 +347,11 @@ class ExpertParallel:
 
     def set_wait_ms(self, ms: int) -> None:
         _native.lib().m26b_ep_set_wait_ms(self._h, ms)
+
+    def set_route_output(self, bf16: bool) -> None:
+        """Result rows cross NVLink and are combined as BF16 instead of FP32; every rank must use the same setting."""
+        if _native.lib().m26b_ep_set_route_output(self._h, 1 if bf16 else 0):
+            raise ExpertError(1, "m26b ep: bad route-output type")
 
     def publish_as(self, peer_rank: int, which: int, stream=None) -> None:
         err = C.create_string_buffer(256)
