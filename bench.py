@@ -6,19 +6,26 @@
 
 A step is one pass of the hot path over one batch of seeded synthetic input: activation quantisation, route plan,
 token permutation, grouped gate/up GEMM + SwiGLU + intermediate quantiser, grouped down GEMM, ordered top-8
-combine. The headline workload (`value`) is BASELINE.json configs[1], the 16-token decode batch; the same JSON
-line carries the 8,192-token prefill segment (configs[3]) under "prefill". Weights are resident in HBM, inputs are
-resident in HBM for `value`, and on the host (pinned) for `e2e`, which goes through the reference-compatible
-host entry point m26b_ffn with both copies inside the timed region.
+combine (and, with N > 1 ranks, the exchange between the GPUs). The headline workload (`value`) is the 16-token
+decode batch; the same JSON line carries the 128-token verify round, the 8,192-token prefill segment and, on several
+GPUs, the 65,536-token batch, each under its own key. Weights are resident in HBM; inputs are resident in HBM for
+`value` and in pinned host memory for `e2e`, which goes through the library's host entry points (m26b_ffn, m26b_ffn_tp,
+m26b_ep_ffn) with both copies inside the timed region.
 
-The timed region is `steps` plain steps (one CUDA-event pair around each, nothing inside, so consecutive kernels
-overlap their launch and set-up as they do in service). The same steps then run once more with an event between
-every two kernels; those per-kernel durations feed `roofline` and `kernels_ms`, and that slower step time is
-reported beside the plain one as `ms_per_step_with_kernel_events`.
+Timing discipline (after the reference's own bench, crates/mimo26-expert/tests/b1_core/bench_connected.cuh:21-88): warm-up,
+then K samples (31 by default), each preceded by a barrier over the ranks, a device synchronisation and an L2 flush and
+bracketed by CUDA events on the launching stream; a sample's time is the maximum over the ranks; the median is reported
+with min / max / mean and the spread between ranks; correctness is checked before AND after the timed region, and an
+identity record (GPU, SMs, commit, command, seed) goes with every line. No events sit inside a timed step (they would
+break the overlap of consecutive kernels); per-kernel durations for the roofline come from a few extra instrumented steps.
 
 With N > 1 ranks the layer is tensor-parallel over the intermediate dimension (the reference's own TP4 scheme,
-generalised): every rank runs the whole batch on its 1/N slice of every expert and the BF16 partial planes are
-exchanged with one NCCL all-gather and summed in rank order on every rank. Total work is fixed: "strong" scaling.
+generalised): every rank runs the whole batch on its 1/N slice of every expert and the BF16 partial planes are summed in
+rank order by one kernel per rank that reads the peers' planes over NVLink (--exchange nccl: an NCCL all-gather followed
+by the sum kernel). Prefill-sized batches are also run expert-parallel (rank r holds 256 / N experts and 1 / N of the
+tokens). Total work is fixed as N grows: strong scaling. Before and after timing every rank checks that the peer
+exchange and the NCCL path give identical bits, rank 0 checks the sum against the CPU oracle, and the expert-parallel
+step is compared bit for bit with the single-GPU layer; a mismatch ends the run with a non-zero exit code.
 
 --impl reference times the reference's CPU expert path (the port in oracle/oracle.c of
 crates/mimo26-spark/src/main.rs:75-95) on the host cores, on a bounded sample of the same workload.
@@ -39,18 +46,23 @@ sys.path.insert(0, ROOT)
 H, I, E, TOPK = 4096, 2048, 256, 8
 EXPERT_BYTES = 13369344                     # 3 x 2048 x 4096 x 17/32 (payload + scales)
 FLOP_PER_TOKEN = 402653184                  # 3 GEMMs x 2 x 4096 x 2048 x top-8
-MXF8F6F4_PEAK_TFLOPS = 4450.0               # measured on this pool: profiles/mxf8f6f4_mma_rate.md (burst, small codes)
-MXF8F6F4_RANDOM_BURST_TFLOPS = 3694.0       # same probe on random operands, first 7 ms launch
+MXF8F6F4_PEAK_TFLOPS = 4450.0               # tcgen05 kind::mxf8f6f4 dense rate measured on this pool (burst, operands of a few small codes)
+MXF8F6F4_RANDOM_BURST_TFLOPS = 3694.0       # same instruction stream on random operands, first 7 ms launch
 MXF8F6F4_RANDOM_SUSTAINED_TFLOPS = 3193.0   # same, after three seconds (1.32 GHz under the 1000 W limit)
-# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch at N = 1, from the ncu captures summarised in
-# profiles/gemm_mx_decode16.md and profiles/gemm_mx_prefill8k.md (the seeded workloads are the same every run)
-FC1_TRAFFIC_BYTES = {"decode16": 915809536, "prefill8k": 2774330624}
 WORKLOADS = {
-    "decode16": dict(tokens=16, zipf=0.0, desc="16-token decode batch, uniform routing (BASELINE configs[1])"),
-    "prefill8k": dict(tokens=8192, zipf=0.0, desc="8192-token prefill segment, uniform routing (BASELINE configs[3])"),
-    "prefill64k": dict(tokens=65536, zipf=1.0, desc="65536-token batch, Zipf(1.0) expert popularity (BASELINE configs[4]; "
-                                                     "expert-parallel only: --parallel ep with --gpus 2/4/8)"),
+    "decode16": dict(tokens=16, zipf=0.0, desc="16-token decode batch, uniform routing"),
+    "verify128": dict(tokens=128, zipf=1.2, desc="speculative verify round: 16 streams x 8 tokens, Zipf(1.2) expert popularity"),
+    "prefill8k": dict(tokens=8192, zipf=0.0, desc="8192-token prefill segment, uniform routing"),
+    "prefill64k": dict(tokens=65536, zipf=1.0, desc="65536-token batch, Zipf(1.0) expert popularity"),
 }
+
+
+def workload_config(name):
+    """The `config` of a JSON line: the workload only, identical for both arms of the benchmark."""
+    wl = WORKLOADS[name]
+    return dict(workload=name, description=wl["desc"], tokens=wl["tokens"], top_k=TOPK, experts=E, hidden=H, intermediate=I,
+                routing="uniform" if not wl["zipf"] else f"zipf{wl['zipf']}", activations="bf16 N(0,1)",
+                weights="MXFP4 (E2M1 + UE8M0 per 32), scale bytes 118..122", input_codec="wire (FP8 E4M3 + UE8M0 K32)")
 
 
 def measured_peaks():
@@ -59,6 +71,36 @@ def measured_peaks():
         p = json.load(open(path))
         return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]), source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+def profiled_traffic():
+    """DRAM bytes per launch of the dominant kernel from the committed ncu captures (profiles/traffic.json, written next
+    to the summaries it comes from); {} when the file is absent."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        return json.load(open(path))
+    except (OSError, ValueError):
+        return {}
+
+
+def identity(args, dev=None):
+    rec = dict(command=" ".join([os.path.basename(sys.executable)] + sys.argv), seed=hex(0x26AFD), host_cores=os.cpu_count())
+    try:
+        rec["commit"] = subprocess.run(["git", "-C", ROOT, "rev-parse", "--short", "HEAD"], capture_output=True, text=True, timeout=5).stdout.strip() or None
+    except Exception:
+        rec["commit"] = None
+    if dev is not None:
+        import torch
+
+        p = torch.cuda.get_device_properties(dev)
+        rec.update(gpu=p.name, sms=p.multi_processor_count, arch=f"sm_{p.major}{p.minor}", hbm_gib=round(p.total_memory / 2 ** 30, 1),
+                   torch=torch.__version__, cuda=torch.version.cuda)
+    return rec
+
+
+def stats(ms):
+    a = np.asarray(ms, dtype=np.float64)
+    return dict(median=float(np.median(a)), min=float(a.min()), max=float(a.max()), mean=float(a.mean()), samples=int(a.size))
 
 
 class ClockSampler:
@@ -138,6 +180,8 @@ class ClockSampler:
                     samples=len(ok), source="nvml" if self.nvml else "nvidia-smi")
 
 
+
+
 def cpu_reference_arm(args, rank):
     """The reference's CPU expert path on the host cores, bounded sample of the headline workload."""
     if rank != 0:
@@ -150,8 +194,9 @@ def cpu_reference_arm(args, rank):
     wl = WORKLOADS[args.workload]
     seed, tokens = synth.MASTER_SEED, wl["tokens"]
     ids, w = synth.routing(seed, tokens, wl["zipf"])
-    x = synth.bf16_to_f32_np(synth.activations_bf16(seed, tokens))
+    x = synth.bf16_to_f32_np(synth.activations_bf16(seed, min(tokens, 8192)))
     xq, xs = oracle.quant_wire(x)
+    ids, w = ids[:xq.shape[0]], w[:xq.shape[0]]
     active = np.unique(ids)
     # sample: the first experts (by id) that together hold about `budget` routed rows; the 16-token batch runs whole
     budget_rows = tokens * TOPK if tokens <= 16 else 256
@@ -169,183 +214,427 @@ def cpu_reference_arm(args, rank):
         done, _, _ = oracle.cpu_path(tensors, xq, xs, ids, w, e_lo, e_hi)
         if it >= args.warmup:
             times.append(time.perf_counter() - t0)
-    step = float(np.mean(times))
+    st = stats([t * 1e3 for t in times])
+    step = st["median"] * 1e-3
     value = tokens * (done / (tokens * TOPK)) / step          # tokens/s if the whole batch ran at the sample's rate
     sample = f"experts {e_lo}..{e_hi - 1} of the batch: {done} of {tokens * TOPK} routed rows per step, extrapolated by rows"
     line = dict(impl="reference", metric="moe_expert_ffn_tokens_per_s_per_layer", value=value, unit="tokens/s",
-                n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=step * 1e3, higher_is_better=True,
-                scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
-                config=dict(workload=args.workload, tokens=tokens, routing="uniform" if not wl["zipf"] else f"zipf{wl['zipf']}",
-                            note="reference CPU expert path (E-FP32 lattice), port in oracle/oracle.c"),
+                n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=step * 1e3, ms_per_step_stats=st,
+                higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+                config=workload_config(args.workload),
+                note="reference CPU expert path (E-FP32 lattice, crates/mimo26-spark/src/main.rs:75-95), port in oracle/oracle.c, OpenMP over output rows",
                 cpu_baseline=dict(value=value, unit="tokens/s", cores=cores, kind="port", sample=sample),
-                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), identity=identity(args))
     print(json.dumps(line), flush=True)
 
 
-def run_workload(name, layer, scratch, dev, stream, args, rank, world, peaks):
-    """Times `steps` passes (device-resident inputs) and `steps` end-to-end passes (host buffers)."""
-    import torch
-    import torch.distributed as dist
+class Ctx:
+    """What every measurement needs: device, launching stream, ranks, the L2 flush buffer."""
 
-    import mimo26f_afd_b200 as M
-    from mimo26f_afd_b200 import expert, synth, tp
+    def __init__(self, args, dev, stream, rank, world):
+        import torch
 
-    wl = WORKLOADS[name]
-    tokens, seed = wl["tokens"], synth.MASTER_SEED
-    x_bits = synth.activations_bf16(seed, tokens)
-    ids, w = synth.routing(seed, tokens, wl["zipf"])
-    active = int(len(np.unique(ids)))
-    xd = torch.from_numpy(x_bits.view(np.int16)).to(dev)
-    idd, wd = torch.from_numpy(ids).to(dev), torch.from_numpy(w).to(dev)
-    out = torch.empty((tokens, H), dtype=torch.int16, device=dev)
-    total = torch.empty((tokens, H), dtype=torch.float32, device=dev) if world > 1 else None
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # > 126 MB L2
+        self.args, self.dev, self.stream, self.rank, self.world = args, dev, stream, rank, world
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # > 126 MB L2
+        self.peaks = measured_peaks()
+        self.traffic = profiled_traffic()
 
-    # N > 1: the ranks' BF16 planes are summed by the NVLink peer-memory exchange kernel (--exchange peer, default) or by
-    # an NCCL all-gather followed by the rank-sum kernel (--exchange nccl)
-    ex = tp.make_exchange(tokens) if world > 1 and args.exchange == "peer" else None
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
 
-    def step():
-        if ex is not None:
-            expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, ex.plane(), stream=stream.cuda_stream)
-            ex.sum(tokens * H, total, stream=stream.cuda_stream)
-            return
-        expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, out, stream=stream.cuda_stream)
-        if world > 1:
-            tp.tp_combine(out, total, stream=stream.cuda_stream)
-
-    def sync_all():
-        if world > 1:
+        if self.world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_steps(with_kernel_events):
-        """`steps` iterations, each bracketed by CUDA events on the launching stream, L2 flushed before each."""
-        scratch.set_debug(2 if with_kernel_events else 0)
-        step()                                               # the first pass after a mode change is not timed
-        scratch.status(stream.cuda_stream)
-        sync_all()
-        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-        per_kernel = []
-        for a, b in pairs:
-            flush.fill_(1)                                   # L2 flush between timed iterations (not timed)
-            a.record(stream)
+    def over_ranks(self, ms):
+        """Per-sample maximum over the ranks of this rank's per-sample times, and the median spread between ranks."""
+        import torch
+        import torch.distributed as dist
+
+        mine = torch.tensor(ms, dtype=torch.float64, device=self.dev)
+        if self.world == 1:
+            return [float(v) for v in ms], 0.0
+        every = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(every, mine)
+        m = torch.stack(every)
+        return [float(v) for v in m.max(0).values.cpu()], float((m.max(0).values - m.min(0).values).median().item())
+
+    def all_true(self, ok):
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return bool(ok)
+        t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    def timed_device(self, step, k):
+        """k samples of step() on the launching stream: barrier + synchronise + L2 flush before each (not timed), CUDA
+        events around it."""
+        import torch
+
+        ms = []
+        for _ in range(k):
+            self.barrier()
+            self.flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(self.stream)
             step()
-            b.record(stream)
+            b.record(self.stream)
             b.synchronize()
-            if with_kernel_events:
-                per_kernel.append(scratch.timings())
-        sync_all()
+            ms.append(a.elapsed_time(b))
+        return self.over_ranks(ms)
+
+    def timed_host(self, call, k):
+        """k samples of a synchronous host call (uploads and downloads inside), wall clock each. The calls follow one
+        another as in a serving loop (with several ranks a barrier lines them up before each sample); no L2 flush: a
+        step streams 1.4 to 3.4 GB of expert weights, an order of magnitude more than the L2 holds."""
+        ms = []
+        for _ in range(k):
+            if self.world > 1:
+                self.barrier()
+            t0 = time.perf_counter()
+            call()
+            ms.append((time.perf_counter() - t0) * 1e3)
+        return self.over_ranks(ms)
+
+
+def make_inputs(ctx, name, lo=None, hi=None):
+    """Seeded inputs of a workload: routes on the host and the device, BF16 activation rows [lo, hi) on the device. Batches
+    above 8,192 tokens get their activations from the device-side generator (nothing on the host reads their values)."""
+    import torch
+
+    from mimo26f_afd_b200 import synth
+
+    wl = WORKLOADS[name]
+    tokens, seed = wl["tokens"], synth.MASTER_SEED
+    lo, hi = (0, tokens) if lo is None else (lo, hi)
+    ids, w = synth.routing(seed, tokens, wl["zipf"])
+    if tokens > 8192:
+        xd, x_bits = synth.activations_bf16_torch(seed, hi - lo, ctx.dev, first_token=lo), None
+    else:
+        x_bits = synth.activations_bf16(seed, hi - lo, first_token=lo)
+        xd = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).to(ctx.dev)
+    idd = torch.from_numpy(np.ascontiguousarray(ids[lo:hi])).to(ctx.dev)
+    wd = torch.from_numpy(np.ascontiguousarray(w[lo:hi])).to(ctx.dev)
+    return dict(tokens=tokens, ids=ids, w=w, x_bits=x_bits, xd=xd, idd=idd, wd=wd, active=int(len(np.unique(ids))))
+
+
+def quantised_on_device(ctx, xd, rows):
+    """The library's own wire quantiser on device rows -> pinned host copies (what a coordinator would send)."""
+    import torch
+
+    from mimo26f_afd_b200 import expert
+
+    q = torch.empty((rows, H), dtype=torch.uint8, device=ctx.dev)
+    s = torch.empty((rows, H // 32), dtype=torch.uint8, device=ctx.dev)
+    f = torch.zeros(1, dtype=torch.int32, device=ctx.dev)
+    if rows:
+        expert.quantize_dev(xd, expert.X_BF16, rows * H, expert.CODEC_WIRE, q, s, f, stream=ctx.stream.cuda_stream)
+    torch.cuda.synchronize()
+    return q.cpu().pin_memory(), s.cpu().pin_memory()
+
+
+PASS_ROWS = 16384          # rows per call of the device entry point
+
+
+def run_tp(ctx, name, layer, scratch, k, y16=False, with_e2e=True, with_kernels=True):
+    """One workload on the (tensor-parallel) layer: device-resident timing, per-kernel durations, end to end."""
+    import torch
+
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import expert, tp
+
+    args, world, dev, stream = ctx.args, ctx.world, ctx.dev, ctx.stream
+    inp = make_inputs(ctx, name)
+    tokens, ids, w = inp["tokens"], inp["ids"], inp["w"]
+    xd, idd, wd = inp["xd"], inp["idd"], inp["wd"]
+    out = torch.empty((tokens, H), dtype=torch.int16, device=dev)
+    total = torch.empty((tokens, H), dtype=torch.float32, device=dev) if world > 1 else None
+    ex = tp.make_exchange(tokens) if world > 1 and args.exchange == "peer" else None
+    scratch.set_route_output(y16)
+
+    def step():
+        dst = ex.plane() if ex is not None else out.data_ptr()
+        for r0 in range(0, tokens, PASS_ROWS):
+            n = min(PASS_ROWS, tokens - r0)
+            expert.ffn_dev(layer, scratch, xd[r0:r0 + n], idd[r0:r0 + n], wd[r0:r0 + n], n, dst + r0 * H * 2, stream=stream.cuda_stream)
+        if ex is not None:
+            ex.sum(tokens * H, total, stream=stream.cuda_stream)
+        elif world > 1:
+            tp.tp_combine(out, total, stream=stream.cuda_stream)
+
+    def check():
         scratch.status(stream.cuda_stream)
-        return pairs, per_kernel
+        if ex is not None:
+            ex.status(stream.cuda_stream)
 
     scratch.set_debug(0)
     for _ in range(args.warmup):
         step()
-    scratch.status(stream.cuda_stream)
-    sync_all()
+    check()
     with ClockSampler(dev.index or 0) as clocks:
-        # the timed region proper: no events inside a step, so the kernels of a step overlap as they do in service
-        ev, _ = timed_steps(False)
-        # the same steps again with an event between every two kernels: the per-kernel durations of the roofline
-        ev_k, kern = timed_steps(True)
-    scratch.set_debug(2)
-    ms_instrumented = float(np.mean([a.elapsed_time(b) for a, b in ev_k]))
-    ms = np.array([a.elapsed_time(b) for a, b in ev])
-    t = torch.tensor([float(ms.sum())], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)             # max over ranks
-    total_ms = float(t.item())
-    value = tokens * args.steps / (total_ms * 1e-3)
+        ms, spread = ctx.timed_device(step, k)
+    check()
+    st = stats(ms)
+    res = dict(workload=name, tokens=tokens, active_experts=inp["active"], parallelism=f"tp{world}" if world > 1 else "single",
+               route_outputs="bf16" if y16 else "f32", value=tokens / (st["median"] * 1e-3), unit="tokens/s",
+               ms_per_step=st["median"], ms_per_step_stats=st, rank_spread_ms=spread, clocks=clocks.summary())
+    il, routes = I // world, tokens * TOPK
+    if with_kernels and tokens <= PASS_ROWS:
+        # the same step with an event between every two kernels: per-kernel durations for the roofline
+        scratch.set_debug(2)
+        step(); check()
+        kern = []
+        for _ in range(5):
+            ctx.barrier(); ctx.flush.fill_(1)
+            step()
+            kern.append(scratch.timings())
+            check()
+        scratch.set_debug(0)
+        km = {key: float(np.median([x[key] for x in kern])) for key in kern[0]}
+        res["kernels_ms"] = km
+        fc1_ms, fc2_ms = km["fc1"], km["fc2"]
+        if tokens <= 128:
+            fc1_bytes = inp["active"] * (2 * il * (H // 2) + 2 * il * (H // 32)) + routes * (H + H // 32) + routes * (il + il // 32)
+            roof = dict(bound="hbm", achieved=fc1_bytes / (fc1_ms * 1e-3) / 1e9, peak=ctx.peaks["hbm_gbs"], unit="GB/s",
+                        peak_source=f"{ctx.peaks['source']} copy bandwidth", kernel="gemm_mx_kernel<FC1>", algorithmic_bytes=fc1_bytes)
+        else:
+            fc1_flops = 2.0 * 2 * H * il * routes
+            roof = dict(bound="tensor", achieved=fc1_flops / (fc1_ms * 1e-3) / 1e12, peak=MXF8F6F4_PEAK_TFLOPS, unit="TFLOP/s",
+                        peak_source="tcgen05 kind::mxf8f6f4 dense rate measured on this pool with the same instruction (burst, few small "
+                                    f"codes); the measured bf16 cuBLAS figure is {ctx.peaks['bf16_tflops']} TF/s",
+                        kernel="gemm_mx_pair_kernel<FC1>", algorithmic_flops=fc1_flops)
+            roof["frac_of_random_operand_burst"] = roof["achieved"] / MXF8F6F4_RANDOM_BURST_TFLOPS
+            roof["frac_of_random_operand_sustained"] = roof["achieved"] / MXF8F6F4_RANDOM_SUSTAINED_TFLOPS
+            fc2_flops = 2.0 * H * il * routes
+            roof["fc2"] = dict(kernel="gemm_mx_pair_kernel<FC2>", achieved=fc2_flops / (fc2_ms * 1e-3) / 1e12, kernel_ms=fc2_ms,
+                               frac=fc2_flops / (fc2_ms * 1e-3) / 1e12 / MXF8F6F4_PEAK_TFLOPS)
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof["kernel_ms"] = fc1_ms
+        t = ctx.traffic.get(name) if world == 1 and not y16 else None
+        roof["traffic"] = t.get("fc1_dram_bytes") if t else None
+        if t:
+            roof["traffic_source"] = t.get("source")
+        res["roofline"] = roof
+    step_s = st["median"] * 1e-3
+    res["whole_step"] = dict(hbm_gbs=(inp["active"] * EXPERT_BYTES / world + tokens * H * 4 + routes * 8) / step_s / 1e9,
+                             tflops=FLOP_PER_TOKEN * tokens / step_s / 1e12, tflops_per_gpu=FLOP_PER_TOKEN * tokens / world / step_s / 1e12)
+    passes = (tokens + PASS_ROWS - 1) // PASS_ROWS
+    per_pass = 4 if tokens <= 128 else 5 if routes <= 4096 else 7
+    res["gpu_launches_per_step"] = passes * per_pass + (1 if world > 1 else 0)
 
-    # end to end through the reference-compatible host entry point: pinned host buffers, copies inside the timed region
-    xq = scratch.peek("x_payload", np.uint8, (tokens, H))
-    xs = scratch.peek("x_scales", np.uint8, (tokens, H // 32))
-    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
-    hq, hs, hi, hw = pin(xq), pin(xs), pin(ids), pin(w)
-    hout = torch.empty((tokens, H), dtype=torch.int16).pin_memory()
-    import ctypes as C
-    from mimo26f_afd_b200 import _native
-    err = C.create_string_buffer(256)
-
-    if world > 1:
-        # tensor-parallel ranks: quantised rows, ids and weights go up from pinned memory, the device entry point runs
-        # the rank's slice, the planes are summed across ranks, and the FP32 result comes back to pinned memory
-        dq, ds = torch.empty_like(hq, device=dev), torch.empty_like(hs, device=dev)
-        di, dw = torch.empty_like(hi, device=dev), torch.empty_like(hw, device=dev)
-        htotal = torch.empty((tokens, H), dtype=torch.float32).pin_memory()
-
-    def e2e_step():
+    if with_e2e and tokens <= PASS_ROWS:
+        # end to end through the host entry points: pinned host buffers, copies inside the timed region
+        hq, hs = quantised_on_device(ctx, xd, tokens)
+        pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+        hi_, hw = pin(ids), pin(w)
         if world == 1:
-            rc = _native.lib().m26b_ffn(layer._h, scratch._h, hq.data_ptr(), H, hs.data_ptr(), H // 32, hi.data_ptr(),
-                                        hw.data_ptr(), tokens, hout.data_ptr(), None, err, 256)
-            if rc:
-                raise M.ExpertError(rc, err.value.decode())
-            return
-        with torch.cuda.stream(stream):
-            dq.copy_(hq, non_blocking=True); ds.copy_(hs, non_blocking=True)
-            di.copy_(hi, non_blocking=True); dw.copy_(hw, non_blocking=True)
-            dst = ex.plane() if ex is not None else out
-            expert.ffn_dev(layer, scratch, dq, di, dw, tokens, dst, x_dtype=expert.X_E4M3, x_scales=ds, stream=stream.cuda_stream)
-            if ex is not None:
-                ex.sum(tokens * H, total, stream=stream.cuda_stream)
-            else:
-                tp.tp_combine(out, total, stream=stream.cuda_stream)
-            htotal.copy_(total, non_blocking=True)
-        scratch.status(stream.cuda_stream)
-
-    for _ in range(max(args.warmup, 10) if tokens <= 128 else min(args.warmup, 3)):   # short calls: let clocks and the driver settle
-        e2e_step()
-    sync_all()
-    with ClockSampler(dev.index or 0) as clocks_e2e:           # the end-to-end region is timed too: its samples join the record
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-    clocks.rows += clocks_e2e.rows
-    t = torch.tensor([e2e_s], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = tokens * args.steps / float(t.item())
-    h2d = tokens * (H + H // 32 + TOPK * 8)
-    d2h = (tokens * H * 2 if world == 1 else tokens * H * 4) + 64
+            hout = torch.empty((tokens, H), dtype=torch.int16).pin_memory()
+            call = lambda: M.ffn(layer, scratch, hq.numpy().reshape(-1), hs.numpy().reshape(-1), hi_.numpy().reshape(-1), hw.numpy().reshape(-1),
+                                 tokens, hout.numpy().view(np.uint16).reshape(-1))
+            d2h = tokens * H * 2 + 64
+        else:
+            ex2 = ex if ex is not None else tp.make_exchange(tokens)
+            hsum = torch.empty((tokens, H), dtype=torch.float32).pin_memory() if ctx.rank == 0 else None
+            call = lambda: M.ffn_tp(layer, scratch, ex2, hq.data_ptr(), hs.data_ptr(), hi_.data_ptr(), hw.data_ptr(), tokens,
+                                    hsum.data_ptr() if hsum is not None else None)
+            d2h = tokens * H * 4 + 64 * world
+        for _ in range(max(args.warmup, 10) if tokens <= 128 else 3):      # short calls: let clocks and the driver settle
+            call()
+        with ClockSampler(dev.index or 0) as clocks_e2e:
+            ms_e, spread_e = ctx.timed_host(call, k)
+        se = stats(ms_e)
+        res["e2e"] = dict(value=tokens / (se["median"] * 1e-3), unit="tokens/s", ms_per_step=se["median"], ms_per_step_stats=se,
+                          rank_spread_ms=spread_e, h2d_bytes_per_step=world * tokens * (H + H // 32 + TOPK * 8), d2h_bytes_per_step=d2h,
+                          entry_point="m26b_ffn" if world == 1 else "m26b_ffn_tp (every rank uploads the request; rank 0 downloads the FP32 sum)",
+                          clocks=clocks_e2e.summary())
+        if world > 1 and ex is None:
+            ex2.close()
     if ex is not None:
-        ex.status(stream.cuda_stream)
-        sync_all()
+        check()
+        ctx.barrier()
         ex.close()
-
-    # roofline of the dominant kernel (FC1): algorithmic work of that launch / its mean event-timed duration
-    fc1_ms = float(np.mean([k["fc1"] for k in kern]))
-    il = I // world
-    routes = tokens * TOPK
-    if name == "decode16":
-        fc1_bytes = active * (2 * il * (H // 2) + 2 * il * (H // 32)) + routes * (H + H // 32) + routes * (il + il // 32)
-        roof = dict(bound="hbm", achieved=fc1_bytes / (fc1_ms * 1e-3) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s",
-                    peak_source=f"{peaks['source']} copy bandwidth (MEASURED_PEAKS.json)", kernel="gemm_mx_kernel<FC1>",
-                    algorithmic_bytes=fc1_bytes, traffic=FC1_TRAFFIC_BYTES[name] if world == 1 else None)
-    else:
-        fc1_flops = 2.0 * 2 * H * il * routes
-        roof = dict(bound="tensor", achieved=fc1_flops / (fc1_ms * 1e-3) / 1e12, peak=MXF8F6F4_PEAK_TFLOPS, unit="TFLOP/s",
-                    peak_source="measured tcgen05 kind::mxf8f6f4 dense rate on this pool (profiles/mxf8f6f4_mma_rate.md); "
-                                f"MEASURED_PEAKS.json holds only bf16 = {peaks['bf16_tflops']} TF/s",
-                    kernel="gemm_mx_pair_kernel<FC1>", algorithmic_flops=fc1_flops,
-                    traffic=FC1_TRAFFIC_BYTES[name] if world == 1 else None)
-        roof["frac_of_random_operand_burst"] = roof["achieved"] / MXF8F6F4_RANDOM_BURST_TFLOPS
-        roof["frac_of_random_operand_sustained"] = roof["achieved"] / MXF8F6F4_RANDOM_SUSTAINED_TFLOPS
-    roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["kernel_ms"] = fc1_ms
-    whole = dict(hbm_gbs=(active * EXPERT_BYTES / world + tokens * H * 4 + routes * 8) / (total_ms / args.steps * 1e-3) / 1e9,
-                 tflops=FLOP_PER_TOKEN * tokens / world / (total_ms / args.steps * 1e-3) / 1e12)
-    launches = (4 if tokens <= 128 else 6 if routes <= 4096 else 8) + (1 if world > 1 else 0)
-    return dict(workload=name, tokens=tokens, active_experts=active, value=value, ms_per_step=total_ms / args.steps,
-                ms_per_step_with_kernel_events=ms_instrumented,
-                e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
-                roofline=roof, whole_step=whole, kernels_ms={k: float(np.mean([x[k] for x in kern])) for k in kern[0]},
-                clocks=clocks.summary(), gpu_launches=launches * args.steps)
+    scratch.set_route_output(False)
+    return res
 
 
-def cpu_baseline_for(name, steps_budget_s=20.0):
+def run_ep(ctx, name, layer, scratch, k, y16=False, with_e2e=True):
+    """Expert-parallel step: rank r holds 256 / N experts and owns 1 / N of the tokens; rows are gathered from and results
+    scattered to their owners over NVLink inside the permutation and FC2 kernels."""
+    import torch
+
+    from mimo26f_afd_b200 import tp
+
+    args, world, dev, stream = ctx.args, ctx.world, ctx.dev, ctx.stream
+    wl = WORKLOADS[name]
+    tokens = wl["tokens"]
+    lo, hi = tp.shard_tokens(tokens, ctx.rank, world)
+    rows = hi - lo
+    inp = make_inputs(ctx, name, lo, hi)
+    ids, w = inp["ids"], inp["w"]
+    xd, idd, wd = inp["xd"], inp["idd"], inp["wd"]
+    n_local = E // world
+    counts = np.bincount(ids.reshape(-1), minlength=E)
+    per_rank = counts.reshape(world, n_local).sum(1)
+    ep = tp.make_expert_parallel(tokens)
+    ep.set_route_output(y16)
+    out = torch.empty((max(rows, 1), H), dtype=torch.int16, device=dev)
+
+    def step():
+        ep.step(layer, scratch, xd, idd, wd, rows, out, stream=stream.cuda_stream)
+
+    def check():
+        scratch.status(stream.cuda_stream)
+        ep.status(stream.cuda_stream)
+
+    for _ in range(args.warmup):
+        step()
+    check()
+    with ClockSampler(dev.index or 0) as clocks:
+        ms, spread = ctx.timed_device(step, k)
+    check()
+    st = stats(ms)
+    step_s = st["median"] * 1e-3
+    busiest = float(per_rank.max()) * (FLOP_PER_TOKEN / TOPK)       # the busiest rank bounds the step
+    res = dict(workload=name, tokens=tokens, active_experts=int((counts > 0).sum()), parallelism=f"ep{world}",
+               route_outputs="bf16" if y16 else "f32", value=tokens / step_s, unit="tokens/s", ms_per_step=st["median"],
+               ms_per_step_stats=st, rank_spread_ms=spread, clocks=clocks.summary(),
+               roofline=dict(bound="tensor" if tokens > 128 else "hbm", kernel="whole expert-parallel step on the busiest rank",
+                             achieved=busiest / step_s / 1e12, peak=MXF8F6F4_PEAK_TFLOPS, unit="TFLOP/s", traffic=None,
+                             frac=busiest / step_s / 1e12 / MXF8F6F4_PEAK_TFLOPS, algorithmic_flops=busiest),
+               whole_step=dict(tflops=FLOP_PER_TOKEN * tokens / step_s / 1e12, tflops_per_gpu=FLOP_PER_TOKEN * tokens / world / step_s / 1e12,
+                               routed_rows_per_rank=[int(v) for v in per_rank], imbalance=float(per_rank.max() / max(per_rank.mean(), 1e-9)),
+                               nvlink_bytes_in_busiest_rank=int(per_rank.max() * (world - 1) / world * (H + H // 32)),
+                               nvlink_bytes_out_busiest_rank=int(per_rank.max() * (world - 1) / world * H * (2 if y16 else 4))),
+               gpu_launches_per_step=3 + 2 + 6 * ((tokens + PASS_ROWS - 1) // PASS_ROWS) + 1)
+    if with_e2e:
+        hq, hs = quantised_on_device(ctx, xd, rows)
+        pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+        hi_, hw = pin(ids[lo:hi]), pin(w[lo:hi])
+        hout = torch.empty((max(rows, 1), H), dtype=torch.int16).pin_memory()
+        call = lambda: ep.ffn_host(layer, scratch, hq.data_ptr(), hs.data_ptr(), hi_.data_ptr(), hw.data_ptr(), rows, hout.data_ptr())
+        for _ in range(3):
+            call()
+        ms_e, spread_e = ctx.timed_host(call, k)
+        se = stats(ms_e)
+        res["e2e"] = dict(value=tokens / (se["median"] * 1e-3), unit="tokens/s", ms_per_step=se["median"], ms_per_step_stats=se,
+                          rank_spread_ms=spread_e, h2d_bytes_per_step=tokens * (H + H // 32 + TOPK * 8), d2h_bytes_per_step=tokens * H * 2,
+                          entry_point="m26b_ep_ffn (every rank uploads its token block and downloads its BF16 rows)")
+    check()
+    ctx.barrier()
+    ep.close()
+    return res
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / max(np.linalg.norm(b.astype(np.float64)), 1e-30))
+
+
+def parity_tp(ctx, layer, scratch):
+    """Correctness of the (tensor-parallel) layer on the 16-token batch: quantised bytes and plan indices exact against the
+    CPU oracle; with several ranks the peer-memory exchange and the NCCL path must give identical bits on every rank and
+    rank 0 compares the sum with the oracle's wire result (rel L2 <= 1e-3 + N 2^-9: every plane is rounded to BF16 first)."""
+    import torch
+
+    import oracle
+    from mimo26f_afd_b200 import expert, synth, tp
+
+    world, dev, stream = ctx.world, ctx.dev, ctx.stream
+    out = dict(ok=True)
+    for tokens, zipf in ((16, 0.0), (300, 1.2)):
+        seed = synth.MASTER_SEED + 77
+        x_bits = synth.activations_bf16(seed, tokens)
+        ids, w = synth.routing(seed, tokens, zipf)
+        xd = torch.from_numpy(x_bits.view(np.int16)).to(dev)
+        idd, wd = torch.from_numpy(ids).to(dev), torch.from_numpy(w).to(dev)
+        plane = torch.empty((tokens, H), dtype=torch.int16, device=dev)
+        part = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, plane, partial_out=part, stream=stream.cuda_stream)
+        scratch.status(stream.cuda_stream)
+        xq, xs = oracle.quant_wire(synth.bf16_to_f32_np(x_bits))
+        st, oinv, _, _, _ = oracle.plan(ids, w)
+        exact = (st == 0 and np.array_equal(scratch.peek("x_payload", np.uint8, (tokens, H)), xq)
+                 and np.array_equal(scratch.peek("x_scales", np.uint8, (tokens, H // 32)), xs)
+                 and np.array_equal(scratch.peek("inverse", np.int32, (tokens * TOPK,)), oinv))
+        out[f"quantised_bytes_and_plan_exact_{tokens}"] = bool(exact)
+        out["ok"] &= bool(exact)
+        if world == 1:
+            if tokens == 16:
+                ref = oracle.ffn_layer(synth.layer_np(synth.MASTER_SEED, np.unique(ids)), xq, xs, ids, w)
+                r = rel_l2(part.cpu().numpy(), ref["partial"])
+                out["rel_l2_vs_oracle"] = r
+                out["bf16_flips_vs_oracle"] = int((plane.cpu().numpy().view(np.uint16) != ref["bf16"]).sum())
+                out["ok"] &= ref["rc"] == 0 and r <= 1e-3
+            continue
+        ex = tp.make_exchange(tokens)
+        peer_sum = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        nccl_sum = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        same = True
+        for _ in range(3):                                      # both slots and a reuse
+            expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, ex.plane(), stream=stream.cuda_stream)
+            ex.sum(tokens * H, peer_sum, stream=stream.cuda_stream)
+            scratch.status(stream.cuda_stream)
+            ex.status(stream.cuda_stream)
+            tp.tp_combine(plane, nccl_sum, stream=stream.cuda_stream)
+            torch.cuda.synchronize()
+            same &= bool(torch.equal(peer_sum.view(torch.int32), nccl_sum.view(torch.int32)))
+        out[f"peer_exchange_equals_nccl_sum_{tokens}"] = ctx.all_true(same)
+        out["ok"] &= out[f"peer_exchange_equals_nccl_sum_{tokens}"]
+        if tokens == 16 and ctx.rank == 0:
+            tensors = synth.layer_np(synth.MASTER_SEED, np.unique(ids))
+            planes = [oracle.ffn_layer(tensors, xq, xs, ids, w, tp_rank=r, tp_size=world)["bf16"] for r in range(world)]
+            wire = oracle.rank_sum(np.stack(planes))
+            r = rel_l2(peer_sum.cpu().numpy(), wire)
+            out["rel_l2_vs_oracle_wire_sum"] = r
+            out["rel_l2_bound"] = 1e-3 + world * 2.0 ** -9
+            out["ok"] &= r <= 1e-3 + world * 2.0 ** -9
+        ctx.barrier()
+        ex.close()
+    out["ok"] = ctx.all_true(out["ok"])
+    return out
+
+
+def parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full):
+    """The expert-parallel step against the single-GPU layer run on the same rank over the whole batch: bit for bit, FP32
+    plane and BF16 rows (a GEMM row does not depend on how routes are tiled)."""
+    import torch
+
+    from mimo26f_afd_b200 import expert, synth, tp
+
+    dev, stream, world = ctx.dev, ctx.stream, ctx.world
+    out = dict(ok=True)
+    for tokens, zipf in ((16, 0.0), (1000, 1.0)):
+        seed = synth.MASTER_SEED + 78
+        x_bits = synth.activations_bf16(seed, tokens)
+        ids, w = synth.routing(seed, tokens, zipf)
+        lo, hi = tp.shard_tokens(tokens, ctx.rank, world)
+        xd = torch.from_numpy(x_bits.view(np.int16)).to(dev)
+        idd, wd = torch.from_numpy(ids).to(dev), torch.from_numpy(w).to(dev)
+        ref = torch.empty((tokens, H), dtype=torch.int16, device=dev)
+        ref_part = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        expert.ffn_dev(full_layer, scratch_full, xd, idd, wd, tokens, ref, partial_out=ref_part, stream=stream.cuda_stream)
+        scratch_full.status(stream.cuda_stream)
+        ep = tp.make_expert_parallel(tokens)
+        got = torch.empty((max(hi - lo, 1), H), dtype=torch.int16, device=dev)
+        part = torch.empty((max(hi - lo, 1), H), dtype=torch.float32, device=dev)
+        same = True
+        for _ in range(2):
+            ep.step(ep_layer, scratch, xd[lo:hi], idd[lo:hi], wd[lo:hi], hi - lo, got, partial_out=part, stream=stream.cuda_stream)
+            scratch.status(stream.cuda_stream)
+            ep.status(stream.cuda_stream)
+            torch.cuda.synchronize()
+            same &= bool(torch.equal(got[:hi - lo], ref[lo:hi])) and bool(torch.equal(part[:hi - lo].view(torch.int32), ref_part[lo:hi].view(torch.int32)))
+        out[f"expert_parallel_equals_single_gpu_{tokens}"] = ctx.all_true(same)
+        out["ok"] &= out[f"expert_parallel_equals_single_gpu_{tokens}"]
+        ctx.barrier()
+        ep.close()
+    return out
+
+
+def cpu_baseline_for(name):
     """The oracle's port of the reference CPU path on this host, bounded sample (rank 0, N = 1 only)."""
     import oracle
     from mimo26f_afd_b200 import synth
@@ -355,7 +644,7 @@ def cpu_baseline_for(name, steps_budget_s=20.0):
     ids, w = synth.routing(seed, tokens, wl["zipf"])
     sub = min(tokens, 16)                                   # the sample keeps whole tokens of the batch
     ids_s, w_s = ids[:sub], w[:sub]
-    xq, xs = oracle.quant_wire(synth.bf16_to_f32_np(synth.activations_bf16(seed, tokens)[:sub]))
+    xq, xs = oracle.quant_wire(synth.bf16_to_f32_np(synth.activations_bf16(seed, sub)))
     active = np.unique(ids_s)
     take, rows = [], 0
     for e in active:                                        # 16 tokens = 128 routed rows: the decode batch runs whole
@@ -377,115 +666,23 @@ def cpu_baseline_for(name, steps_budget_s=20.0):
                        f"{take[0]}..{take[-1]}, {dt:.1f} s in all; reference CPU expert path (E-FP32), OpenMP over output rows")
 
 
-def run_expert_parallel(name, dev, stream, args, rank, world):
-    """Expert-parallel step (--parallel ep): rank r holds 256 / N experts and owns 1 / N of the tokens; rows are gathered
-    from and results scattered to their owners over NVLink inside the permutation and FC2 kernels."""
-    import torch
-    import torch.distributed as dist
-
-    import mimo26f_afd_b200 as M
-    from mimo26f_afd_b200 import expert, synth, tp
-
-    wl = WORKLOADS[name]
-    tokens, seed = wl["tokens"], synth.MASTER_SEED
-    n_local = E // world
-    wts = synth.layer_torch(seed, dev, n_experts=n_local, first_expert=rank * n_local)
-    layer = M.Layer.from_checkpoint_ep(*[wts[n] for n in synth.TENSORS], ep_rank=rank, ep_size=world)
-    del wts
-    torch.cuda.empty_cache()
-    scratch = M.Scratch()
-    ep = tp.make_expert_parallel(tokens)
-    lo, hi = tp.shard_tokens(tokens, rank, world)
-    rows = hi - lo
-    ids, w = synth.routing(seed, tokens, wl["zipf"])
-    counts = np.bincount(ids.reshape(-1), minlength=E)
-    per_rank = counts.reshape(world, n_local).sum(1)
-    x_bits = synth.activations_bf16(seed, rows, first_token=lo)
-    xd = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).to(dev)
-    idd, wd = torch.from_numpy(np.ascontiguousarray(ids[lo:hi])).to(dev), torch.from_numpy(np.ascontiguousarray(w[lo:hi])).to(dev)
-    out = torch.empty((rows, H), dtype=torch.int16, device=dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-
-    def step():
-        ep.step(layer, scratch, xd, idd, wd, rows, out, stream=stream.cuda_stream)
-
-    def sync_all():
-        dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    scratch.status(stream.cuda_stream); ep.status(stream.cuda_stream)
-    sync_all()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    with ClockSampler(dev.index or 0) as clocks:
-        for a, b in ev:
-            flush.fill_(1)
-            a.record(stream); step(); b.record(stream)
-            b.synchronize()
-        sync_all()
-    scratch.status(stream.cuda_stream); ep.status(stream.cuda_stream)
-    t = torch.tensor([float(sum(a.elapsed_time(b) for a, b in ev))], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    value = tokens * args.steps / (total_ms * 1e-3)
-
-    # end to end: this rank's BF16 rows, ids and weights from pinned memory, its BF16 result rows back to pinned memory
-    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
-    hx, hi_, hw = pin(x_bits.view(np.int16)), pin(ids[lo:hi]), pin(w[lo:hi])
-    hout = torch.empty((rows, H), dtype=torch.int16).pin_memory()
-
-    def e2e_step():
-        with torch.cuda.stream(stream):
-            xd.copy_(hx, non_blocking=True); idd.copy_(hi_, non_blocking=True); wd.copy_(hw, non_blocking=True)
-            step()
-            hout.copy_(out, non_blocking=True)
-        scratch.status(stream.cuda_stream)
-
-    for _ in range(2):
-        e2e_step()
-    sync_all()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    t = torch.tensor([time.perf_counter() - t0], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = tokens * args.steps / float(t.item())
-    ep.status(stream.cuda_stream)
-    sync_all()
-    ep.close()
-    step_s = total_ms / args.steps * 1e-3
-    # the busiest rank bounds the step: its share of the routed rows x FLOP per routed row
-    busiest = float(per_rank.max()) * (FLOP_PER_TOKEN / TOPK)
-    roof = dict(bound="tensor", kernel="whole expert-parallel step on the busiest rank (FC1 + FC2 + gather/scatter over NVLink)",
-                achieved=busiest / step_s / 1e12, peak=MXF8F6F4_PEAK_TFLOPS, unit="TFLOP/s", traffic=None,
-                algorithmic_flops=busiest, peak_source="measured tcgen05 kind::mxf8f6f4 dense rate (profiles/mxf8f6f4_mma_rate.md)")
-    roof["frac"] = roof["achieved"] / roof["peak"]
-    launches = 3 + 2 + 8 * ((tokens + 16383) // 16384) + 1
-    return dict(workload=name, tokens=tokens, active_experts=int((counts > 0).sum()), value=value, ms_per_step=total_ms / args.steps,
-                e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=rows * (H * 2 + TOPK * 8) * world,
-                         d2h_bytes_per_step=rows * H * 2 * world),
-                roofline=roof, clocks=clocks.summary(), gpu_launches=launches * args.steps,
-                whole_step=dict(tflops=FLOP_PER_TOKEN * tokens / step_s / 1e12, tflops_per_gpu=FLOP_PER_TOKEN * tokens / world / step_s / 1e12,
-                                routed_rows_per_rank=[int(v) for v in per_rank],
-                                imbalance=float(per_rank.max() / per_rank.mean()),
-                                nvlink_bytes_in_busiest_rank=int(per_rank.max() * (world - 1) / world * (H + H // 32)),
-                                nvlink_bytes_out_busiest_rank=int(per_rank.max() * (world - 1) / world * H * 4)))
+def fail(ctx, what, parity):
+    if ctx.rank == 0:
+        print(json.dumps(dict(error=f"parity check failed ({what})", parity=parity)), file=sys.stderr, flush=True)
+    sys.exit(3)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=31)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode16", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-prefill", action="store_true", help="skip the 8192-token prefill sub-result")
+    ap.add_argument("--workload", default="decode16", choices=["decode16", "verify128", "prefill8k"],
+                    help="the headline workload of the JSON line (the others are reported under their own keys)")
+    ap.add_argument("--no-extra", action="store_true", help="headline workload only: no sub-results, no CPU baseline")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the ranks' planes are summed (NVLink peer-memory kernel, or NCCL all-gather + sum kernel)")
-    ap.add_argument("--parallel", default="tp", choices=["tp", "ep"],
-                    help="N > 1: tensor parallel over the intermediate dimension (default) or expert parallel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -510,27 +707,7 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    peaks = measured_peaks()
-    if args.parallel == "ep" or args.workload == "prefill64k":
-        if world < 2:
-            raise SystemExit("--parallel ep / prefill64k need --gpus 2, 4 or 8 (launch with torch.distributed.run)")
-        stream = torch.cuda.Stream(device=dev)
-        torch.cuda.set_stream(stream)
-        r = run_expert_parallel(args.workload, dev, stream, args, rank, world)
-        if rank == 0:
-            line = dict(metric="moe_expert_ffn_tokens_per_s_per_layer", value=r["value"], unit="tokens/s", n_gpus=world,
-                        steps=args.steps, warmup=args.warmup, ms_per_step=r["ms_per_step"], higher_is_better=True,
-                        scaling="strong", vs_baseline=None, dtype="e4m3 x e2m1 (mxf8f6f4), f32 accumulate", data="synthetic",
-                        config=dict(workload=args.workload, description=WORKLOADS[args.workload]["desc"], tokens=r["tokens"],
-                                    top_k=TOPK, experts=E, hidden=H, intermediate=I, active_experts=r["active_experts"],
-                                    parallelism=f"ep{world}", l2="flushed between timed iterations",
-                                    input_codec="wire (FP8 E4M3 + UE8M0 K32)"),
-                        e2e=r["e2e"], gpu_launches=r["gpu_launches"], clocks=r["clocks"], roofline=r["roofline"],
-                        whole_step=r["whole_step"], cpu_baseline=None)
-            print(json.dumps(line), flush=True)
-        dist.barrier()
-        dist.destroy_process_group()
-        return
+    k, k_big = args.steps, max(3, min(args.steps, 7))
     weights = synth.layer_torch(synth.MASTER_SEED, dev)
     layer = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS], tp_rank=rank, tp_size=world)
     del weights
@@ -538,46 +715,64 @@ def main():
     scratch = M.Scratch()
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
+    ctx = Ctx(args, dev, stream, rank, world)
 
-    main_r = run_workload(args.workload, layer, scratch, dev, stream, args, rank, world, peaks)
-    extra = None
-    if not args.no_prefill and args.workload == "decode16":
-        sub = argparse.Namespace(**vars(args))
-        sub.steps, sub.warmup = max(3, min(args.steps, 10)), max(3, min(args.warmup, 5))
-        extra = run_workload("prefill8k", layer, scratch, dev, stream, sub, rank, world, peaks)
-        extra["parallelism"] = f"tp{world}" if world > 1 else "single"
-    prefill_ep = None
-    if extra is not None and world > 1:
-        # Prefill under tensor parallelism repeats the per-token work on every rank and stops scaling at two GPUs; the
-        # scheme for prefill on several GPUs is expert parallelism, so the same segment is also reported that way.
+    parity = dict(checked=True, before=parity_tp(ctx, layer, scratch))
+    if not parity["before"]["ok"]:
+        fail(ctx, "before timing", parity)
+    main_r = run_tp(ctx, args.workload, layer, scratch, k)
+    extra = {}
+    if not args.no_extra:
+        for name, key in (("decode16", "decode16"), ("verify128", "verify128"), ("prefill8k", "prefill")):
+            if name != args.workload:
+                extra[key] = run_tp(ctx, name, layer, scratch, k)
+        if world == 1:
+            extra["prefill_bf16_route_outputs"] = run_tp(ctx, "prefill8k", layer, scratch, k, y16=True, with_e2e=False)
+        else:
+            extra["prefill64k_tp"] = run_tp(ctx, "prefill64k", layer, scratch, k_big, with_e2e=False, with_kernels=False)
+    parity["after"] = parity_tp(ctx, layer, scratch)
+    if not parity["after"]["ok"]:
+        fail(ctx, "after timing", parity)
+    if world > 1 and not args.no_extra:
+        # Prefill under tensor parallelism repeats the per-token work on every rank; the scheme for prefill on several GPUs
+        # is expert parallelism, so the same batches are also reported that way (and the decode batch, for comparison).
         layer.close()
         del layer
         torch.cuda.empty_cache()
-        prefill_ep = run_expert_parallel("prefill8k", dev, stream, sub, rank, world)
-        prefill_ep["parallelism"] = f"ep{world}"
+        n_local = E // world
+        wts = synth.layer_torch(synth.MASTER_SEED, dev, n_experts=n_local, first_expert=rank * n_local)
+        ep_layer = M.Layer.from_checkpoint_ep(*[wts[n] for n in synth.TENSORS], ep_rank=rank, ep_size=world)
+        del wts
+        weights = synth.layer_torch(synth.MASTER_SEED, dev)
+        full_layer = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS])
+        del weights
+        torch.cuda.empty_cache()
+        scratch_full = M.Scratch()
+        parity["expert_parallel_before"] = parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full)
+        if not parity["expert_parallel_before"]["ok"]:
+            fail(ctx, "expert parallel, before timing", parity)
+        extra["prefill_expert_parallel"] = run_ep(ctx, "prefill8k", ep_layer, scratch, k)
+        extra["prefill_expert_parallel_bf16_route_outputs"] = run_ep(ctx, "prefill8k", ep_layer, scratch, k, y16=True, with_e2e=False)
+        extra["decode16_expert_parallel"] = run_ep(ctx, "decode16", ep_layer, scratch, k, with_e2e=False)
+        extra["prefill64k_ep"] = run_ep(ctx, "prefill64k", ep_layer, scratch, k_big, with_e2e=False)
+        extra["prefill64k_ep_bf16_route_outputs"] = run_ep(ctx, "prefill64k", ep_layer, scratch, k_big, y16=True, with_e2e=False)
+        parity["expert_parallel_after"] = parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full)
+        if not parity["expert_parallel_after"]["ok"]:
+            fail(ctx, "expert parallel, after timing", parity)
     if rank == 0:
-        cpu = cpu_baseline_for(args.workload) if world == 1 else None
+        cpu = cpu_baseline_for(args.workload) if world == 1 and not args.no_extra else None
         line = dict(metric="moe_expert_ffn_tokens_per_s_per_layer", value=main_r["value"], unit="tokens/s", n_gpus=world,
-                    steps=args.steps, warmup=args.warmup, ms_per_step=main_r["ms_per_step"], higher_is_better=True,
-                    scaling="strong" if world > 1 else "weak", vs_baseline=None, dtype="e4m3 x e2m1 (mxf8f6f4), f32 accumulate",
-                    data="synthetic",
-                    config=dict(workload=args.workload, description=WORKLOADS[args.workload]["desc"], tokens=main_r["tokens"],
-                                top_k=TOPK, experts=E, hidden=H, intermediate=I, active_experts=main_r["active_experts"],
-                                parallelism=f"tp{world}" if world > 1 else "single",
-                                exchange=(args.exchange if world > 1 else None), l2="flushed between timed iterations",
-                                input_codec="wire (FP8 E4M3 + UE8M0 K32)"),
-                    e2e=main_r["e2e"], gpu_launches=main_r["gpu_launches"], clocks=main_r["clocks"], roofline=main_r["roofline"],
-                    whole_step=main_r["whole_step"], kernels_ms=main_r["kernels_ms"],
-                    ms_per_step_with_kernel_events=main_r["ms_per_step_with_kernel_events"], cpu_baseline=cpu)
-        if extra:
-            line["prefill"] = {k: extra[k] for k in ("workload", "tokens", "value", "ms_per_step", "ms_per_step_with_kernel_events", "e2e", "roofline", "whole_step",
-                                                     "kernels_ms", "clocks")}
-            line["prefill"]["unit"] = "tokens/s"
-            line["prefill"]["parallelism"] = extra["parallelism"]
-        if prefill_ep:
-            line["prefill_expert_parallel"] = {k: prefill_ep[k] for k in ("workload", "tokens", "value", "ms_per_step", "e2e", "roofline",
-                                                                           "whole_step", "clocks", "parallelism")}
-            line["prefill_expert_parallel"]["unit"] = "tokens/s"
+                    steps=k, warmup=args.warmup, ms_per_step=main_r["ms_per_step"], ms_per_step_stats=main_r["ms_per_step_stats"],
+                    rank_spread_ms=main_r["rank_spread_ms"], higher_is_better=True, scaling="strong", vs_baseline=None,
+                    dtype="e4m3 x e2m1 (mxf8f6f4), f32 accumulate", data="synthetic", config=workload_config(args.workload),
+                    parallelism=main_r["parallelism"], exchange=(args.exchange if world > 1 else None),
+                    timing="value: per sample a barrier over the ranks, a device synchronise and an L2 flush (256 MB fill), then CUDA events "
+                           "on the launching stream around the step, max over ranks, value = tokens / median sample; e2e: wall clock "
+                           "around each synchronous host call, calls back to back (inputs larger than L2: 1.4-3.4 GB of weights per step)",
+                    active_experts=main_r["active_experts"], e2e=main_r.get("e2e"), gpu_launches=main_r["gpu_launches_per_step"] * k,
+                    clocks=main_r["clocks"], roofline=main_r.get("roofline"), whole_step=main_r["whole_step"],
+                    kernels_ms=main_r.get("kernels_ms"), cpu_baseline=cpu, parity=parity, identity=identity(args, dev))
+        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

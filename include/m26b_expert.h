@@ -27,6 +27,8 @@ extern "C" {
 
 typedef struct m26b_layer m26b_layer;
 typedef struct m26b_scratch m26b_scratch;
+typedef struct m26b_exchange m26b_exchange;
+typedef struct m26b_ep m26b_ep;
 
 #define M26B_HIDDEN 4096
 #define M26B_INTERMEDIATE 2048
@@ -62,6 +64,14 @@ int m26b_layer_new_from_checkpoint(const uint8_t* gate_w, const uint8_t* gate_s,
  * scale byte lies in [2, 252]. Informational here: the block-scaled MMA takes
  * every UE8M0 byte 0..254, and byte 255 is stored as 254 at prepare time. */
 int m26b_layer_all_normal(const m26b_layer* layer);
+/* Read-only view of the prepared operand image in device memory, for tests of the repack (the reference proves its
+ * prepare step a byte permutation the same way: crates/mimo26-expert/kernels/b1/prepared.cuh:63-88, tests/b1/host.cpp).
+ * which: 0 = gate/up payload [E][I/128][256 rows][2048 B] (rows 0..127 gate, 128..255 up of the same 128 features),
+ * 1 = gate/up scale blocks [E][I/128][32 chunks][2][512 B], 2 = down payload [E][4096][I/2 B],
+ * 3 = down scale blocks [E][16][I/128][2][512 B]; a 512-byte scale block holds rows r = 0..127 x K32 blocks kb = 0..3 of
+ * one 128-wide K chunk at byte (r % 32) * 16 + (r / 32) * 4 + kb. E = the experts the layer holds, I = its local
+ * intermediate width. Returns NULL for a bad argument; *bytes (may be NULL) receives the image size. */
+const void* m26b_layer_image(const m26b_layer* layer, int which, uint64_t* bytes);
 /* Local intermediate width of the layer (2048 / tp_size). */
 int m26b_layer_i_local(const m26b_layer* layer);
 /* Replaces m26s_b1_layer_free (b1_serve.cu:270-276). */
@@ -184,7 +194,6 @@ int m26b_produce_dev(const float* logits, const float* bias, uint32_t rows, int3
  *   set_wait_ms: the bound of the wait (default 2000 ms).
  *   publish_as: marks the next step as published by `peer_rank` from the host; for single-process tests and for a
  *             coordinator that stands in for a rank it knows to be idle. */
-typedef struct m26b_exchange m26b_exchange;
 int m26b_exchange_new(uint64_t plane_bytes, uint32_t rank, uint32_t world, m26b_exchange** out, uint8_t* handle_out,
                       char* err, size_t errlen);
 int m26b_exchange_connect(m26b_exchange* x, const uint8_t* handles, char* err, size_t errlen);
@@ -198,6 +207,20 @@ int m26b_exchange_sum_residual_dev(m26b_exchange* x, uint64_t n_elems, const flo
                                    char* err, size_t errlen);
 int m26b_exchange_status(m26b_exchange* x, void* stream, char* err, size_t errlen);
 void m26b_exchange_free(m26b_exchange* x);
+
+/* m26b_ffn for one rank of a tensor-parallel group inside one box (one process per GPU): the host-pointer entry a
+ * serving loop calls once per request on every rank, where the reference's ranks each receive the request frame and
+ * return a BF16 partial for the coordinator to sum (crates/mimo26-spark/src/serve.rs:206-246, then
+ * crates/mimo26-wire/src/l4.rs:169-244). The request goes up from HOST memory exactly as in m26b_ffn, the rank's slice
+ * runs with its BF16 plane written into the exchange window `x`, the planes are summed in rank order over NVLink
+ * (m26b_exchange_sum_dev), and the FP32 sum [rows*4096] comes back to HOST memory on the ranks that pass sum_out (NULL
+ * elsewhere: one rank downloading is enough). Every rank of the group must make the call for every request.
+ * rows x 8192 bytes must fit the exchange plane. Synchronous. ms (or NULL): [0] upload + enqueue, [1] GPU time
+ * including the exchange, [2] host tail, [3] token tiles, the rest 0. Returns m26b_ffn's codes, or 5 when a peer's
+ * plane did not arrive within the exchange's bound. */
+int m26b_ffn_tp(const m26b_layer* layer, m26b_scratch* scratch, m26b_exchange* x, const uint8_t* payload, size_t payload_pitch,
+                const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
+                float* sum_out, float* ms, char* err, size_t errlen);
 
 /* Expert parallelism inside one NVLink box, one process per GPU (BASELINE configs[4]; the reference has no expert-
  * parallel mode: it shards every expert's intermediate dimension over its four ranks, crates/mimo26-repack/src/geom.rs:29-35).
@@ -215,7 +238,6 @@ void m26b_exchange_free(m26b_exchange* x);
  * rendezvous ran out of time (default bound 5 s), 4 on a quantiser / combine fault. Windows are connected like the plane
  * exchange's (64-byte handles gathered by the caller, or connect_local inside one process); publish_as marks a
  * rendezvous (0 rows ready of the NEXT step, 1 results complete of the CURRENT step) as reached by `peer_rank`. */
-typedef struct m26b_ep m26b_ep;
 int m26b_layer_new_from_checkpoint_ep(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w, const uint8_t* up_s,
                                       const uint8_t* down_w, const uint8_t* down_s, uint32_t ep_rank, uint32_t ep_size,
                                       m26b_layer** out, char* err, size_t errlen);
@@ -233,6 +255,13 @@ int m26b_ep_begin_dev(m26b_ep* e, const void* x, int x_dtype, const uint8_t* x_s
 int m26b_ep_compute_dev(m26b_ep* e, const m26b_layer* l, m26b_scratch* s, void* stream, char* err, size_t errlen);
 int m26b_ep_finish_dev(m26b_ep* e, uint16_t* bf16_out, float* partial_out, void* stream, char* err, size_t errlen);
 int m26b_ep_status(m26b_ep* e, void* stream, char* err, size_t errlen);
+/* One expert-parallel step from HOST memory on the scratch's stream: this rank's block of the step's tokens goes up
+ * (quantised rows at payload_pitch / scales_pitch as in m26b_ffn, ids, weights; rows = m26b_ep_rows of this rank, which
+ * may be 0), begin / compute / finish run, and the rank's BF16 rows [rows*4096] come back. Synchronous; every rank
+ * must make the call. Returns 0, or the first failing stage's code. */
+int m26b_ep_ffn(m26b_ep* e, const m26b_layer* l, m26b_scratch* s, const uint8_t* payload, size_t payload_pitch,
+                const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
+                uint16_t* bf16_out, char* err, size_t errlen);
 void m26b_ep_free(m26b_ep* e);
 
 /* DS41RTE3 v3 frames (host memory): the request a rank receives and the compact return it sends

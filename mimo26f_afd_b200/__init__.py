@@ -16,6 +16,7 @@ from .expert import (  # noqa: F401
     ffn,
     ffn_dev,
     ffn_strided,
+    ffn_tp,
     plan_static,
     produce_dev,
     quantize_dev,

@@ -20,6 +20,7 @@ SYMBOLS = (
     "m26b_ep_set_wait_ms", "m26b_ep_publish_as", "m26b_ep_begin_dev", "m26b_ep_compute_dev", "m26b_ep_finish_dev",
     "m26b_ep_status", "m26b_ep_free", "m26b_produce_dev",
     "m26b_rank_sum_residual_dev", "m26b_exchange_sum_residual_dev", "m26b_scratch_set_route_output", "m26b_ep_set_route_output",
+    "m26b_ffn_tp", "m26b_ep_ffn", "m26b_layer_image",
     "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c", "m26b_frame_crc32c_table", "m26b_frame_encode_request",
     "m26b_serve_frame", "m26b_frame_parse_return", "m26b_frame_check_request",
 )
@@ -45,6 +46,8 @@ def lib() -> C.CDLL:
     L.m26b_layer_new_from_checkpoint.argtypes = [u8p] * 6 + [C.c_uint32, C.c_uint32, C.POINTER(vp), *err]
     L.m26b_layer_all_normal.argtypes = [vp]
     L.m26b_layer_i_local.argtypes = [vp]
+    L.m26b_layer_image.argtypes = [vp, C.c_int, C.POINTER(C.c_uint64)]
+    L.m26b_layer_image.restype = C.c_void_p
     L.m26b_layer_free.argtypes = [vp]
     L.m26b_layer_free.restype = None
     L.m26b_scratch_new.argtypes = [C.POINTER(vp), *err]
@@ -54,6 +57,8 @@ def lib() -> C.CDLL:
     L.m26b_ffn_dev.argtypes = [vp, vp, vp, C.c_int, u8p, C.c_int, i32p, f32p, C.c_uint32, u16p, f32p, vp, *err]
     L.m26b_scratch_status.argtypes = [vp, vp, *err]
     L.m26b_scratch_set_debug.argtypes = [vp, C.c_uint32]
+    L.m26b_ffn_tp.argtypes = [vp, vp, vp, u8p, C.c_size_t, u8p, C.c_size_t, i32p, f32p, C.c_uint32, f32p, f32p, *err]
+    L.m26b_ep_ffn.argtypes = [vp, vp, vp, u8p, C.c_size_t, u8p, C.c_size_t, i32p, f32p, C.c_uint32, u16p, *err]
     L.m26b_scratch_set_route_output.argtypes = [vp, C.c_int]
     L.m26b_ep_set_route_output.argtypes = [vp, C.c_int]
     L.m26b_scratch_timings.argtypes = [vp, f32p, *err]
@@ -106,7 +111,7 @@ def lib() -> C.CDLL:
                                            C.POINTER(C.c_uint32), *err]
     L.m26b_produce_dev.argtypes = [f32p, f32p, C.c_uint32, i32p, f32p, vp, C.c_int, C.c_int, u8p, u8p, u32p, vp, *err]
     for name in SYMBOLS:
-        if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version", "m26b_exchange_plane", "m26b_exchange_free",
+        if name not in ("m26b_layer_free", "m26b_scratch_free", "m26b_version", "m26b_exchange_plane", "m26b_exchange_free", "m26b_layer_image",
                         "m26b_ep_free", "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c",
                         "m26b_frame_crc32c_table"):
             getattr(L, name).restype = C.c_int

@@ -222,13 +222,13 @@ struct m26b_scratch {
     uint32_t debug = 0;
     bool y16 = false;           // route outputs (FC2 rows) as BF16 instead of FP32
     Dev xq, xs, iw, dstage, inverse, original, gweights, experts, tiles, items1, items2, x_perm, sfb1, mid_q, mid_sf, mid_f32, y,
-        partial, bf16, status, gather, plan_cnt;
+        partial, bf16, status, gather, plan_cnt, tp_sum;
     TokenMaps map_x, map_mid;
     PairMaps pair_x, pair_mid;
     void* pair_sfb1_base = nullptr; void* pair_midsf_base = nullptr; size_t pair_sfb1_n = 0, pair_midsf_n = 0;
     void* map_x_base = nullptr; void* map_mid_base = nullptr;
     uint64_t map_x_rows = 0, map_mid_rows = 0; int map_mid_cols = 0;
-    std::vector<uint8_t> hiw;
+    uint8_t* hiw = nullptr; size_t hiw_n = 0;   // pinned, grow-only: ids and weights of a larger request
     uint8_t* hstage = nullptr;       // pinned: rows, scales, ids and weights of a small request, uploaded in one copy
     Status* hstatus = nullptr;       // pinned
     // last pass
@@ -540,6 +540,62 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     return 0;
 }
 
+// Host request -> device, on the scratch's stream: rows, scales, ids and weights. Requests of at most kStageRows tokens
+// are packed into one pinned block and go up in one copy; larger ones in three copies (contiguous rows as linear
+// copies), with ids and weights staged through pinned memory so that no copy falls back to the synchronous pageable path.
+int upload_request(m26b_scratch* S, const uint8_t* payload, size_t payload_pitch, const uint8_t* scales, size_t scales_pitch,
+                   const int32_t* ids, const float* weights, uint32_t rows, const uint8_t** xq_out, const uint8_t** xs_out,
+                   const int32_t** ids_out, const float** w_out, char* err, size_t errlen) {
+    cudaError_t e;
+    const size_t routes = size_t(rows) * kTopK;
+    const uint8_t* xq_d;
+    const uint8_t* xs_d;
+    const int32_t* ids_d;
+    const float* w_d;
+    if (rows <= kStageRows) {
+        M26B_CK(S->dstage.ensure(kStageBytes), "m26b staging alloc");
+        const size_t o_s = size_t(rows) * kHidden, o_i = o_s + size_t(rows) * (kHidden / kBlockK), o_w = o_i + routes * 4;
+        for (uint32_t r = 0; r < rows; ++r) {
+            std::memcpy(S->hstage + size_t(r) * kHidden, payload + size_t(r) * payload_pitch, kHidden);
+            std::memcpy(S->hstage + o_s + size_t(r) * (kHidden / kBlockK), scales + size_t(r) * scales_pitch, kHidden / kBlockK);
+        }
+        std::memcpy(S->hstage + o_i, ids, routes * 4);
+        std::memcpy(S->hstage + o_w, weights, routes * 4);
+        M26B_CK(cudaMemcpyAsync(S->dstage.p, S->hstage, o_w + routes * 4, cudaMemcpyHostToDevice, S->st), "m26b request upload");
+        xq_d = S->dstage.as<uint8_t>(); xs_d = xq_d + o_s;
+        ids_d = reinterpret_cast<const int32_t*>(xq_d + o_i); w_d = reinterpret_cast<const float*>(xq_d + o_w);
+    } else {
+        M26B_CK(S->xq.ensure(size_t(rows) * kHidden), "m26b x alloc");
+        M26B_CK(S->xs.ensure(size_t(rows) * (kHidden / kBlockK)), "m26b xs alloc");
+        M26B_CK(S->iw.ensure(routes * 8), "m26b ids/w alloc");
+        // contiguous rows go up as one linear copy (a pitched copy of the same bytes takes a slower path)
+        if (payload_pitch == kHidden)
+            M26B_CK(cudaMemcpyAsync(S->xq.p, payload, size_t(rows) * kHidden, cudaMemcpyHostToDevice, S->st), "m26b x upload");
+        else
+            M26B_CK(cudaMemcpy2DAsync(S->xq.p, kHidden, payload, payload_pitch, kHidden, rows, cudaMemcpyHostToDevice, S->st),
+                    "m26b x upload");
+        if (scales_pitch == kHidden / kBlockK)
+            M26B_CK(cudaMemcpyAsync(S->xs.p, scales, size_t(rows) * (kHidden / kBlockK), cudaMemcpyHostToDevice, S->st), "m26b xs upload");
+        else
+            M26B_CK(cudaMemcpy2DAsync(S->xs.p, kHidden / kBlockK, scales, scales_pitch, kHidden / kBlockK, rows,
+                                      cudaMemcpyHostToDevice, S->st), "m26b xs upload");
+        if (S->hiw_n < routes * 8) {
+            // the previous request's copy out of this block has finished: every host entry point ends with a stream sync
+            if (S->hiw) cudaFreeHost(S->hiw);
+            S->hiw = nullptr; S->hiw_n = 0;
+            M26B_CK(cudaMallocHost(reinterpret_cast<void**>(&S->hiw), routes * 8), "m26b ids/w staging alloc");
+            S->hiw_n = routes * 8;
+        }
+        std::memcpy(S->hiw, ids, routes * 4);
+        std::memcpy(S->hiw + routes * 4, weights, routes * 4);
+        M26B_CK(cudaMemcpyAsync(S->iw.p, S->hiw, routes * 8, cudaMemcpyHostToDevice, S->st), "m26b ids/w upload");
+        xq_d = S->xq.as<uint8_t>(); xs_d = S->xs.as<uint8_t>();
+        ids_d = S->iw.as<int32_t>(); w_d = reinterpret_cast<const float*>(S->iw.as<uint8_t>() + routes * 4);
+    }
+    *xq_out = xq_d; *xs_out = xs_d; *ids_out = ids_d; *w_out = w_d;
+    return 0;
+}
+
 int decode_status(const Status* hs, uint32_t n, char* err, size_t errlen) {
     for (uint32_t i = 0; i < n; ++i) {
         const Status& s = hs[i];
@@ -640,6 +696,15 @@ int m26b_layer_new_from_checkpoint_ep(const uint8_t* gate_w, const uint8_t* gate
     return prepare_layer(gate, up, down, 0, 1, out, err, errlen, int(ep_rank) * n_local, n_local);
 }
 
+const void* m26b_layer_image(const m26b_layer* L, int which, uint64_t* bytes) {
+    if (!L || which < 0 || which > 3) return nullptr;
+    const uint64_t n = uint64_t(L->n_local), il = uint64_t(L->i_local);
+    const uint64_t size[4] = {n * 2 * il * (kHidden / 2), n * 2 * il * (kHidden / kBlockK), n * kHidden * (il / 2), n * kHidden * (il / kBlockK)};
+    const uint8_t* base[4] = {L->w13, L->s13, L->w2, L->s2};
+    if (bytes) *bytes = size[which];
+    return base[which];
+}
+
 int m26b_layer_all_normal(const m26b_layer* L) { return L && L->all_normal ? 1 : 0; }
 int m26b_layer_i_local(const m26b_layer* L) { return L ? L->i_local : 0; }
 
@@ -698,6 +763,7 @@ void m26b_scratch_free(m26b_scratch* S) {
     if (S->st) cudaStreamDestroy(S->st);
     if (S->hstatus) cudaFreeHost(S->hstatus);
     if (S->hstage) cudaFreeHost(S->hstage);
+    if (S->hiw) cudaFreeHost(S->hiw);
     delete S;
 }
 
@@ -725,7 +791,6 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     cudaError_t e;
     const auto t0 = std::chrono::steady_clock::now();
     S->kev_quant = false;          // this entry point takes quantised rows: the quantiser slot of the timings reads zero
-    const size_t routes = size_t(rows) * kTopK;
     const uint32_t pass_rows = rows < kMaxPassRows ? rows : kMaxPassRows;
     const uint32_t passes = (rows + kMaxPassRows - 1) / kMaxPassRows;
     if (passes > 64) { set_msg(err, errlen, "m26b ffn: bad rows/handles/pitch"); return 1; }
@@ -736,40 +801,8 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     const uint8_t* xs_d;
     const int32_t* ids_d;
     const float* w_d;
-    if (rows <= kStageRows) {
-        M26B_CK(S->dstage.ensure(kStageBytes), "m26b staging alloc");
-        const size_t o_s = size_t(rows) * kHidden, o_i = o_s + size_t(rows) * (kHidden / kBlockK), o_w = o_i + routes * 4;
-        for (uint32_t r = 0; r < rows; ++r) {
-            std::memcpy(S->hstage + size_t(r) * kHidden, payload + size_t(r) * payload_pitch, kHidden);
-            std::memcpy(S->hstage + o_s + size_t(r) * (kHidden / kBlockK), scales + size_t(r) * scales_pitch, kHidden / kBlockK);
-        }
-        std::memcpy(S->hstage + o_i, ids, routes * 4);
-        std::memcpy(S->hstage + o_w, weights, routes * 4);
-        M26B_CK(cudaMemcpyAsync(S->dstage.p, S->hstage, o_w + routes * 4, cudaMemcpyHostToDevice, S->st), "m26b request upload");
-        xq_d = S->dstage.as<uint8_t>(); xs_d = xq_d + o_s;
-        ids_d = reinterpret_cast<const int32_t*>(xq_d + o_i); w_d = reinterpret_cast<const float*>(xq_d + o_w);
-    } else {
-        M26B_CK(S->xq.ensure(size_t(rows) * kHidden), "m26b x alloc");
-        M26B_CK(S->xs.ensure(size_t(rows) * (kHidden / kBlockK)), "m26b xs alloc");
-        M26B_CK(S->iw.ensure(routes * 8), "m26b ids/w alloc");
-        // contiguous rows go up as one linear copy (a pitched copy of the same bytes takes a slower path)
-        if (payload_pitch == kHidden)
-            M26B_CK(cudaMemcpyAsync(S->xq.p, payload, size_t(rows) * kHidden, cudaMemcpyHostToDevice, S->st), "m26b x upload");
-        else
-            M26B_CK(cudaMemcpy2DAsync(S->xq.p, kHidden, payload, payload_pitch, kHidden, rows, cudaMemcpyHostToDevice, S->st),
-                    "m26b x upload");
-        if (scales_pitch == kHidden / kBlockK)
-            M26B_CK(cudaMemcpyAsync(S->xs.p, scales, size_t(rows) * (kHidden / kBlockK), cudaMemcpyHostToDevice, S->st), "m26b xs upload");
-        else
-            M26B_CK(cudaMemcpy2DAsync(S->xs.p, kHidden / kBlockK, scales, scales_pitch, kHidden / kBlockK, rows,
-                                      cudaMemcpyHostToDevice, S->st), "m26b xs upload");
-        S->hiw.resize(routes * 8);
-        std::memcpy(S->hiw.data(), ids, routes * 4);
-        std::memcpy(S->hiw.data() + routes * 4, weights, routes * 4);
-        M26B_CK(cudaMemcpyAsync(S->iw.p, S->hiw.data(), routes * 8, cudaMemcpyHostToDevice, S->st), "m26b ids/w upload");
-        xq_d = S->xq.as<uint8_t>(); xs_d = S->xs.as<uint8_t>();
-        ids_d = S->iw.as<int32_t>(); w_d = reinterpret_cast<const float*>(S->iw.as<uint8_t>() + routes * 4);
-    }
+    rc = upload_request(S, payload, payload_pitch, scales, scales_pitch, ids, weights, rows, &xq_d, &xs_d, &ids_d, &w_d, err, errlen);
+    if (rc) return rc;
     uint16_t* const out_d = S->gather.as<uint16_t>();
     // stage timings cost four events between the kernels (and the overlap of dependent launches): only when asked for
     const bool timed = ms != nullptr && passes == 1;
@@ -1306,6 +1339,116 @@ void m26b_ep_free(m26b_ep* E) {
     if (E->fault) cudaFree(E->fault);
     if (E->hfault) cudaFreeHost(E->hfault);
     delete E;
+}
+
+// ---- host entry points of a tensor-parallel / expert-parallel rank -----------------------------------------------
+// m26b_ffn for a rank of a tensor-parallel group inside one box: the request (host rows, as every rank of the
+// reference receives the request frame) goes up, the rank's slice runs with its BF16 plane written straight into the
+// exchange window, the planes are summed over NVLink by the exchange kernel, and the FP32 sum comes back to the host
+// on the ranks that ask for it (sum_out != NULL; one rank is enough).
+int m26b_ffn_tp(const m26b_layer* L, m26b_scratch* S, m26b_exchange* X, const uint8_t* payload, size_t payload_pitch,
+                const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
+                float* sum_out, float* ms, char* err, size_t errlen) {
+    if (!L || !S || !X || !rows || payload_pitch < kHidden || scales_pitch < kHidden / kBlockK || !payload || !scales || !ids ||
+        !weights || uint64_t(rows) * kHidden * 2 > X->plane_bytes) {
+        set_msg(err, errlen, "m26b ffn_tp: bad rows/handles/pitch (the request must fit the exchange plane)");
+        return 1;
+    }
+    if (!device_ok(L->device, err, errlen) || !device_ok(S->device, err, errlen) || !device_ok(X->device, err, errlen)) return 1;
+    if (uint32_t(X->world) != L->tp_size || uint32_t(X->rank) != L->tp_rank) {
+        set_msg(err, errlen, "m26b ffn_tp: the exchange window and the layer belong to different ranks");
+        return 1;
+    }
+    cudaError_t e;
+    const auto t0 = std::chrono::steady_clock::now();
+    S->kev_quant = false;
+    const uint32_t pass_rows = rows < kMaxPassRows ? rows : kMaxPassRows;
+    const uint32_t passes = (rows + kMaxPassRows - 1) / kMaxPassRows;
+    if (passes > 64) { set_msg(err, errlen, "m26b ffn_tp: bad rows/handles/pitch"); return 1; }
+    int rc = ensure_pass(S, pass_rows, L->i_local, false, err, errlen);
+    if (rc) return rc;
+    M26B_CK(S->tp_sum.ensure(size_t(rows) * kHidden * 4), "m26b sum alloc");
+    const uint8_t* xq_d;
+    const uint8_t* xs_d;
+    const int32_t* ids_d;
+    const float* w_d;
+    rc = upload_request(S, payload, payload_pitch, scales, scales_pitch, ids, weights, rows, &xq_d, &xs_d, &ids_d, &w_d, err, errlen);
+    if (rc) return rc;
+    uint16_t* const plane = static_cast<uint16_t*>(m26b_exchange_plane(X));
+    M26B_CK(cudaEventRecord(S->e0, S->st), "m26b event 0");
+    for (uint32_t ps = 0; ps < passes; ++ps) {
+        const uint32_t r0 = ps * kMaxPassRows, n = rows - r0 < kMaxPassRows ? rows - r0 : kMaxPassRows;
+        rc = enqueue_pass(L, S, xq_d + size_t(r0) * kHidden, xs_d + size_t(r0) * (kHidden / kBlockK), ids_d + size_t(r0) * kTopK,
+                          w_d + size_t(r0) * kTopK, n, plane + size_t(r0) * kHidden, nullptr, S->status.as<Status>() + ps, S->st,
+                          false, err, errlen);
+        if (rc) return rc;
+    }
+    rc = m26b_exchange_sum_residual_dev(X, uint64_t(rows) * kHidden, nullptr, S->tp_sum.as<float>(), S->st, err, errlen);
+    if (rc) return rc;
+    M26B_CK(cudaEventRecord(S->e1, S->st), "m26b event 1");
+    if (sum_out)
+        M26B_CK(cudaMemcpyAsync(sum_out, S->tp_sum.p, size_t(rows) * kHidden * 4, cudaMemcpyDeviceToHost, S->st), "m26b sum download");
+    M26B_CK(cudaMemcpyAsync(S->hstatus, S->status.p, sizeof(Status) * passes, cudaMemcpyDeviceToHost, S->st), "m26b status download");
+    // the exchange's error word rides in the unused tail of the pinned status block
+    uint32_t* xerr = reinterpret_cast<uint32_t*>(S->hstatus + 63) + 15;
+    M26B_CK(cudaMemcpyAsync(xerr, &static_cast<ExchangeWindow*>(X->window)->error, 4, cudaMemcpyDeviceToHost, S->st), "m26b exchange status");
+    const auto t1 = std::chrono::steady_clock::now();
+    M26B_CK(cudaStreamSynchronize(S->st), "m26b compute sync");
+    S->pending = false;
+    rc = decode_status(S->hstatus, passes, err, errlen);
+    if (rc) return rc;
+    if (*xerr) return m26b_exchange_status(X, S->st, err, errlen);      // clears the word and words the message
+    if (ms) {
+        float gpu_ms = 0.f;
+        cudaEventElapsedTime(&gpu_ms, S->e0, S->e1);
+        ms[0] = std::chrono::duration<float, std::milli>(t1 - t0).count();
+        ms[1] = gpu_ms;
+        const float tail = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t1).count() - gpu_ms;
+        ms[2] = tail > 0.f ? tail : 0.f;
+        ms[3] = float(S->hstatus[0].meta.n_tiles);
+        ms[4] = ms[5] = ms[6] = ms[7] = 0.f;
+    }
+    return 0;
+}
+
+// The same for a rank of an expert-parallel group: this rank's block of the step's tokens goes up (quantised rows, ids,
+// weights), the three phases of the step run on the scratch's stream, and the rank's BF16 result rows come back.
+int m26b_ep_ffn(m26b_ep* E, const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_t payload_pitch,
+                const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
+                uint16_t* bf16_out, char* err, size_t errlen) {
+    if (!E || !L || !S || payload_pitch < kHidden || scales_pitch < kHidden / kBlockK || rows != E->lo[E->rank + 1] - E->lo[E->rank] ||
+        (rows && (!payload || !scales || !ids || !weights || !bf16_out))) {
+        set_msg(err, errlen, "m26b ep_ffn: bad rows/handles/pitch (rows must be this rank's token block)");
+        return 1;
+    }
+    if (!device_ok(E->device, err, errlen) || !device_ok(S->device, err, errlen)) return 1;
+    cudaError_t e;
+    int rc;
+    const uint8_t* xq_d = nullptr;
+    const uint8_t* xs_d = nullptr;
+    const int32_t* ids_d = nullptr;
+    const float* w_d = nullptr;
+    if (rows) {
+        rc = upload_request(S, payload, payload_pitch, scales, scales_pitch, ids, weights, rows, &xq_d, &xs_d, &ids_d, &w_d, err, errlen);
+        if (rc) return rc;
+        M26B_CK(S->gather.ensure(size_t(rows) * kHidden * 2), "m26b out alloc");
+    }
+    // a rank without tokens still takes part in the step's rendezvous; begin_dev needs non-null pointers only for rows > 0
+    static const uint8_t kNone[16] = {};
+    rc = m26b_ep_begin_dev(E, rows ? static_cast<const void*>(xq_d) : kNone, 2, rows ? xs_d : kNone, 0,
+                           rows ? ids_d : reinterpret_cast<const int32_t*>(kNone), rows ? w_d : reinterpret_cast<const float*>(kNone), rows,
+                           S->st, err, errlen);
+    if (rc) return rc;
+    rc = m26b_ep_compute_dev(E, L, S, S->st, err, errlen);
+    if (rc) return rc;
+    if (rows) {
+        rc = m26b_ep_finish_dev(E, S->gather.as<uint16_t>(), nullptr, S->st, err, errlen);
+        if (rc) return rc;
+        M26B_CK(cudaMemcpyAsync(bf16_out, S->gather.p, size_t(rows) * kHidden * 2, cudaMemcpyDeviceToHost, S->st), "m26b bf16 download");
+    }
+    rc = m26b_scratch_status(S, S->st, err, errlen);
+    if (rc) return rc;
+    return m26b_ep_status(E, S->st, err, errlen);
 }
 
 // ---- DS41RTE3 v3 frames ----------------------------------------------------------------------

@@ -90,6 +90,16 @@ class Layer:
             C.byref(out), err, 256), err)
         return cls(out.value)
 
+    IMAGES = {"w13": 0, "s13": 1, "w2": 2, "s2": 3}
+
+    def image(self, which: str):
+        """(device address, bytes) of a prepared operand image: ``w13`` / ``s13`` / ``w2`` / ``s2`` (read-only)."""
+        n = C.c_uint64()
+        p = _native.lib().m26b_layer_image(self._h, self.IMAGES[which], C.byref(n))
+        if not p:
+            raise ExpertError(1, "m26b layer image: bad handle")
+        return int(p), int(n.value)
+
     def all_scales_normal(self) -> bool:
         return _native.lib().m26b_layer_all_normal(self._h) != 0
 
@@ -205,6 +215,18 @@ def ffn_strided(layer: Layer, scratch: Scratch, hidden: np.ndarray, row_stride: 
     weights = np.ascontiguousarray(weights, dtype=np.float32)
     base = hidden.ctypes.data
     return _ffn_raw(layer, scratch, base, row_stride, base + H, row_stride, ids, weights, rows, bf16_out)
+
+
+def ffn_tp(layer: Layer, scratch: Scratch, exchange: "Exchange", payload, scales, ids, weights, rows: int, sum_out=None) -> FfnStats:
+    """``ffn`` for one rank of a tensor-parallel group: host rows in, the rank-ordered FP32 sum of every rank's plane out
+    (``sum_out`` [rows*4096] float32 in host memory, or None on ranks that do not need it). Arguments are host arrays or
+    addresses of (pinned) host buffers. Every rank of the group makes the call for every request."""
+    ms = (C.c_float * 8)()
+    err = C.create_string_buffer(256)
+    rc = _native.lib().m26b_ffn_tp(layer._h, scratch._h, exchange._h, _ptr(payload), H, _ptr(scales), H // 32, _ptr(ids),
+                                   _ptr(weights), rows, _ptr(sum_out), ms, err, 256)
+    _check(rc, err)
+    return FfnStats(ms[0], ms[1], ms[2], int(ms[3]), (ms[4], ms[5], ms[6], ms[7]))
 
 
 X_BF16, X_F32, X_E4M3 = 0, 1, 2
@@ -375,6 +397,12 @@ class ExpertParallel:
         self.begin(x, ids, weights, rows, x_dtype=x_dtype, x_scales=x_scales, codec=codec, stream=stream)
         self.compute(layer, scratch, stream=stream)
         self.finish(bf16_out, partial_out, stream=stream)
+
+    def ffn_host(self, layer: "Layer", scratch: "Scratch", payload, scales, ids, weights, rows: int, bf16_out) -> None:
+        """One step from host memory: this rank's quantised rows, ids and weights up, its BF16 rows back (synchronous)."""
+        err = C.create_string_buffer(256)
+        _check(_native.lib().m26b_ep_ffn(self._h, layer._h, scratch._h, _ptr(payload), H, _ptr(scales), H // 32, _ptr(ids),
+                                         _ptr(weights), rows, _ptr(bf16_out), err, 256), err)
 
     def status(self, stream=None) -> None:
         err = C.create_string_buffer(256)

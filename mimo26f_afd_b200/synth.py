@@ -132,6 +132,37 @@ def activations_bf16(seed: int, tokens: int, first_token: int = 0) -> np.ndarray
     return bf16_rne_np(normal_np(seed, 0, tokens * H, first_token * H)).reshape(tokens, H)
 
 
+def activations_bf16_torch(seed: int, tokens: int, device, first_token: int = 0):
+    """Device-side generator for batches too large to make on the host in reasonable time: BF16 N(0,1) bit patterns
+    [tokens, 4096] as int16, a deterministic function of (seed, token, column) on the same counter stream as
+    ``activations_bf16`` but with the Box-Muller step in FP32 on the device, so the two are NOT bit-identical. Used
+    where no host-side oracle looks at the values (timing of the 65,536-token batch). torch is the allocator and the
+    element-wise engine here, not a compute path of the library."""
+    import torch
+
+    def s64(v: int) -> int:
+        return v - (1 << 64) if v >= (1 << 63) else v
+
+    def lsr(z, n):
+        return (z >> n) & ((1 << (64 - n)) - 1)
+
+    base = s64(stream_base(seed, 100))
+    out = torch.empty((tokens, H), dtype=torch.int16, device=device)
+    step = 2048
+    for t0 in range(0, tokens, step):
+        n = min(step, tokens - t0)
+        idx = torch.arange((first_token + t0) * H + 1, (first_token + t0 + n) * H + 1, dtype=torch.int64, device=device)
+        z = base + idx * s64(GOLDEN)
+        z = (z ^ lsr(z, 30)) * s64(M1)
+        z = (z ^ lsr(z, 27)) * s64(M2)
+        z = z ^ lsr(z, 31)
+        u1 = (lsr(z, 40).to(torch.float32) + 1.0) / 16777217.0
+        u2 = (z & 0xFFFFFF).to(torch.float32) / 16777216.0
+        g = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(6.283185307179586 * u2)
+        out[t0:t0 + n] = g.to(torch.bfloat16).view(torch.int16).reshape(n, H)
+    return out
+
+
 def routing(seed: int, tokens: int, zipf_s: float = 0.0):
     """Top-8 routing: FP32 logits N(0,1) (+ log popularity, Zipf exponent ``zipf_s`` over a seeded
     expert permutation), top-8 by value with ties to the lower id

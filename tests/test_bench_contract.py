@@ -52,3 +52,69 @@ def test_clock_record_summary_from_fake_samples():
               ["garbage"]]
     s = c.summary()
     assert s["samples"] == 3 and s["sm_mhz"] == 1410.0 and s["sm_max_mhz"] == 1965.0 and s["reasons"] == ["sw_power_cap"]
+
+
+def _load_bench():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    argv, sys.argv = sys.argv, ["bench.py"]
+    try:
+        spec.loader.exec_module(bench)
+    finally:
+        sys.argv = argv
+    return bench
+
+
+def test_config_statistics_and_traffic_record():
+    """`config` names the workload only and is what both arms print; a sample set is reported as median / min / max /
+    mean; the traffic of the roofline is read from the record next to the profiler summaries, not typed into the script."""
+    bench = _load_bench()
+    for name in ("decode16", "verify128", "prefill8k", "prefill64k"):
+        c = bench.workload_config(name)
+        assert c["workload"] == name and c["tokens"] == bench.WORKLOADS[name]["tokens"] and c["top_k"] == 8
+        assert "parallelism" not in c and "model" not in c
+    assert bench.workload_config("verify128")["routing"] == "zipf1.2" and bench.workload_config("decode16")["routing"] == "uniform"
+    s = bench.stats([3.0, 1.0, 2.0, 10.0, 4.0])
+    assert s == dict(median=3.0, min=1.0, max=10.0, mean=4.0, samples=5)
+    t = bench.profiled_traffic()
+    assert t["decode16"]["fc1_dram_bytes"] > 9e8 and "profiles/" in t["decode16"]["source"] and t["prefill8k"]["fc1_dram_bytes"] > 2e9
+    src = open(os.path.join(ROOT, "bench.py")).read()
+    assert "915809536" not in src and "2774330624" not in src
+    assert bench.identity(type("A", (), {})())["seed"] == "0x26afd"
+
+
+def _ranks_worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    bench = _load_bench()
+    ctx = object.__new__(bench.Ctx)
+    ctx.dev, ctx.rank, ctx.world = torch.device("cpu"), rank, world
+    per, spread = ctx.over_ranks([1.0 + rank, 5.0 - 2 * rank, 2.0])          # rank 0: 1, 5, 2; rank 1: 2, 3, 2
+    ok_all = ctx.all_true(True)
+    ok_one = ctx.all_true(rank == 0)
+    q.put((rank, per, spread, ok_all, ok_one))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sample_time_is_the_maximum_over_ranks_and_parity_needs_every_rank():
+    """Two gloo ranks: a sample's time is the slowest rank's, the spread is the median difference between ranks, and a
+    parity flag is true only when every rank says so."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ranks_worker, args=(r, 2, 29731, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, per, spread, ok_all, ok_one in got:
+        assert per == [2.0, 5.0, 2.0] and spread == 1.0 and ok_all is True and ok_one is False
