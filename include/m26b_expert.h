@@ -222,7 +222,7 @@ int m26b_ffn_tp(const m26b_layer* layer, m26b_scratch* scratch, m26b_exchange* x
                 const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
                 float* sum_out, float* ms, char* err, size_t errlen);
 
-/* Expert parallelism inside one NVLink box, one process per GPU (BASELINE configs[4]; the reference has no expert-
+/* Expert parallelism inside one NVLink box, one process per GPU (the reference has no expert-
  * parallel mode: it shards every expert's intermediate dimension over its four ranks, crates/mimo26-repack/src/geom.rs:29-35).
  * Rank r holds experts [r 256/G, (r+1) 256/G) (m26b_layer_new_from_checkpoint_ep: the six checkpoint tensors stacked over
  * THOSE experts) and owns a contiguous block of the step's tokens (the first `tokens % G` ranks one token more;

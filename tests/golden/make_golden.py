@@ -27,7 +27,9 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("M26B_REFERENCE_TREE", "")
+if not REF:
+    raise SystemExit("usage: make_golden.py REFERENCE_TREE   (or set M26B_REFERENCE_TREE)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
 # the reference's packages must win: keep this repository's root (which has its own `oracle/`) off sys.path

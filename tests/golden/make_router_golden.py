@@ -12,7 +12,9 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.sep, "root", "reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("M26B_REFERENCE_TREE", "")
+if not REF:
+    raise SystemExit("usage: make_router_golden.py REFERENCE_TREE   (or set M26B_REFERENCE_TREE)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
 sys.path = [p for p in sys.path if os.path.abspath(p or ".") != REPO]

@@ -484,7 +484,7 @@ def check_ffn(layer, scratch, dev, oracle_mod, tokens, zipf, codec, tp_rank=0, t
 
 
 def test_ffn_decode_16_tokens_wire_codec(layer, scratch, dev, oracle_mod):
-    """BASELINE configs 0/1: 16 tokens, uniform routing, 128 routes over about 102 experts."""
+    """The decode batch: 16 tokens, uniform routing, 128 routes over about 102 experts."""
     r = check_ffn(layer, scratch, dev, oracle_mod, 16, 0.0, codec=0)
     print("decode16", r)
 
@@ -495,7 +495,7 @@ def test_ffn_decode_16_tokens_quant_v1_input(layer, scratch, dev, oracle_mod):
 
 
 def test_ffn_verify_round_128_tokens_zipf(layer, scratch, dev, oracle_mod):
-    """BASELINE config 2: 16 streams x 8 tokens, Zipf(1.2) expert popularity (one expert gets most rows)."""
+    """The speculative verify round: 16 streams x 8 tokens, Zipf(1.2) expert popularity (one expert gets most rows)."""
     r = check_ffn(layer, scratch, dev, oracle_mod, 128, 1.2, codec=0)
     print("verify128", r)
 
@@ -755,7 +755,7 @@ def test_exceptional_weight_scales(dev, oracle_mod):
 
 # ------------------------------------------------------------------------------------------ full size, by properties
 def test_prefill_8192_tokens_properties_and_sampled_oracle(layer, dev, oracle_mod):
-    """BASELINE config 3 at full size. The oracle cannot run 65,536 routes, so: (a) the output is row-local -
+    """The 8,192-token prefill segment at full size. The oracle cannot run 65,536 routes, so: (a) the output is row-local -
     permuting the tokens permutes the outputs bit for bit, and two half-size calls give the same bytes; (b)
     doubling the route weights doubles the FP32 plane exactly; (c) the routes of two experts are checked
     against the oracle."""
@@ -835,7 +835,7 @@ def test_prefill_8192_tokens_properties_and_sampled_oracle(layer, dev, oracle_mo
 
 
 def test_config4_65536_tokens_zipf_through_the_host_entry_point(layer, dev, oracle_mod):
-    """BASELINE config 4's batch (65,536 tokens, Zipf 1.0: one expert receives about 62,000 rows) on one GPU through
+    """The long-prefill batch (65,536 tokens, Zipf 1.0: one expert receives about 62,000 rows) on one GPU through
     m26b_ffn, which cuts it into passes of 16,384 tokens. Properties: the bytes do not depend on the cut (four
     quarter-size calls and a shifted cut give the same rows), and sampled tokens match the oracle end to end."""
     import mimo26f_afd_b200 as M
