@@ -39,10 +39,7 @@ constexpr int kPairThreads = kGemmThreads;
 constexpr int kAccBufs = 3;                            // ring of 128-column accumulator buffers
 constexpr uint32_t kPairSfSlot0 = kAccBufs * kMaxN;    // scale slots above the accumulators
 constexpr uint32_t kPairSfSlots = 8;                   // 16 columns each: SFA tile 0, SFA tile 1, SFB
-#ifndef M26B_PAIR_LEAD
-#define M26B_PAIR_LEAD 3
-#endif
-constexpr int kPairLead = M26B_PAIR_LEAD;              // chunks of tile 0 issued before tile 1 of the item starts
+constexpr int kPairLead = 2;                           // chunks of tile 0 issued before tile 1 of the item starts (1, 2 and 3 time alike)
 static_assert(kPairSfSlot0 + kPairSfSlots * kSfSlotStride <= kTmemCols, "tensor memory holds 512 columns");
 static_assert(kPairLead >= 1 && kPairLead < kPairStages && kPairLead < int(kPairSfSlots), "the lead chunks hold their stages and scale slots");
 
