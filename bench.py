@@ -461,9 +461,10 @@ def run_tp(ctx, name, layer, scratch, k, y16=False, with_e2e=True, with_kernels=
     return res
 
 
-def run_ep(ctx, name, layer, scratch, k, y16=False, with_e2e=True):
+def run_ep(ctx, name, layer, scratch, k, y16=False, with_e2e=True, hot=None):
     """Expert-parallel step: rank r holds 256 / N experts and owns 1 / N of the tokens; rows are gathered from and results
-    scattered to their owners over NVLink inside the permutation and FC2 kernels."""
+    scattered to their owners over NVLink inside the permutation and FC2 kernels. `hot`: the experts every rank holds a
+    copy of (their routes are served by the token's owner)."""
     import torch
 
     from mimo26f_afd_b200 import tp
@@ -478,7 +479,11 @@ def run_ep(ctx, name, layer, scratch, k, y16=False, with_e2e=True):
     xd, idd, wd = inp["xd"], inp["idd"], inp["wd"]
     n_local = E // world
     counts = np.bincount(ids.reshape(-1), minlength=E)
-    per_rank = counts.reshape(world, n_local).sum(1)
+    flat = ids.reshape(-1)
+    owner = np.repeat(np.searchsorted(np.array([tp.shard_tokens(tokens, r, world)[1] for r in range(world)]), np.arange(tokens), side="right"), TOPK)
+    serving = np.where(np.isin(flat, hot), owner, flat // n_local) if hot is not None else flat // n_local
+    per_rank = np.bincount(serving, minlength=world)
+    crossing = int((serving != owner).sum())                   # routed rows whose token lives on another rank
     ep = tp.make_expert_parallel(tokens)
     ep.set_route_output(y16)
     out = torch.empty((max(rows, 1), H), dtype=torch.int16, device=dev)
@@ -507,8 +512,10 @@ def run_ep(ctx, name, layer, scratch, k, y16=False, with_e2e=True):
                              frac=busiest / step_s / 1e12 / MXF8F6F4_PEAK_TFLOPS, algorithmic_flops=busiest),
                whole_step=dict(tflops=FLOP_PER_TOKEN * tokens / step_s / 1e12, tflops_per_gpu=FLOP_PER_TOKEN * tokens / world / step_s / 1e12,
                                routed_rows_per_rank=[int(v) for v in per_rank], imbalance=float(per_rank.max() / max(per_rank.mean(), 1e-9)),
-                               nvlink_bytes_in_busiest_rank=int(per_rank.max() * (world - 1) / world * (H + H // 32)),
-                               nvlink_bytes_out_busiest_rank=int(per_rank.max() * (world - 1) / world * H * (2 if y16 else 4))),
+                               imbalance_without_replicas=float(counts.reshape(world, n_local).sum(1).max() / max(counts.sum() / world, 1e-9)),
+                               replicated_experts=0 if hot is None else int(len(hot)),
+                               routed_rows_crossing_nvlink=crossing, nvlink_bytes_in=crossing * (H + H // 32),
+                               nvlink_bytes_out=crossing * H * (2 if y16 else 4)),
                gpu_launches_per_step=3 + 2 + 6 * ((tokens + PASS_ROWS - 1) // PASS_ROWS) + 1)
     if with_e2e:
         hq, hs = quantised_on_device(ctx, xd, rows)
@@ -527,6 +534,33 @@ def run_ep(ctx, name, layer, scratch, k, y16=False, with_e2e=True):
     ctx.barrier()
     ep.close()
     return res
+
+
+REPLICATED_EXPERTS = 32      # copies of the busiest experts on every expert-parallel rank when the routing is skewed
+
+
+def build_ep_layer(ctx, name):
+    """This rank's expert-parallel layer for a workload: its block of 256 / N experts and, when the workload's routing is
+    skewed, copies of the batch's busiest experts (the same set on every rank: all ranks see the same seeded routing, as a
+    serving system would share its popularity statistics)."""
+    import torch
+
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import synth
+
+    wl = WORKLOADS[name]
+    n_local = E // ctx.world
+    hot = None
+    if wl["zipf"]:
+        ids, _ = synth.routing(synth.MASTER_SEED, wl["tokens"], wl["zipf"])
+        hot = np.argsort(-np.bincount(ids.reshape(-1), minlength=E), kind="stable")[:REPLICATED_EXPERTS].astype(np.int32)
+    wts = synth.layer_torch(synth.MASTER_SEED, ctx.dev, n_experts=n_local, first_expert=ctx.rank * n_local)
+    reps = synth.layer_torch(synth.MASTER_SEED, ctx.dev, experts=hot) if hot is not None else None
+    layer = M.Layer.from_checkpoint_ep(*[wts[n] for n in synth.TENSORS], ep_rank=ctx.rank, ep_size=ctx.world,
+                                       replicas=[reps[n] for n in synth.TENSORS] if hot is not None else None, replica_ids=hot)
+    del wts, reps
+    torch.cuda.empty_cache()
+    return layer, hot
 
 
 def rel_l2(a, b):
@@ -597,9 +631,9 @@ def parity_tp(ctx, layer, scratch):
     return out
 
 
-def parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full):
+def parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full, tag=""):
     """The expert-parallel step against the single-GPU layer run on the same rank over the whole batch: bit for bit, FP32
-    plane and BF16 rows (a GEMM row does not depend on how routes are tiled)."""
+    plane and BF16 rows (a GEMM row does not depend on how routes are tiled, nor on which rank serves it)."""
     import torch
 
     from mimo26f_afd_b200 import expert, synth, tp
@@ -627,8 +661,8 @@ def parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full):
             ep.status(stream.cuda_stream)
             torch.cuda.synchronize()
             same &= bool(torch.equal(got[:hi - lo], ref[lo:hi])) and bool(torch.equal(part[:hi - lo].view(torch.int32), ref_part[lo:hi].view(torch.int32)))
-        out[f"expert_parallel_equals_single_gpu_{tokens}"] = ctx.all_true(same)
-        out["ok"] &= out[f"expert_parallel_equals_single_gpu_{tokens}"]
+        out[f"expert_parallel{tag}_equals_single_gpu_{tokens}"] = ctx.all_true(same)
+        out["ok"] &= out[f"expert_parallel{tag}_equals_single_gpu_{tokens}"]
         ctx.barrier()
         ep.close()
     return out
@@ -739,26 +773,29 @@ def main():
         layer.close()
         del layer
         torch.cuda.empty_cache()
-        n_local = E // world
-        wts = synth.layer_torch(synth.MASTER_SEED, dev, n_experts=n_local, first_expert=rank * n_local)
-        ep_layer = M.Layer.from_checkpoint_ep(*[wts[n] for n in synth.TENSORS], ep_rank=rank, ep_size=world)
-        del wts
+        ep_layer, _ = build_ep_layer(ctx, "prefill8k")
+        ep_layer_hot, hot = build_ep_layer(ctx, "prefill64k")
         weights = synth.layer_torch(synth.MASTER_SEED, dev)
         full_layer = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS])
         del weights
         torch.cuda.empty_cache()
         scratch_full = M.Scratch()
-        parity["expert_parallel_before"] = parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full)
-        if not parity["expert_parallel_before"]["ok"]:
-            fail(ctx, "expert parallel, before timing", parity)
+
+        def ep_parity(key):
+            parity[key] = parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full)
+            parity[key].update({k2: v for k2, v in parity_ep(ctx, ep_layer_hot, full_layer, scratch, scratch_full, "_with_replicas").items() if k2 != "ok"})
+            parity[key]["ok"] = all(v for k2, v in parity[key].items() if k2 != "ok")
+            if not parity[key]["ok"]:
+                fail(ctx, key, parity)
+
+        ep_parity("expert_parallel_before")
         extra["prefill_expert_parallel"] = run_ep(ctx, "prefill8k", ep_layer, scratch, k)
         extra["prefill_expert_parallel_bf16_route_outputs"] = run_ep(ctx, "prefill8k", ep_layer, scratch, k, y16=True, with_e2e=False)
         extra["decode16_expert_parallel"] = run_ep(ctx, "decode16", ep_layer, scratch, k, with_e2e=False)
-        extra["prefill64k_ep"] = run_ep(ctx, "prefill64k", ep_layer, scratch, k_big, with_e2e=False)
-        extra["prefill64k_ep_bf16_route_outputs"] = run_ep(ctx, "prefill64k", ep_layer, scratch, k_big, y16=True, with_e2e=False)
-        parity["expert_parallel_after"] = parity_ep(ctx, ep_layer, full_layer, scratch, scratch_full)
-        if not parity["expert_parallel_after"]["ok"]:
-            fail(ctx, "expert parallel, after timing", parity)
+        extra["prefill64k_ep_no_replicas"] = run_ep(ctx, "prefill64k", ep_layer, scratch, k_big, with_e2e=False)
+        extra["prefill64k_ep"] = run_ep(ctx, "prefill64k", ep_layer_hot, scratch, k_big, with_e2e=False, hot=hot)
+        extra["prefill64k_ep_bf16_route_outputs"] = run_ep(ctx, "prefill64k", ep_layer_hot, scratch, k_big, y16=True, with_e2e=False, hot=hot)
+        ep_parity("expert_parallel_after")
     if rank == 0:
         cpu = cpu_baseline_for(args.workload) if world == 1 and not args.no_extra else None
         line = dict(metric="moe_expert_ffn_tokens_per_s_per_layer", value=main_r["value"], unit="tokens/s", n_gpus=world,

@@ -241,6 +241,19 @@ int m26b_ffn_tp(const m26b_layer* layer, m26b_scratch* scratch, m26b_exchange* x
 int m26b_layer_new_from_checkpoint_ep(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w, const uint8_t* up_s,
                                       const uint8_t* down_w, const uint8_t* down_s, uint32_t ep_rank, uint32_t ep_size,
                                       m26b_layer** out, char* err, size_t errlen);
+/* The same with replicated experts, for skewed routing: besides its own block the rank holds copies of n_rep experts
+ * (ids rep_ids[], a HOST array; their six tensors stacked in that order in the rep_* arguments). EVERY rank of the group
+ * must be built with the same rep_ids. A route to a replicated expert is served by the rank that owns the route's token,
+ * so a popular expert's rows spread over the ranks as evenly as the tokens do and neither its token rows nor its result
+ * rows cross NVLink; routes to all other experts go to the rank whose block holds them, as before. Results stay equal to
+ * the single-GPU layer bit for bit. Cost: 13,369,344 bytes of HBM per replicated expert and rank. n_rep = 0 is exactly
+ * m26b_layer_new_from_checkpoint_ep. */
+int m26b_layer_new_from_checkpoint_ep_replicated(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w, const uint8_t* up_s,
+                                                 const uint8_t* down_w, const uint8_t* down_s, const uint8_t* rep_gate_w,
+                                                 const uint8_t* rep_gate_s, const uint8_t* rep_up_w, const uint8_t* rep_up_s,
+                                                 const uint8_t* rep_down_w, const uint8_t* rep_down_s, const int32_t* rep_ids,
+                                                 uint32_t n_rep, uint32_t ep_rank, uint32_t ep_size, m26b_layer** out, char* err,
+                                                 size_t errlen);
 int m26b_ep_new(uint32_t tokens, uint32_t rank, uint32_t world, m26b_ep** out, uint8_t* handle_out, char* err, size_t errlen);
 int m26b_ep_connect(m26b_ep* e, const uint8_t* handles, char* err, size_t errlen);
 int m26b_ep_connect_local(m26b_ep* e, m26b_ep* const* all, char* err, size_t errlen);

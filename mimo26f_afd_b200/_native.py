@@ -20,7 +20,7 @@ SYMBOLS = (
     "m26b_ep_set_wait_ms", "m26b_ep_publish_as", "m26b_ep_begin_dev", "m26b_ep_compute_dev", "m26b_ep_finish_dev",
     "m26b_ep_status", "m26b_ep_free", "m26b_produce_dev",
     "m26b_rank_sum_residual_dev", "m26b_exchange_sum_residual_dev", "m26b_scratch_set_route_output", "m26b_ep_set_route_output",
-    "m26b_ffn_tp", "m26b_ep_ffn", "m26b_layer_image",
+    "m26b_ffn_tp", "m26b_ep_ffn", "m26b_layer_image", "m26b_layer_new_from_checkpoint_ep_replicated",
     "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c", "m26b_frame_crc32c_table", "m26b_frame_encode_request",
     "m26b_serve_frame", "m26b_frame_parse_return", "m26b_frame_check_request",
 )
@@ -80,6 +80,7 @@ def lib() -> C.CDLL:
     L.m26b_exchange_free.argtypes = [vp]
     L.m26b_exchange_free.restype = None
     L.m26b_layer_new_from_checkpoint_ep.argtypes = [u8p] * 6 + [C.c_uint32, C.c_uint32, C.POINTER(vp), *err]
+    L.m26b_layer_new_from_checkpoint_ep_replicated.argtypes = [u8p] * 12 + [i32p, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(vp), *err]
     L.m26b_ep_new.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(vp), u8p, *err]
     L.m26b_ep_connect.argtypes = [vp, u8p, *err]
     L.m26b_ep_connect_local.argtypes = [vp, C.POINTER(vp), *err]

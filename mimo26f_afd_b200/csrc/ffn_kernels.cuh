@@ -211,11 +211,19 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lan
 // neighbouring weight tile pairs per item).
 //
 // skip_foreign (expert parallelism: this GPU holds a subset of the experts and sees every route of the request): a
-// route to an expert that is not resident here is left out of the plan (inverse = -1) instead of rejecting the request;
-// the other rules still apply to every route.
+// route this rank does not serve (slot_serves: an expert it does not hold, or a replicated expert and somebody else's
+// token) is left out of the plan (inverse = -1) instead of rejecting the request; the other rules still apply to every
+// route. `slots` is the layer's expert table, [own_lo, own_hi) the tokens of the pass this rank owns.
+struct PlanScope {
+    const int16_t* slots;
+    uint32_t own_lo, own_hi;
+    int skip_foreign;
+};
 __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
-                                                    uint32_t rows, const uint8_t* __restrict__ resident, int max_n,
-                                                    int mt_fc1, int mt_fc2, int m_step, int skip_foreign, PlanOut o) {
+                                                    uint32_t rows, PlanScope sc, int max_n,
+                                                    int mt_fc1, int mt_fc2, int m_step, PlanOut o) {
+    const int skip_foreign = sc.skip_foreign;
+    const int16_t* __restrict__ slots = sc.slots;
     mt_fc1 /= m_step;
     mt_fc2 /= m_step;
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
@@ -243,7 +251,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
             ok = e >= 0 && e < kExperts && wt >= 0.0f && wt <= 3.402823466e+38f;
             if (ok)
                 for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
-            const bool here = ok && resident[e];
+            const bool here = ok && slot_serves(sc.slots[e], r / kTopK, sc.own_lo, sc.own_hi);
             if (skip_foreign ? !ok : !here) my_bad = 1;
             ok = here;
         }
@@ -291,7 +299,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
         const uint32_t r = r0 + lane;
         const bool in = r < hi;
         int32_t e = in ? ids[r] : -1;
-        const bool live = in && (!skip_foreign || resident[e]);
+        const bool live = in && (!skip_foreign || slot_serves(sc.slots[e], r / kTopK, sc.own_lo, sc.own_hi));
         if (!live) e = -1 - int32_t(lane);
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
@@ -314,7 +322,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
         if (lane == 0) o.experts[e] = ExpertPlan{int32_t(ce), int32_t(rbase[e]), int32_t(tstart[e]), int32_t(wd)};
         for (uint32_t j = lane; j < ne; j += 32) {
             const uint32_t nv = ce - j * wd < wd ? ce - j * wd : wd;
-            o.tiles[tstart[e] + j] = TokenTile{int32_t(e), int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
+            o.tiles[tstart[e] + j] = TokenTile{int32_t(slots[e]) & kSlotMask, int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
         for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
             o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
@@ -330,9 +338,9 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
 // routes: global offset of its (CTA, expert) pair + the per-warp offset inside
 // the CTA + the rank inside the 32-route group. Stable by construction.
 __device__ __forceinline__ void plan_warp_counts(const int32_t* __restrict__ ids, const float* __restrict__ w,
-                                                 const uint8_t* __restrict__ resident, uint32_t lo, uint32_t hi,
-                                                 uint32_t lane, uint32_t* __restrict__ wrow, bool validate, uint32_t& bad,
-                                                 int skip_foreign) {
+                                                 const PlanScope& sc, uint32_t lo, uint32_t hi,
+                                                 uint32_t lane, uint32_t* __restrict__ wrow, bool validate, uint32_t& bad) {
+    const int skip_foreign = sc.skip_foreign;
     for (uint32_t r0 = lo; r0 < hi; r0 += 32) {
         const uint32_t r = r0 + lane;
         const bool live = r < hi;
@@ -346,11 +354,11 @@ __device__ __forceinline__ void plan_warp_counts(const int32_t* __restrict__ ids
                 ok = e >= 0 && e < kExperts && wt >= 0.0f && wt <= 3.402823466e+38f;
                 if (ok)
                     for (uint32_t k = (r / kTopK) * kTopK; k < r; ++k) ok = ok && ids[k] != e;
-                const bool here = ok && resident[e];
+                const bool here = ok && slot_serves(sc.slots[e], r / kTopK, sc.own_lo, sc.own_hi);
                 if (skip_foreign ? !ok : !here) bad = 1;
                 ok = here;
             } else if (skip_foreign) {
-                ok = resident[e] != 0;      // validated by the counting launch
+                ok = slot_serves(sc.slots[e], r / kTopK, sc.own_lo, sc.own_hi);      // validated by the counting launch
             }
         }
         const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : -1 - int32_t(lane));
@@ -359,9 +367,9 @@ __device__ __forceinline__ void plan_warp_counts(const int32_t* __restrict__ ids
     }
 }
 __global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
-                                                          uint32_t rows, const uint8_t* __restrict__ resident,
+                                                          uint32_t rows, PlanScope sc,
                                                           uint32_t cta_routes, uint32_t* __restrict__ cta_cnt,
-                                                          PlanMeta* __restrict__ meta, int skip_foreign) {
+                                                          PlanMeta* __restrict__ meta) {
     __shared__ uint32_t wcnt[32][kExperts];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, routes = rows * kTopK;
     const uint32_t seg = cta_routes / 32u, base = blockIdx.x * cta_routes;
@@ -370,7 +378,7 @@ __global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restr
     for (uint32_t i = tid; i < 32 * kExperts; i += 1024) (&wcnt[0][0])[i] = 0;
     __syncthreads();
     uint32_t bad = 0;
-    plan_warp_counts(ids, w, resident, lo, hi, lane, wcnt[warp], true, bad, skip_foreign);
+    plan_warp_counts(ids, w, sc, lo, hi, lane, wcnt[warp], true, bad);
     if (bad) atomicOr(&meta->fault, uint32_t(kFaultPlan));
     __syncthreads();
     if (tid < kExperts) {
@@ -380,7 +388,8 @@ __global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restr
     }
 }
 __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_t* __restrict__ cta_cnt, int max_n,
-                                                         int mt_fc1, int mt_fc2, int m_step, PlanOut o) {
+                                                         int mt_fc1, int mt_fc2, int m_step, const int16_t* __restrict__ slots,
+                                                         PlanOut o) {
     mt_fc1 /= m_step;
     mt_fc2 /= m_step;
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
@@ -447,7 +456,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_
         if (lane == 0) o.experts[e] = ExpertPlan{int32_t(ce), int32_t(rbase[e]), int32_t(tstart[e]), int32_t(wd)};
         for (uint32_t j = lane; j < ne; j += 32) {
             const uint32_t nv = ce - j * wd < wd ? ce - j * wd : wd;
-            o.tiles[tstart[e] + j] = TokenTile{int32_t(e), int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
+            o.tiles[tstart[e] + j] = TokenTile{int32_t(slots[e]) & kSlotMask, int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
         for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
             o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
@@ -457,8 +466,8 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_
 }
 __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                           uint32_t rows, uint32_t cta_routes,
-                                                          const uint32_t* __restrict__ cta_off, PlanOut o,
-                                                          const uint8_t* __restrict__ resident, int skip_foreign) {
+                                                          const uint32_t* __restrict__ cta_off, PlanOut o, PlanScope sc) {
+    const int skip_foreign = sc.skip_foreign;
     __shared__ uint32_t wcnt[32][kExperts];
     if (o.meta->fault) return;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, routes = rows * kTopK;
@@ -468,7 +477,7 @@ __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restr
     for (uint32_t i = tid; i < 32 * kExperts; i += 1024) (&wcnt[0][0])[i] = 0;
     __syncthreads();
     uint32_t bad = 0;
-    plan_warp_counts(ids, w, resident, lo, hi, lane, wcnt[warp], false, bad, skip_foreign);
+    plan_warp_counts(ids, w, sc, lo, hi, lane, wcnt[warp], false, bad);
     __syncthreads();
     if (tid < kExperts) {   // per-warp exclusive offsets, on top of this CTA's global start for the expert
         uint32_t run = uint32_t(o.experts[tid].rbase) + cta_off[blockIdx.x * kExperts + tid];
@@ -479,7 +488,7 @@ __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restr
         const uint32_t r = r0 + lane;
         const bool in = r < hi;
         int32_t e = in ? ids[r] : -1;
-        const bool live = in && (!skip_foreign || resident[e]);
+        const bool live = in && (!skip_foreign || slot_serves(sc.slots[e], r / kTopK, sc.own_lo, sc.own_hi));
         if (!live) e = -1 - int32_t(lane);
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         const uint32_t rank = __popc(peers & ((1u << lane) - 1u));

@@ -78,7 +78,6 @@ struct GemmArgs {
     // FC2 epilogue
     float* y;                   // [routes][4096] FP32 (BF16 with the route-output option), original route order
     const int32_t* original_routes;
-    int expert_base;            // first expert of the weight image (a layer may hold a contiguous subset of the experts)
     RouteSinks sinks;
 };
 
@@ -203,7 +202,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         cur.wi = WorkItem{wi.x, wi.y};
                         cur.tt = TokenTile{tt.x, tt.y, tt.z, tt.w};
                     }
-                    const int slot = (cur.tt.expert - p.expert_base) * p.m_tiles + cur.wi.m_tile;
+                    const int slot = cur.tt.expert * p.m_tiles + cur.wi.m_tile;
                     const uint8_t* sfa_g = p.sfa + size_t(slot) * p.k_chunks * 2 * kScaleBlockBytes;
                     const uint32_t tx = kPairM * 64 + cur.tt.n_mma * 128 + 3 * kScaleBlockBytes;
                     early = p.k_chunks < STAGES ? p.k_chunks : STAGES;       // every stage is free at the start
@@ -220,8 +219,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const ItemInfo cur = load_item(p, it, n_items);
                 const WorkItem wi = cur.wi;
                 const TokenTile tt = cur.tt;
-                const int w_row = ((tt.expert - p.expert_base) * p.m_tiles + wi.m_tile) * kPairM;
-                const uint8_t* sfa_g = p.sfa + size_t((tt.expert - p.expert_base) * p.m_tiles + wi.m_tile) * p.k_chunks * 2 * kScaleBlockBytes;
+                const int w_row = (tt.expert * p.m_tiles + wi.m_tile) * kPairM;
+                const uint8_t* sfa_g = p.sfa + size_t(tt.expert * p.m_tiles + wi.m_tile) * p.k_chunks * 2 * kScaleBlockBytes;
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
                 const uint32_t tx = kPairM * 64 + tt.n_mma * 128 + 3 * kScaleBlockBytes;
                 for (int c = 0; c < p.k_chunks; ++c) {

@@ -104,8 +104,8 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const WorkItem wi = cur.wi;
                 const TokenTile tt = cur.tt;
                 const int m_tile = wi.m_tile + int(rank);
-                const int w_row = ((tt.expert - p.expert_base) * p.m_tiles + m_tile) * kPairM;
-                const int sfa_row = ((tt.expert - p.expert_base) * p.m_tiles + m_tile) * p.k_chunks * 2;
+                const int w_row = (tt.expert * p.m_tiles + m_tile) * kPairM;
+                const int sfa_row = (tt.expert * p.m_tiles + m_tile) * p.k_chunks * 2;
                 const int sfb_row = wi.tile * p.k_chunks;
                 const int half = tt.n_mma >> 1;                   // token rows this CTA holds
                 const int tok_row = tt.row_base + int(rank) * half;

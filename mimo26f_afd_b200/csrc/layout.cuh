@@ -41,9 +41,22 @@ __host__ __device__ constexpr int scale_block_offset(int row, int kb) {
     return (row % 32) * 16 + (row / 32) * 4 + kb;
 }
 
+// Per-layer expert table (256 x int16): which slot of the layer's weight image holds expert e, or kSlotNone. An
+// expert-parallel rank may hold, besides its own block of the experts, copies of experts every rank holds
+// ("replicated", flag kSlotReplicated): a route to such an expert is served by the rank that owns the route's token, so
+// the rows of a popular expert spread over the ranks like the tokens do and never cross NVLink.
+constexpr int kSlotNone = -1;
+constexpr int kSlotReplicated = 0x4000;
+constexpr int kSlotMask = 0x3fff;
+// Does this rank serve a route of `token` (index inside the pass) to the expert with table entry `slot`?
+// [own_lo, own_hi) = the tokens of the pass this rank owns.
+__host__ __device__ inline bool slot_serves(int slot, uint32_t token, uint32_t own_lo, uint32_t own_hi) {
+    return slot >= 0 && (!(slot & kSlotReplicated) || (token >= own_lo && token < own_hi));
+}
+
 // A run of routed rows of one expert that one MMA tile covers.
 struct TokenTile {
-    int32_t expert;
+    int32_t expert;     // the expert's slot in the layer's weight image
     int32_t row_base;   // first grouped (expert-sorted) route of the tile
     int32_t n_valid;    // routed rows in the tile
     int32_t n_mma;      // n_valid rounded up to a multiple of 16 (the MMA N)

@@ -177,10 +177,12 @@ static_assert(sizeof(Status) == 64, "status block is 64 bytes");
 }  // namespace
 
 struct m26b_layer {
-    uint8_t *w13 = nullptr, *s13 = nullptr, *w2 = nullptr, *s2 = nullptr, *resident = nullptr;
+    uint8_t *w13 = nullptr, *s13 = nullptr, *w2 = nullptr, *s2 = nullptr;
+    int16_t* slots = nullptr;                   // device, [256]: slot of each expert in the weight image (layout.cuh)
     int i_local = 0;
     uint32_t tp_rank = 0, tp_size = 1;
-    int expert_lo = 0, n_local = kExperts;      // the experts this layer holds: [expert_lo, expert_lo + n_local)
+    int expert_lo = 0, n_local = kExperts;      // the rank's own experts: [expert_lo, expert_lo + n_local), slots 0 .. n_local - 1
+    int n_rep = 0;                              // replicated experts held besides them, slots n_local .. n_local + n_rep - 1
     bool all_normal = false;
     int device = 0;
     CUtensorMap map_w13, map_w2, map_s13, map_s2;
@@ -238,8 +240,16 @@ struct m26b_scratch {
 
 namespace {
 
-int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, uint32_t tp_rank, uint32_t tp_size,
-                  m26b_layer** out, char* err, size_t errlen, int expert_lo = 0, int n_local = kExperts) {
+// Sources of a set of experts stacked in one group of six tensors.
+struct ExpertSet {
+    ProjSrc gate, up, down;
+    int n;                    // experts in the set
+};
+
+// Repack `home` (the rank's own experts, ids expert_lo ..) and, for an expert-parallel rank, `rep` (copies of experts every
+// rank holds, ids rep_ids[]) into one operand image: home in slots 0 .. n - 1, replicas behind them.
+int prepare_layer(const ExpertSet& home, const ExpertSet* rep, const int32_t* rep_ids, uint32_t tp_rank, uint32_t tp_size,
+                  m26b_layer** out, char* err, size_t errlen, int expert_lo = 0) {
     const int i_local = kInter / int(tp_size);
     // The repack kernels below run on the default stream and take no stream argument: whatever produced the source
     // tensors, on any stream of this device, is waited for here (this runs once per layer, off the serving path).
@@ -247,14 +257,26 @@ int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, u
         const cudaError_t se = cudaDeviceSynchronize();
         if (se != cudaSuccess) { set_err(err, errlen, "m26b layer: waiting for the source tensors", se); return 2; }
     }
+    const int n_local = home.n, n_rep = rep ? rep->n : 0, n_slots = n_local + n_rep;
+    int16_t table[kExperts];
+    for (int e = 0; e < kExperts; ++e) table[e] = int16_t(kSlotNone);
+    for (int i = 0; i < n_local; ++i) table[expert_lo + i] = int16_t(i);
+    for (int i = 0; i < n_rep; ++i) {
+        const int32_t e = rep_ids[i];
+        if (e < 0 || e >= kExperts || (table[e] != kSlotNone && (table[e] & kSlotReplicated))) {
+            set_msg(err, errlen, "m26b layer: bad or repeated replicated expert id");
+            return 1;
+        }
+        // an expert of the rank's own block that is also replicated keeps one copy: the replica's slot
+        table[e] = int16_t((n_local + i) | kSlotReplicated);
+    }
     auto* L = new m26b_layer();
     L->i_local = i_local; L->tp_rank = tp_rank; L->tp_size = tp_size;
-    L->expert_lo = expert_lo; L->n_local = n_local;
+    L->expert_lo = expert_lo; L->n_local = n_local; L->n_rep = n_rep;
     cudaGetDevice(&L->device);
-    const size_t w13_bytes = size_t(n_local) * 2 * i_local * (kHidden / 2);
-    const size_t s13_bytes = size_t(n_local) * 2 * i_local * (kHidden / kBlockK);
-    const size_t w2_bytes = size_t(n_local) * kHidden * (i_local / 2);
-    const size_t s2_bytes = size_t(n_local) * kHidden * (i_local / kBlockK);
+    const size_t w13_e = size_t(2) * i_local * (kHidden / 2), s13_e = size_t(2) * i_local * (kHidden / kBlockK);
+    const size_t w2_e = size_t(kHidden) * (i_local / 2), s2_e = size_t(kHidden) * (i_local / kBlockK);
+    const size_t w13_bytes = n_slots * w13_e, s13_bytes = n_slots * s13_e, w2_bytes = n_slots * w2_e, s2_bytes = n_slots * s2_e;
     cudaError_t e;
     uint32_t* flag = nullptr;
     auto fail = [&](const char* what, cudaError_t ce, int rc) {
@@ -265,23 +287,28 @@ int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, u
     };
     if ((e = cudaMalloc(&L->w13, w13_bytes)) != cudaSuccess || (e = cudaMalloc(&L->s13, s13_bytes)) != cudaSuccess ||
         (e = cudaMalloc(&L->w2, w2_bytes)) != cudaSuccess || (e = cudaMalloc(&L->s2, s2_bytes)) != cudaSuccess ||
-        (e = cudaMalloc(&L->resident, kExperts)) != cudaSuccess || (e = cudaMalloc(&flag, 4)) != cudaSuccess)
+        (e = cudaMalloc(&L->slots, sizeof table)) != cudaSuccess || (e = cudaMalloc(&flag, 4)) != cudaSuccess)
         return fail("m26b layer alloc", e, 2);
-    if ((e = cudaMemset(flag, 0, 4)) != cudaSuccess || (e = cudaMemset(L->resident, 0, kExperts)) != cudaSuccess ||
-        (e = cudaMemset(L->resident + expert_lo, 1, size_t(n_local))) != cudaSuccess)
+    if ((e = cudaMemset(flag, 0, 4)) != cudaSuccess || (e = cudaMemcpy(L->slots, table, sizeof table, cudaMemcpyHostToDevice)) != cudaSuccess)
         return fail("m26b layer metadata", e, 2);
-    prep_w13_kernel<<<2048, 256>>>(gate, up, i_local, L->w13, n_local);
-    prep_s13_kernel<<<2048, 256>>>(gate, up, i_local, L->s13, flag, n_local);
-    prep_w2_kernel<<<2048, 256>>>(down, i_local, L->w2, n_local);
-    prep_s2_kernel<<<2048, 256>>>(down, i_local, L->s2, flag, n_local);
+    const ExpertSet* sets[2] = {&home, rep};
+    for (int k = 0; k < 2; ++k) {
+        if (!sets[k] || sets[k]->n == 0) continue;
+        const ExpertSet& src = *sets[k];
+        const size_t first = k == 0 ? 0 : size_t(n_local);
+        prep_w13_kernel<<<2048, 256>>>(src.gate, src.up, i_local, L->w13 + first * w13_e, src.n);
+        prep_s13_kernel<<<2048, 256>>>(src.gate, src.up, i_local, L->s13 + first * s13_e, flag, src.n);
+        prep_w2_kernel<<<2048, 256>>>(src.down, i_local, L->w2 + first * w2_e, src.n);
+        prep_s2_kernel<<<2048, 256>>>(src.down, i_local, L->s2 + first * s2_e, flag, src.n);
+    }
     uint32_t h = 1;
     if ((e = cudaGetLastError()) != cudaSuccess || (e = cudaMemcpy(&h, flag, 4, cudaMemcpyDeviceToHost)) != cudaSuccess ||
         (e = cudaDeviceSynchronize()) != cudaSuccess)
         return fail("m26b layer prepare", e, 2);
     cudaFree(flag); flag = nullptr;
     L->all_normal = h == 0;
-    if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(n_local) * 2 * i_local, kHidden / 2, kPairM) ||
-        !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(n_local) * kHidden, uint64_t(i_local) / 2, kPairM)) {
+    if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(n_slots) * 2 * i_local, kHidden / 2, kPairM) ||
+        !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(n_slots) * kHidden, uint64_t(i_local) / 2, kPairM)) {
         set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight operands");
         m26b_layer_free(L);
         return 2;
@@ -294,6 +321,24 @@ int prepare_layer(const ProjSrc& gate, const ProjSrc& up, const ProjSrc& down, u
     }
     *out = L;
     return 0;
+}
+
+// The six checkpoint tensors stacked over `n` experts, as repack sources for a tensor-parallel slice.
+ExpertSet checkpoint_set(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w, const uint8_t* up_s, const uint8_t* down_w,
+                         const uint8_t* down_s, uint32_t tp_rank, uint32_t tp_size, int n) {
+    const uint64_t il = kInter / tp_size;
+    ExpertSet s{};
+    s.n = n;
+    s.gate.payload = gate_w; s.gate.scales = gate_s;
+    s.gate.expert_stride_p = uint64_t(kInter) * (kHidden / 2); s.gate.expert_stride_s = uint64_t(kInter) * (kHidden / kBlockK);
+    s.gate.row_stride_p = kHidden / 2; s.gate.row_stride_s = kHidden / kBlockK;
+    s.gate.row0 = il * tp_rank;
+    s.up = s.gate; s.up.payload = up_w; s.up.scales = up_s;
+    s.down.payload = down_w; s.down.scales = down_s;
+    s.down.expert_stride_p = uint64_t(kHidden) * (kInter / 2); s.down.expert_stride_s = uint64_t(kHidden) * (kInter / kBlockK);
+    s.down.row_stride_p = kInter / 2; s.down.row_stride_s = kInter / kBlockK;
+    s.down.col0_p = il * tp_rank / 2; s.down.col0_s = il * tp_rank / kBlockK;
+    return s;
 }
 
 ProjSrc canonical_proj(const uint8_t* base, uint64_t image, uint64_t payload_off, uint64_t scale_off, uint64_t in_cols) {
@@ -388,7 +433,7 @@ struct RawInput {
 
 template <int CODEC, int IN>
 void launch_small_prologue(uint32_t sms, cudaStream_t st, const SmallIo& io, const int32_t* ids, const float* w, uint32_t rows,
-                           const uint8_t* resident, int max_n, int mt1, int mt2, const PlanOut& po) {
+                           const int16_t* resident, int max_n, int mt1, int mt2, const PlanOut& po) {
     const uint32_t routes = rows * kTopK;
     if (rows <= kSmallRows) {
         small_prologue_kernel<CODEC, IN, 256><<<routes < sms ? routes : sms, 256, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
@@ -403,6 +448,7 @@ struct EpPass {
     TokenSources src;
     RouteSinks sinks;
     bool y16;
+    uint32_t own_lo, own_hi;      // the tokens of the pass this rank owns (routes to replicated experts are served by the owner)
 };
 
 // Enqueue one pass: plan -> permute -> FC1 (+SwiGLU, quantiser) -> FC2 -> combine. `raw` names activations still to be
@@ -426,7 +472,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     const int m_step = pair ? 2 : 1;
     const bool kt = (S->debug & 2u) != 0;
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
-    const int skip_foreign = ep ? 1 : 0;
+    const PlanScope scope{L->slots, ep ? ep->own_lo : 0u, ep ? ep->own_hi : rows, ep ? 1 : 0};
     const TokenSources src = ep ? ep->src : TokenSources{};
     if (rows <= kMediumRows && !ep) {
         // one launch: plan + (quantise) + gate + permutation; timed as the permutation, the plan slot reads zero
@@ -439,25 +485,25 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         const uint32_t grid = uint32_t(S->sms);
         const int sel = raw ? raw->codec * 2 + raw->dtype : 4;
         switch (sel) {
-            case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
-            case 1: launch_small_prologue<0, 1>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
-            case 2: launch_small_prologue<1, 0>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
-            case 3: launch_small_prologue<1, 1>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
-            default: launch_small_prologue<0, 2>(grid, st, io, ids, w, rows, L->resident, lc.max_n, mt1, mt2, po); break;
+            case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
+            case 1: launch_small_prologue<0, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
+            case 2: launch_small_prologue<1, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
+            case 3: launch_small_prologue<1, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
+            default: launch_small_prologue<0, 2>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
         }
         M26B_CK(cudaGetLastError(), "m26b prologue launch");
     } else {
         if (routes <= 4096) {
-            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, L->resident, lc.max_n, mt1, mt2, m_step, skip_foreign, po);
+            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, scope, lc.max_n, mt1, mt2, m_step, po);
         } else {
             // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
             const uint32_t slabs = (routes + 1023u) / 1024u;
             const uint32_t n_cta = slabs < 128u ? slabs : 128u;
             const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
             uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
-            plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, L->resident, cta_routes, cta_cnt, &status->meta, skip_foreign);
-            plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step, po);
-            plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po, L->resident, skip_foreign);
+            plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, scope, cta_routes, cta_cnt, &status->meta);
+            plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step, L->slots, po);
+            plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po, scope);
         }
         M26B_CK(cudaGetLastError(), "m26b plan launch");
         if (kt) M26B_CK(cudaEventRecord(S->kev[2], st), "m26b event");
@@ -492,7 +538,6 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     a.mid_f32 = dump ? S->mid_f32.as<float>() : nullptr;
     a.y = S->y.as<float>();
     a.original_routes = S->original.as<int32_t>();
-    a.expert_base = L->expert_lo;
     if (ep) a.sinks = ep->sinks;
     // FC1: weights w13 (K = hidden), tokens x_perm
     a.items = S->items1.as<WorkItem>(); a.n_items = &status->meta.n_items_fc1;
@@ -643,10 +688,12 @@ int m26b_layer_new_tp(const uint8_t* canonical_dev, uint64_t canonical_bytes, ui
         set_msg(err, errlen, "m26b layer: bad canonical extent/rank");
         return 1;
     }
-    const ProjSrc gate = canonical_proj(canonical_dev, image, 0, gp, kHidden);
-    const ProjSrc up = canonical_proj(canonical_dev, image, gp + gs, gp + gs + gp, kHidden);
-    const ProjSrc down = canonical_proj(canonical_dev, image, 2 * (gp + gs), 2 * (gp + gs) + dp, il);
-    return prepare_layer(gate, up, down, tp_rank, tp_size, out, err, errlen);
+    ExpertSet home{};
+    home.n = kExperts;
+    home.gate = canonical_proj(canonical_dev, image, 0, gp, kHidden);
+    home.up = canonical_proj(canonical_dev, image, gp + gs, gp + gs + gp, kHidden);
+    home.down = canonical_proj(canonical_dev, image, 2 * (gp + gs), 2 * (gp + gs) + dp, il);
+    return prepare_layer(home, nullptr, nullptr, tp_rank, tp_size, out, err, errlen);
 }
 
 int m26b_layer_new(const uint8_t* canonical_dev, uint64_t canonical_bytes, uint32_t rank, m26b_layer** out, char* err,
@@ -662,18 +709,8 @@ int m26b_layer_new_from_checkpoint(const uint8_t* gate_w, const uint8_t* gate_s,
         set_msg(err, errlen, "m26b layer: bad checkpoint tensors/rank");
         return 1;
     }
-    const uint64_t il = kInter / tp_size;
-    ProjSrc gate{}, up{}, down{};
-    gate.payload = gate_w; gate.scales = gate_s;
-    gate.expert_stride_p = uint64_t(kInter) * (kHidden / 2); gate.expert_stride_s = uint64_t(kInter) * (kHidden / kBlockK);
-    gate.row_stride_p = kHidden / 2; gate.row_stride_s = kHidden / kBlockK;
-    gate.row0 = il * tp_rank;
-    up = gate; up.payload = up_w; up.scales = up_s;
-    down.payload = down_w; down.scales = down_s;
-    down.expert_stride_p = uint64_t(kHidden) * (kInter / 2); down.expert_stride_s = uint64_t(kHidden) * (kInter / kBlockK);
-    down.row_stride_p = kInter / 2; down.row_stride_s = kInter / kBlockK;
-    down.col0_p = il * tp_rank / 2; down.col0_s = il * tp_rank / kBlockK;
-    return prepare_layer(gate, up, down, tp_rank, tp_size, out, err, errlen);
+    return prepare_layer(checkpoint_set(gate_w, gate_s, up_w, up_s, down_w, down_s, tp_rank, tp_size, kExperts), nullptr, nullptr, tp_rank,
+                         tp_size, out, err, errlen);
 }
 
 int m26b_layer_new_from_checkpoint_ep(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w,
@@ -684,21 +721,32 @@ int m26b_layer_new_from_checkpoint_ep(const uint8_t* gate_w, const uint8_t* gate
         set_msg(err, errlen, "m26b layer: bad checkpoint tensors/rank");
         return 1;
     }
-    ProjSrc gate{}, up{}, down{};
-    gate.payload = gate_w; gate.scales = gate_s;
-    gate.expert_stride_p = uint64_t(kInter) * (kHidden / 2); gate.expert_stride_s = uint64_t(kInter) * (kHidden / kBlockK);
-    gate.row_stride_p = kHidden / 2; gate.row_stride_s = kHidden / kBlockK;
-    up = gate; up.payload = up_w; up.scales = up_s;
-    down.payload = down_w; down.scales = down_s;
-    down.expert_stride_p = uint64_t(kHidden) * (kInter / 2); down.expert_stride_s = uint64_t(kHidden) * (kInter / kBlockK);
-    down.row_stride_p = kInter / 2; down.row_stride_s = kInter / kBlockK;
     const int n_local = kExperts / int(ep_size);
-    return prepare_layer(gate, up, down, 0, 1, out, err, errlen, int(ep_rank) * n_local, n_local);
+    return prepare_layer(checkpoint_set(gate_w, gate_s, up_w, up_s, down_w, down_s, 0, 1, n_local), nullptr, nullptr, 0, 1, out, err,
+                         errlen, int(ep_rank) * n_local);
+}
+
+int m26b_layer_new_from_checkpoint_ep_replicated(const uint8_t* gate_w, const uint8_t* gate_s, const uint8_t* up_w,
+                                                 const uint8_t* up_s, const uint8_t* down_w, const uint8_t* down_s,
+                                                 const uint8_t* rep_gate_w, const uint8_t* rep_gate_s, const uint8_t* rep_up_w,
+                                                 const uint8_t* rep_up_s, const uint8_t* rep_down_w, const uint8_t* rep_down_s,
+                                                 const int32_t* rep_ids, uint32_t n_rep, uint32_t ep_rank, uint32_t ep_size,
+                                                 m26b_layer** out, char* err, size_t errlen) {
+    if (!out || !gate_w || !gate_s || !up_w || !up_s || !down_w || !down_s ||
+        !(ep_size == 1 || ep_size == 2 || ep_size == 4 || ep_size == 8) || ep_rank >= ep_size || n_rep > uint32_t(kExperts) ||
+        (n_rep && (!rep_gate_w || !rep_gate_s || !rep_up_w || !rep_up_s || !rep_down_w || !rep_down_s || !rep_ids))) {
+        set_msg(err, errlen, "m26b layer: bad checkpoint tensors/rank");
+        return 1;
+    }
+    const int n_local = kExperts / int(ep_size);
+    const ExpertSet home = checkpoint_set(gate_w, gate_s, up_w, up_s, down_w, down_s, 0, 1, n_local);
+    const ExpertSet rep = checkpoint_set(rep_gate_w, rep_gate_s, rep_up_w, rep_up_s, rep_down_w, rep_down_s, 0, 1, int(n_rep));
+    return prepare_layer(home, n_rep ? &rep : nullptr, rep_ids, 0, 1, out, err, errlen, int(ep_rank) * n_local);
 }
 
 const void* m26b_layer_image(const m26b_layer* L, int which, uint64_t* bytes) {
     if (!L || which < 0 || which > 3) return nullptr;
-    const uint64_t n = uint64_t(L->n_local), il = uint64_t(L->i_local);
+    const uint64_t n = uint64_t(L->n_local + L->n_rep), il = uint64_t(L->i_local);
     const uint64_t size[4] = {n * 2 * il * (kHidden / 2), n * 2 * il * (kHidden / kBlockK), n * kHidden * (il / 2), n * kHidden * (il / kBlockK)};
     const uint8_t* base[4] = {L->w13, L->s13, L->w2, L->s2};
     if (bytes) *bytes = size[which];
@@ -710,7 +758,7 @@ int m26b_layer_i_local(const m26b_layer* L) { return L ? L->i_local : 0; }
 
 void m26b_layer_free(m26b_layer* L) {
     if (!L) return;
-    cudaFree(L->w13); cudaFree(L->s13); cudaFree(L->w2); cudaFree(L->s2); cudaFree(L->resident);
+    cudaFree(L->w13); cudaFree(L->s13); cudaFree(L->w2); cudaFree(L->s2); cudaFree(L->slots);
     delete L;
 }
 
@@ -1273,8 +1321,14 @@ int m26b_ep_compute_dev(m26b_ep* E, const m26b_layer* L, m26b_scratch* S, void* 
     M26B_CK(cudaGetLastError(), "m26b ep gather launch");
     for (uint32_t ps = 0; ps < passes; ++ps) {
         const uint32_t r0 = ps * kMaxPassRows, n = E->tokens - r0 < kMaxPassRows ? E->tokens - r0 : kMaxPassRows;
-        EpPass pass{shards, sinks, E->y16};
+        EpPass pass{shards, sinks, E->y16, 0u, 0u};
         pass.src.token_base = r0; pass.sinks.token_base = r0;
+        {   // this rank's tokens inside the pass
+            const uint32_t lo = E->lo[E->rank], hi = E->lo[E->rank + 1];
+            const uint32_t a0 = lo > r0 ? lo - r0 : 0u, a1 = hi > r0 ? hi - r0 : 0u;
+            pass.own_lo = a0 < n ? a0 : n;
+            pass.own_hi = a1 < n ? a1 : n;
+        }
         rc = enqueue_pass(L, S, nullptr, nullptr, E->ids.as<int32_t>() + size_t(r0) * kTopK, E->w.as<float>() + size_t(r0) * kTopK, n,
                           nullptr, nullptr, S->status.as<Status>() + ps, st, false, err, errlen, nullptr, false, &pass);
         if (rc) return rc;
@@ -1634,7 +1688,7 @@ int m26b_scratch_timings(m26b_scratch* S, float* ms6, char* err, size_t errlen) 
 
 // ---- allocation-free route planner ---------------------------------------------------------
 // Scratch of m26b_plan_static: per-CTA expert counts, the expert table, token tiles and work
-// items of the plan, and an all-resident table. It lives in the library's data segment on every
+// items of the plan, and an identity slot table (every expert held). It lives in the library's data segment on every
 // GPU that loads the library (about 0.47 MB) instead of coming from cudaMalloc.
 namespace {
 constexpr uint32_t kStaticPlanMaxRows = 4096;
@@ -1645,10 +1699,11 @@ struct StaticPlanScratch {
     TokenTile tiles[kStaticPlanTiles];
     WorkItem items_fc1[kStaticPlanTiles * (kInter / kTileM)];
     WorkItem items_fc2[kStaticPlanTiles * (kHidden / kPairM)];
-    uint8_t resident[kExperts];
+    int16_t slots[kExperts];
 };
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_plan_scratch[sizeof(StaticPlanScratch)];
+static __global__ void identity_slots_kernel(int16_t* slots) { slots[threadIdx.x] = int16_t(threadIdx.x); }
 
 int m26b_plan_static(const int32_t* ids, const float* weights, uint32_t rows, int32_t* inverse, int32_t* original_routes,
                      float* grouped_weights, uint32_t* meta_out, void* stream, char* err, size_t errlen) {
@@ -1680,16 +1735,17 @@ int m26b_plan_static(const int32_t* ids, const float* weights, uint32_t rows, in
     // the array keeps the previous call's contents: the fault word and the residency table are rewritten
     // here, every other field is overwritten by the kernels before it is read
     M26B_CK(cudaMemsetAsync(meta, 0, sizeof(PlanMeta), st), "m26b plan_static clear");
-    M26B_CK(cudaMemsetAsync(sc->resident, 1, kExperts, st), "m26b plan_static residency");
+    identity_slots_kernel<<<1, kExperts, 0, st>>>(sc->slots);      // every expert counts as held: slot e for expert e
     const uint32_t routes = rows * kTopK;
     const LaunchClass lc = launch_class(rows);
     const uint32_t slabs = (routes + 1023u) / 1024u;
     const uint32_t n_cta = slabs < 128u ? slabs : 128u;
     const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
     PlanOut po{inverse, original_routes, grouped_weights, sc->experts, sc->tiles, sc->items_fc1, sc->items_fc2, meta};
-    plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, sc->resident, cta_routes, sc->cta_cnt, meta, 0);
-    plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, 1, po);
-    plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, cta_routes, sc->cta_cnt, po, sc->resident, 0);
+    const PlanScope scope{sc->slots, 0u, rows, 0};
+    plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, scope, cta_routes, sc->cta_cnt, meta);
+    plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, 1, sc->slots, po);
+    plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, cta_routes, sc->cta_cnt, po, scope);
     M26B_CK(cudaGetLastError(), "m26b plan_static launch");
     return 0;
 }

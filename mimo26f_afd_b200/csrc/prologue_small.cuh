@@ -31,7 +31,7 @@ struct SmallIo {
 template <int CODEC, int IN, int THREADS>
 __global__ void __launch_bounds__(THREADS) small_prologue_kernel(SmallIo io, const int32_t* __restrict__ ids,
                                                              const float* __restrict__ w, uint32_t rows,
-                                                             const uint8_t* __restrict__ resident, int max_n, int mt_fc1,
+                                                             const int16_t* __restrict__ slots, int max_n, int mt_fc1,
                                                              int mt_fc2, PlanOut o) {
     constexpr int kWarps = THREADS / 32;
     constexpr uint32_t kRowsAtOnce = THREADS / 256;      // grouped rows a CTA produces side by side
@@ -54,7 +54,8 @@ __global__ void __launch_bounds__(THREADS) small_prologue_kernel(SmallIo io, con
     if (live) {
         e = ids[tid];
         wt = w[tid];
-        ok = e >= 0 && e < kExperts && resident[e] && wt >= 0.0f && wt <= 3.402823466e+38f;
+        ok = e >= 0 && e < kExperts && wt >= 0.0f && wt <= 3.402823466e+38f;
+        ok = ok && slots[e] >= 0;
         if (ok)
             for (uint32_t k = (tid / kTopK) * kTopK; k < tid; ++k) ok = ok && ids[k] != e;
     }
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(THREADS) small_prologue_kernel(SmallIo io, con
         o.experts[tid] = ExpertPlan{int32_t(c), int32_t(rbase[tid]), int32_t(tstart[tid]), int32_t(width[tid])};
         for (uint32_t j = 0; j < n; ++j) {
             const uint32_t wd = width[tid], nv = c - j * wd < wd ? c - j * wd : wd;
-            o.tiles[tstart[tid] + j] = TokenTile{int32_t(tid), int32_t(rbase[tid] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
+            o.tiles[tstart[tid] + j] = TokenTile{int32_t(slots[tid]) & kSlotMask, int32_t(rbase[tid] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
     }
     if (is_expert && blockIdx.x == 2u % gridDim.x)

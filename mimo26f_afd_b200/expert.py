@@ -82,9 +82,18 @@ class Layer:
         return cls(out.value)
 
     @classmethod
-    def from_checkpoint_ep(cls, gate_w, gate_s, up_w, up_s, down_w, down_s, ep_rank: int, ep_size: int) -> "Layer":
-        """Expert-parallel rank: the six tensors stacked over this rank's 256 / ep_size experts only."""
+    def from_checkpoint_ep(cls, gate_w, gate_s, up_w, up_s, down_w, down_s, ep_rank: int, ep_size: int, replicas=None,
+                           replica_ids=None) -> "Layer":
+        """Expert-parallel rank: the six tensors stacked over this rank's 256 / ep_size experts only. ``replicas`` (the six
+        tensors stacked over the experts ``replica_ids``, the same set on every rank) adds copies of popular experts: a
+        route to one of them is served where its token lives."""
         out, err = C.c_void_p(), C.create_string_buffer(256)
+        if replica_ids is not None and len(replica_ids):
+            rid = np.ascontiguousarray(replica_ids, dtype=np.int32)
+            _check(_native.lib().m26b_layer_new_from_checkpoint_ep_replicated(
+                _ptr(gate_w), _ptr(gate_s), _ptr(up_w), _ptr(up_s), _ptr(down_w), _ptr(down_s), *[_ptr(t) for t in replicas],
+                rid.ctypes.data, rid.size, ep_rank, ep_size, C.byref(out), err, 256), err)
+            return cls(out.value)
         _check(_native.lib().m26b_layer_new_from_checkpoint_ep(
             _ptr(gate_w), _ptr(gate_s), _ptr(up_w), _ptr(up_s), _ptr(down_w), _ptr(down_s), ep_rank, ep_size,
             C.byref(out), err, 256), err)

@@ -75,12 +75,15 @@ def layer_np(seed: int, experts, scale_lo: int = 118, scale_hi: int = 122) -> di
     return out
 
 
-def layer_torch(seed: int, device, scale_lo: int = 118, scale_hi: int = 122, n_experts: int = E, first_expert: int = 0) -> dict:
-    """Experts ``first_expert .. first_expert + n_experts - 1`` (default all 256) generated on ``device`` with torch
-    integer ops; bit-identical to ``expert_tensor_np``. torch is the device allocator here, not a compute path."""
+def layer_torch(seed: int, device, scale_lo: int = 118, scale_hi: int = 122, n_experts: int = E, first_expert: int = 0,
+                experts=None) -> dict:
+    """Experts ``first_expert .. first_expert + n_experts - 1`` (default all 256), or the experts listed in ``experts`` in
+    that order, generated on ``device`` with torch integer ops; bit-identical to ``expert_tensor_np``. torch is the
+    device allocator here, not a compute path."""
     import torch
 
-    E = n_experts  # noqa: N806 (shadows the module constant inside this function only)
+    ids = [first_expert + e for e in range(n_experts)] if experts is None else [int(e) for e in experts]
+    E = len(ids)  # noqa: N806 (shadows the module constant inside this function only)
 
     def s64(v: int) -> int:
         return v - (1 << 64) if v >= (1 << 63) else v
@@ -92,7 +95,7 @@ def layer_torch(seed: int, device, scale_lo: int = 118, scale_hi: int = 122, n_e
     for ti, name in enumerate(TENSORS):
         shape = SHAPES[name]
         n_words = shape[0] * shape[1] // 8
-        bases = torch.tensor([s64(stream_base(seed, ti, first_expert + e)) for e in range(E)], dtype=torch.int64, device=device)
+        bases = torch.tensor([s64(stream_base(seed, ti, e)) for e in ids], dtype=torch.int64, device=device)
         res = torch.empty((E, n_words), dtype=torch.int64, device=device)
         idx = torch.arange(1, n_words + 1, dtype=torch.int64, device=device) * s64(GOLDEN)
         for e0 in range(0, E, 32):  # bound the temporaries

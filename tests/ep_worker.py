@@ -32,7 +32,19 @@ def main():
     scratch, scratch_full = M.Scratch(), M.Scratch()
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
-    for tokens, zipf in ((16, 0.0), (1000, 1.0), (20000, 0.0)):
+    plain = mine
+    for tokens, zipf, n_rep in ((16, 0.0, 0), (1000, 1.0, 0), (20000, 0.0, 0), (3000, 1.0, 16)):
+        if n_rep:
+            # copies of the batch's busiest experts on every rank: their routes are served where the tokens live
+            all_ids, _ = synth.routing(seed, tokens, zipf)
+            hot = np.argsort(-np.bincount(all_ids.reshape(-1), minlength=256), kind="stable")[:n_rep].astype(np.int32)
+            w = synth.layer_torch(seed, dev, n_experts=n_local, first_expert=rank * n_local)
+            reps = synth.layer_torch(seed, dev, experts=hot)
+            mine = M.Layer.from_checkpoint_ep(*[w[n] for n in synth.TENSORS], ep_rank=rank, ep_size=world,
+                                              replicas=[reps[n] for n in synth.TENSORS], replica_ids=hot)
+            del w, reps
+        else:
+            mine = plain
         ep = tp.make_expert_parallel(tokens)
         lo, hi = tp.shard_tokens(tokens, rank, world)
         x_bits = synth.activations_bf16(seed, tokens)

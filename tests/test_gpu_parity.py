@@ -334,11 +334,13 @@ def test_plane_exchange_two_windows_one_process(dev, oracle_mod):
         e_.close()
 
 
-@pytest.mark.parametrize("tokens,zipf", [(9, 0.0), (96, 1.2), (300, 0.0)])
-def test_expert_parallel_two_ranks_one_process_equals_single_gpu(layer, scratch, dev, tokens, zipf):
+@pytest.mark.parametrize("tokens,zipf,n_rep", [(9, 0.0, 0), (96, 1.2, 0), (300, 0.0, 0), (96, 1.2, 6), (700, 1.0, 12)])
+def test_expert_parallel_two_ranks_one_process_equals_single_gpu(layer, scratch, dev, tokens, zipf, n_rep):
     """Expert parallelism with both ranks in this process (each rank's rendezvous is marked reached from the host, so no
     kernel waits for another kernel): experts split 128 / 128, tokens split in two blocks, rows gathered from and
-    results scattered to the owner's window. Output must equal the single-GPU layer's bit for bit."""
+    results scattered to the owner's window. Output must equal the single-GPU layer's bit for bit. With n_rep > 0 both
+    ranks also hold copies of the batch's n_rep busiest experts (routes to those are served where the token lives), and
+    every route must still be served exactly once."""
     import torch
 
     import mimo26f_afd_b200 as M
@@ -348,9 +350,13 @@ def test_expert_parallel_two_ranks_one_process_equals_single_gpu(layer, scratch,
     ids, w = synth.routing(SEED + 3, tokens, zipf)
     bf_ref, part_ref = run_dev(layer, scratch, dev, x_bits, ids, w)
     layers, eps = [], []
+    counts = np.bincount(ids.reshape(-1), minlength=256)
+    hot = np.argsort(-counts, kind="stable")[:n_rep].astype(np.int32)
+    reps = synth.layer_torch(SEED, dev, experts=hot) if n_rep else None
     for r in range(2):
         wt = synth.layer_torch(SEED, dev, n_experts=128, first_expert=128 * r)
-        layers.append(M.Layer.from_checkpoint_ep(*[wt[n] for n in synth.TENSORS], ep_rank=r, ep_size=2))
+        layers.append(M.Layer.from_checkpoint_ep(*[wt[n] for n in synth.TENSORS], ep_rank=r, ep_size=2,
+                                                 replicas=[reps[n] for n in synth.TENSORS] if n_rep else None, replica_ids=hot))
         del wt
         eps.append(M.ExpertParallel(tokens, r, 2, export=False))
     for e in eps:
@@ -376,6 +382,12 @@ def test_expert_parallel_two_ranks_one_process_equals_single_gpu(layer, scratch,
         for r in range(2):
             assert np.array_equal(outs[r].cpu().numpy().view(np.uint16), bf_ref[lo[r]:lo[r + 1]]), (step, r)
             assert np.array_equal(parts[r].cpu().numpy().view(np.uint32), part_ref[lo[r]:lo[r + 1]].view(np.uint32)), (step, r)
+        if n_rep and step == 0:
+            # the rank that ran last planned only the routes it serves: the replicated experts' routes of its own tokens
+            # plus its own block's routes of all tokens
+            inv = s2.peek("inverse", np.int32, (tokens * TOPK,))
+            mine = np.isin(ids, hot) & (np.arange(tokens)[:, None] >= lo[1]) | (~np.isin(ids, hot) & (ids >= 128))
+            assert np.array_equal(inv >= 0, mine.reshape(-1))
     # a rendezvous nobody else reaches: bounded wait, status 5, window usable afterwards
     eps[0].set_wait_ms(20)
     eps[0].begin(xd[lo[0]:lo[1]], idd[lo[0]:lo[1]], wd[lo[0]:lo[1]], lo[1])
