@@ -858,7 +858,10 @@ def test_config4_65536_tokens_zipf_through_the_host_entry_point(layer, dev, orac
     ids, w = synth.routing(SEED + 4, tokens, 1.0)
     counts = np.bincount(ids.reshape(-1), minlength=256)
     assert counts.max() > 40000 and (counts > 0).all()
-    sample = np.array([0, 1, 16383, 16384, 40000, 65535])
+    # sampled tokens: both sides of every pass boundary (passes of 16,384 tokens), both sides of the other cut below, the
+    # ends, and a seeded scatter; 40 tokens, 320 routes
+    sample = np.unique(np.concatenate([[0, 1, 9999, 10000, 16383, 16384, 32767, 32768, 40000, 49151, 49152, 65534, 65535],
+                                       np.random.default_rng(5).integers(0, tokens, 27)]))
     # quantised rows: seeded bytes directly (valid E4M3 codes, scale bytes 118..125), the host entry point's own input form
     rng = np.random.default_rng(99)
     xq = rng.integers(0, 256, (tokens, H), dtype=np.uint8)
