@@ -479,10 +479,9 @@ def run_ep(ctx, name, layer, scratch, k, y16=False, with_e2e=True, hot=None):
     xd, idd, wd = inp["xd"], inp["idd"], inp["wd"]
     n_local = E // world
     counts = np.bincount(ids.reshape(-1), minlength=E)
-    flat = ids.reshape(-1)
-    owner = np.repeat(np.searchsorted(np.array([tp.shard_tokens(tokens, r, world)[1] for r in range(world)]), np.arange(tokens), side="right"), TOPK)
-    serving = np.where(np.isin(flat, hot), owner, flat // n_local) if hot is not None else flat // n_local
-    per_rank = np.bincount(serving, minlength=world)
+    serving = tp.serving_rank(ids, world, hot)
+    per_rank = np.bincount(serving.reshape(-1), minlength=world)
+    owner = tp.serving_rank(ids, world, np.arange(E))          # with every expert replicated a route stays with its token's owner
     crossing = int((serving != owner).sum())                   # routed rows whose token lives on another rank
     ep = tp.make_expert_parallel(tokens)
     ep.set_route_output(y16)
@@ -546,14 +545,14 @@ def build_ep_layer(ctx, name):
     import torch
 
     import mimo26f_afd_b200 as M
-    from mimo26f_afd_b200 import synth
+    from mimo26f_afd_b200 import synth, tp
 
     wl = WORKLOADS[name]
     n_local = E // ctx.world
     hot = None
     if wl["zipf"]:
         ids, _ = synth.routing(synth.MASTER_SEED, wl["tokens"], wl["zipf"])
-        hot = np.argsort(-np.bincount(ids.reshape(-1), minlength=E), kind="stable")[:REPLICATED_EXPERTS].astype(np.int32)
+        hot = tp.busiest_experts(ids, REPLICATED_EXPERTS)
     wts = synth.layer_torch(synth.MASTER_SEED, ctx.dev, n_experts=n_local, first_expert=ctx.rank * n_local)
     reps = synth.layer_torch(synth.MASTER_SEED, ctx.dev, experts=hot) if hot is not None else None
     layer = M.Layer.from_checkpoint_ep(*[wts[n] for n in synth.TENSORS], ep_rank=ctx.rank, ep_size=ctx.world,

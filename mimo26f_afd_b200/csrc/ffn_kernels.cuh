@@ -207,7 +207,8 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lan
     }
     return v;
 }
-// Work items: for every token tile, weight tile pairs 0, m_step, 2 m_step ... (m_step 2 when a CTA pair takes two
+// Work items: for every token tile, weight tile pairs 0, m_step, 2 m_step ... of each GEMM (m_step1 for FC1, m_step2 for FC2:
+// 2 when a CTA pair takes two
 // neighbouring weight tile pairs per item).
 //
 // skip_foreign (expert parallelism: this GPU holds a subset of the experts and sees every route of the request): a
@@ -221,11 +222,11 @@ struct PlanScope {
 };
 __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,
                                                     uint32_t rows, PlanScope sc, int max_n,
-                                                    int mt_fc1, int mt_fc2, int m_step, PlanOut o) {
+                                                    int mt_fc1, int mt_fc2, int m_step1, int m_step2, PlanOut o) {
     const int skip_foreign = sc.skip_foreign;
     const int16_t* __restrict__ slots = sc.slots;
-    mt_fc1 /= m_step;
-    mt_fc2 /= m_step;
+    mt_fc1 /= m_step1;
+    mt_fc2 /= m_step2;
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
     __shared__ uint32_t i1base[kExperts], i2base[kExperts];
     __shared__ uint32_t wcnt[32][kExperts];
@@ -325,9 +326,9 @@ __global__ void __launch_bounds__(1024) plan_kernel(const int32_t* __restrict__ 
             o.tiles[tstart[e] + j] = TokenTile{int32_t(slots[e]) & kSlotMask, int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
         for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
-            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
+            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step1};
         for (uint32_t i = lane; i < ne * mt_fc2; i += 32)
-            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
+            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step2};
     }
 }
 
@@ -388,10 +389,10 @@ __global__ void __launch_bounds__(1024) plan_count_kernel(const int32_t* __restr
     }
 }
 __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_t* __restrict__ cta_cnt, int max_n,
-                                                         int mt_fc1, int mt_fc2, int m_step, const int16_t* __restrict__ slots,
+                                                         int mt_fc1, int mt_fc2, int m_step1, int m_step2, const int16_t* __restrict__ slots,
                                                          PlanOut o) {
-    mt_fc1 /= m_step;
-    mt_fc2 /= m_step;
+    mt_fc1 /= m_step1;
+    mt_fc2 /= m_step2;
     __shared__ uint32_t cnt[kExperts], rbase[kExperts], tstart[kExperts], width[kExperts], ntl[kExperts];
     __shared__ uint32_t i1base[kExperts], i2base[kExperts];
     __shared__ uint32_t wsum[4][8];
@@ -459,9 +460,9 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t n_cta, uint32_
             o.tiles[tstart[e] + j] = TokenTile{int32_t(slots[e]) & kSlotMask, int32_t(rbase[e] + j * wd), int32_t(nv), int32_t((nv + 15u) & ~15u)};
         }
         for (uint32_t i = lane; i < ne * mt_fc1; i += 32)
-            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
+            o.items_fc1[i1base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step1};
         for (uint32_t i = lane; i < ne * mt_fc2; i += 32)
-            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step};
+            o.items_fc2[i2base[e] + i] = WorkItem{int32_t(tstart[e] + i % ne), int32_t(i / ne) * m_step2};
     }
 }
 __global__ void __launch_bounds__(1024) plan_place_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w,

@@ -68,6 +68,7 @@ struct GemmArgs {
     const uint8_t* sfa;         // weight scale blocks [E][m_tiles][k_chunks][2][512]
     const uint8_t* sfb;         // token scale blocks  [tile][k_chunks][512]
     int m_tiles;                // 256-row weight tile pairs per expert
+    int m_span;                 // weight tile pairs one work item of the single-CTA kernel covers (consecutive, same token tile)
     int k_chunks;               // K / 128
     uint32_t* fault;            // one word, OR of fault codes
     // FC1 epilogue
@@ -146,7 +147,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return __fmul_rn(__fmul_rn(num, r), u);
 }
 
-static_assert(sizeof(GemmSmem<32, 6>) + 1024 <= 232448 && sizeof(GemmSmem<kMaxN, 4>) + 1024 <= 232448,
+static_assert(sizeof(GemmSmem<32, 6>) + 1024 <= 232448 && sizeof(GemmSmem<kMaxN, 4>) + 1024 <= 232448 && sizeof(GemmSmem<64, 5>) + 1024 <= 232448,
               "a CTA has at most 227 KB of shared memory");
 
 // DUMP: also store the FP32 intermediate (stage dumps of the parity tests). Y16: FC2 rows as BF16.
@@ -215,33 +216,36 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 grid_dep_wait();
                 grid_dep_launch();
             }
-                        for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
+            for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
                 const ItemInfo cur = load_item(p, it, n_items);
                 const WorkItem wi = cur.wi;
                 const TokenTile tt = cur.tt;
-                const int w_row = (tt.expert * p.m_tiles + wi.m_tile) * kPairM;
-                const uint8_t* sfa_g = p.sfa + size_t(tt.expert * p.m_tiles + wi.m_tile) * p.k_chunks * 2 * kScaleBlockBytes;
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
                 const uint32_t tx = kPairM * 64 + tt.n_mma * 128 + 3 * kScaleBlockBytes;
-                for (int c = 0; c < p.k_chunks; ++c) {
-                    const bool weights_in_flight = kEarlyWeights && it == blockIdx.x && c < early;
-                    if (!weights_in_flight) {
-                        if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-                        mbar_expect_tx(&s.full[stage], tx);
-                        tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
-                        bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
-                    }
-                    int r = 0;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int rows = 128 >> i;
-                        if (tt.n_mma - r >= rows) {   // n_mma <= 128: each size is needed at most once
-                            tma_load_2d(s.b[stage] + r * 128, &maps_x.box[i], c * kChunkK, tt.row_base + r, &s.full[stage]);
-                            r += rows;
+                for (int mm = 0; mm < p.m_span && ok; ++mm) {
+                    const int slot = tt.expert * p.m_tiles + wi.m_tile + mm;
+                    const int w_row = slot * kPairM;
+                    const uint8_t* sfa_g = p.sfa + size_t(slot) * p.k_chunks * 2 * kScaleBlockBytes;
+                    for (int c = 0; c < p.k_chunks; ++c) {
+                        const bool weights_in_flight = kEarlyWeights && it == blockIdx.x && mm == 0 && c < early;
+                        if (!weights_in_flight) {
+                            if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                            mbar_expect_tx(&s.full[stage], tx);
+                            tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
+                            bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
                         }
+                        int r = 0;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rows = 128 >> i;
+                            if (tt.n_mma - r >= rows) {   // n_mma <= 128: each size is needed at most once
+                                tma_load_2d(s.b[stage] + r * 128, &maps_x.box[i], c * kChunkK, tt.row_base + r, &s.full[stage]);
+                                r += rows;
+                            }
+                        }
+                        bulk_load(s.sfb[stage], sfb_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
-                    bulk_load(s.sfb[stage], sfb_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
@@ -257,10 +261,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint64_t sfa_desc0 = desc_scale_block(smem_u32(s.sfa[0])), sfb_desc0 = desc_scale_block(smem_u32(s.sfb[0]));
             constexpr uint64_t kAStage = sizeof(s.a[0]) >> 4, kBStage = sizeof(s.b[0]) >> 4;
             constexpr uint64_t kSfaStage = sizeof(s.sfa[0]) >> 4, kSfbStage = sizeof(s.sfb[0]) >> 4;
-                        for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
+            for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
                 const ItemInfo cur = load_item(p, it, n_items);
                 const TokenTile tt = cur.tt;
                 const uint32_t idesc0 = idesc_mx(kFmtE2M1, kFmtE4M3, uint32_t(tt.n_mma), 0, 0);
+              for (int mm = 0; mm < p.m_span && ok; ++mm, ++local) {
                 // the accumulators are free once every epilogue warp has pulled its slice of the previous item
                 const uint32_t aset = local % kAccSets, ause = local / kAccSets;
                 if (!mbar_wait(&s.acc_empty[aset], (ause & 1u) ^ 1u, abort_flag)) { ok = false; break; }
@@ -290,6 +295,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit(&s.acc_full[aset]);
+              }
             }
             if (!ok) atomicOr(p.fault, uint32_t(kFaultPipeline));
         }
@@ -300,9 +306,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         static_assert(kEpiWarps == 16 && kMaxN == 128, "the register drain below is sized for 4 warps per quadrant");
         uint32_t local = 0;
         bool ok = true;
-                for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++local) {
+        for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
             const ItemInfo cur = load_item(p, it, n_items);
-            const WorkItem wi = cur.wi;
+            WorkItem wi = cur.wi;
             const TokenTile tt = cur.tt;
             // FC2: where this warp's token columns go. Lane l holds the route of token (wq >> 1) * 8 + 16 (l / 8) + l % 8 as
             // the address of its output row (0 for a padding column), fetched before the accumulators are waited for.
@@ -312,6 +318,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (t < tt.n_valid) row_lo = reinterpret_cast<unsigned long long>(y_row<Y16>(p, p.original_routes[tt.row_base + t]));
                 if (t + 64 < tt.n_valid) row_hi = reinterpret_cast<unsigned long long>(y_row<Y16>(p, p.original_routes[tt.row_base + t + 64]));
             }
+          // the item's weight tile pairs one after the other: same token tile, same output rows
+          for (int mm = 0; mm < p.m_span && ok; ++mm, ++local, ++wi.m_tile) {
             const uint32_t aset = local % kAccSets, ause = local / kAccSets;
             if (!mbar_wait(&s.acc_full[aset], ause & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -383,6 +391,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (fault && lane == 0) atomicOr(p.fault, fault);
             }
+          }
         }
         if (!ok && lane == 0) atomicOr(p.fault, uint32_t(kFaultPipeline));
     }

@@ -157,13 +157,18 @@ constexpr size_t kStageBytes = size_t(kStageRows) * (kHidden + kHidden / kBlockK
 constexpr uint32_t kPairMinRows = 129;
 
 // The single-CTA kernels by launch class; `variant` = the FP32 stage dump for FC1, BF16 route outputs for FC2.
+template <int MODE, int B_ROWS, int STAGES>
+cudaError_t launch_gemm_variant(bool variant, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
+    constexpr bool kFc1 = MODE == kModeFc1;
+    return variant ? launch_gemm<MODE, B_ROWS, STAGES, kFc1, !kFc1>(mw, mx, a, ctas, st) : launch_gemm<MODE, B_ROWS, STAGES, false, false>(mw, mx, a, ctas, st);
+}
 template <int MODE>
 cudaError_t launch_gemm_class(uint32_t rows, bool variant, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas,
                               cudaStream_t st) {
-    constexpr bool kFc1 = MODE == kModeFc1;
-    if (rows <= 32)
-        return variant ? launch_gemm<MODE, 32, 6, kFc1, !kFc1>(mw, mx, a, ctas, st) : launch_gemm<MODE, 32, 6, false, false>(mw, mx, a, ctas, st);
-    return variant ? launch_gemm<MODE, kMaxN, 4, kFc1, !kFc1>(mw, mx, a, ctas, st) : launch_gemm<MODE, kMaxN, 4, false, false>(mw, mx, a, ctas, st);
+    const LaunchClass lc = launch_class(rows);
+    if (lc.b_rows == 32) return launch_gemm_variant<MODE, 32, 6>(variant, mw, mx, a, ctas, st);
+    if (lc.b_rows == 64) return launch_gemm_variant<MODE, 64, 5>(variant, mw, mx, a, ctas, st);
+    return launch_gemm_variant<MODE, kMaxN, 4>(variant, mw, mx, a, ctas, st);
 }
 
 // Device status block of one pass: PlanMeta then four fault words.
@@ -433,13 +438,13 @@ struct RawInput {
 
 template <int CODEC, int IN>
 void launch_small_prologue(uint32_t sms, cudaStream_t st, const SmallIo& io, const int32_t* ids, const float* w, uint32_t rows,
-                           const int16_t* resident, int max_n, int mt1, int mt2, const PlanOut& po) {
+                           const int16_t* resident, int max_n, int mt1, int mt2, int span2, const PlanOut& po) {
     const uint32_t routes = rows * kTopK;
     if (rows <= kSmallRows) {
-        small_prologue_kernel<CODEC, IN, 256><<<routes < sms ? routes : sms, 256, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
+        small_prologue_kernel<CODEC, IN, 256><<<routes < sms ? routes : sms, 256, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, span2, po);
     } else {
         const uint32_t need = (routes + 3u) / 4u;          // four rows side by side per CTA
-        small_prologue_kernel<CODEC, IN, 1024><<<need < sms ? need : sms, 1024, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, po);
+        small_prologue_kernel<CODEC, IN, 1024><<<need < sms ? need : sms, 1024, 0, st>>>(io, ids, w, rows, resident, max_n, mt1, mt2, span2, po);
     }
 }
 
@@ -469,7 +474,11 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     const bool pair = rows >= kPairMinRows && (mt1 % 2 == 0) && S->pair_ctas >= S->sms / 2;
     const bool dump = (S->debug & 1u) != 0;
     const bool y16 = ep ? ep->y16 : S->y16;
-    const int m_step = pair ? 2 : 1;
+    // FC2 items of the single-CTA kernel span several weight tile pairs when a rank's K slice is short (tensor parallelism:
+    // 2 or 4 chunks): the item's records and output-row addresses are then fetched once per 8 chunks of work, not per 2
+    const int k2 = L->i_local / kChunkK;
+    const int span2 = pair ? 1 : (k2 >= 8 ? 1 : k2 >= 4 ? 2 : 4);
+    const int m_step1 = pair ? 2 : 1, m_step2 = pair ? 2 : span2;
     const bool kt = (S->debug & 2u) != 0;
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
     const PlanScope scope{L->slots, ep ? ep->own_lo : 0u, ep ? ep->own_hi : rows, ep ? 1 : 0};
@@ -485,16 +494,16 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         const uint32_t grid = uint32_t(S->sms);
         const int sel = raw ? raw->codec * 2 + raw->dtype : 4;
         switch (sel) {
-            case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
-            case 1: launch_small_prologue<0, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
-            case 2: launch_small_prologue<1, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
-            case 3: launch_small_prologue<1, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
-            default: launch_small_prologue<0, 2>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, po); break;
+            case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
+            case 1: launch_small_prologue<0, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
+            case 2: launch_small_prologue<1, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
+            case 3: launch_small_prologue<1, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
+            default: launch_small_prologue<0, 2>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
         }
         M26B_CK(cudaGetLastError(), "m26b prologue launch");
     } else {
         if (routes <= 4096) {
-            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, scope, lc.max_n, mt1, mt2, m_step, po);
+            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, scope, lc.max_n, mt1, mt2, m_step1, m_step2, po);
         } else {
             // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
             const uint32_t slabs = (routes + 1023u) / 1024u;
@@ -502,7 +511,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
             const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
             uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
             plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, scope, cta_routes, cta_cnt, &status->meta);
-            plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step, L->slots, po);
+            plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step1, m_step2, L->slots, po);
             plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po, scope);
         }
         M26B_CK(cudaGetLastError(), "m26b plan launch");
@@ -541,7 +550,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (ep) a.sinks = ep->sinks;
     // FC1: weights w13 (K = hidden), tokens x_perm
     a.items = S->items1.as<WorkItem>(); a.n_items = &status->meta.n_items_fc1;
-    a.sfa = L->s13; a.sfb = S->sfb1.as<uint8_t>(); a.m_tiles = mt1; a.k_chunks = kHidden / kChunkK;
+    a.sfa = L->s13; a.sfb = S->sfb1.as<uint8_t>(); a.m_tiles = mt1; a.k_chunks = kHidden / kChunkK; a.m_span = 1;
     a.fault = &status->fault_fc1;
     if (pair) {
         PairMaps pm = S->pair_x;
@@ -554,7 +563,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     if (kt) M26B_CK(cudaEventRecord(S->kev[4], st), "m26b event");
     // FC2: weights w2 (K = i_local), tokens mid_q
     a.items = S->items2.as<WorkItem>(); a.n_items = &status->meta.n_items_fc2;
-    a.sfa = L->s2; a.sfb = S->mid_sf.as<uint8_t>(); a.m_tiles = mt2; a.k_chunks = L->i_local / kChunkK;
+    a.sfa = L->s2; a.sfb = S->mid_sf.as<uint8_t>(); a.m_tiles = mt2; a.k_chunks = L->i_local / kChunkK; a.m_span = span2;
     a.fault = &status->fault_fc2;
     if (pair) {
         PairMaps pm = S->pair_mid;
@@ -1744,7 +1753,7 @@ int m26b_plan_static(const int32_t* ids, const float* weights, uint32_t rows, in
     PlanOut po{inverse, original_routes, grouped_weights, sc->experts, sc->tiles, sc->items_fc1, sc->items_fc2, meta};
     const PlanScope scope{sc->slots, 0u, rows, 0};
     plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, scope, cta_routes, sc->cta_cnt, meta);
-    plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, 1, sc->slots, po);
+    plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, sc->cta_cnt, lc.max_n, kInter / kTileM, kHidden / kPairM, 1, 1, sc->slots, po);
     plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, weights, rows, cta_routes, sc->cta_cnt, po, scope);
     M26B_CK(cudaGetLastError(), "m26b plan_static launch");
     return 0;

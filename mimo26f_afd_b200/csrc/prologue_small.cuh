@@ -32,7 +32,8 @@ template <int CODEC, int IN, int THREADS>
 __global__ void __launch_bounds__(THREADS) small_prologue_kernel(SmallIo io, const int32_t* __restrict__ ids,
                                                              const float* __restrict__ w, uint32_t rows,
                                                              const int16_t* __restrict__ slots, int max_n, int mt_fc1,
-                                                             int mt_fc2, PlanOut o) {
+                                                             int mt_fc2, int m_step2, PlanOut o) {
+    mt_fc2 /= m_step2;      // an FC2 work item covers m_step2 consecutive weight tile pairs
     constexpr int kWarps = THREADS / 32;
     constexpr uint32_t kRowsAtOnce = THREADS / 256;      // grouped rows a CTA produces side by side
     __shared__ uint32_t wcnt[kWarps][kExperts];
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(THREADS) small_prologue_kernel(SmallIo io, con
             o.items_fc1[i1base[tid] + i] = WorkItem{int32_t(tstart[tid] + i % n), int32_t(i / n)};
     if (is_expert && blockIdx.x == 3u % gridDim.x)
         for (uint32_t i = 0; i < n * uint32_t(mt_fc2); ++i)
-            o.items_fc2[i2base[tid] + i] = WorkItem{int32_t(tstart[tid] + i % n), int32_t(i / n)};
+            o.items_fc2[i2base[tid] + i] = WorkItem{int32_t(tstart[tid] + i % n), int32_t(i / n) * m_step2};
     __syncthreads();
     // ---- grouped rows, kRowsAtOnce side by side: thread t of a row's 256 holds elements [16 t, 16 t + 16), a K32 block is
     // a pair of threads. The bound is the same for every thread of a warp (a warp never straddles two rows).

@@ -32,6 +32,33 @@ def shard_tokens(tokens: int, rank: int, world: int):
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+def serving_rank(ids, world: int, replicated=None):
+    """Which expert-parallel rank serves each route of a batch: ``ids`` int [tokens, 8] -> int array [tokens, 8].
+    A route to an expert in ``replicated`` (experts every rank holds a copy of) is served by the rank that owns the
+    route's token (``shard_tokens``); every other route by the rank whose block of 256 / world experts holds the expert.
+    The library's planner applies the same rule on the device; this host form is for load statistics (rows per rank,
+    rows that cross NVLink) and for choosing which experts to replicate."""
+    import numpy as np
+
+    ids = np.asarray(ids)
+    tokens = ids.shape[0]
+    his = np.array([shard_tokens(tokens, r, world)[1] for r in range(world)])
+    owner = np.searchsorted(his, np.arange(tokens), side="right")[:, None]
+    home = ids // (256 // world)
+    if replicated is None or len(replicated) == 0:
+        return home
+    return np.where(np.isin(ids, np.asarray(replicated)), owner, home)
+
+
+def busiest_experts(ids, n: int):
+    """The ``n`` experts with the most routes in ``ids`` (ties to the lower id): a replication set for ``serving_rank`` /
+    ``Layer.from_checkpoint_ep(replica_ids=...)`` when the batch itself is the popularity statistic."""
+    import numpy as np
+
+    counts = np.bincount(np.asarray(ids).reshape(-1), minlength=256)
+    return np.argsort(-counts, kind="stable")[:n].astype(np.int32)
+
+
 def all_gather_planes(plane, group=None):
     """All-gather one BF16 partial plane [tokens, 4096] per rank; returns the list in rank order.
     Works on CUDA tensors (NCCL) and on CPU tensors (gloo), so the exchange can be tested without GPUs."""

@@ -74,3 +74,30 @@ def test_tp_slice_rejects_bad_geometry():
         tp.tp_slice(4, 4)
     assert tp.tp_slice(3, 4) == (1536, 512)
     assert tp.shard_tokens(7, 2, 4) == (4, 6)
+
+
+def test_serving_rank_with_replicated_experts():
+    """Host form of the planner's rule for expert parallelism: routes to replicated experts stay with the token's owner,
+    the others go to the expert's home rank; every route is served by exactly one rank, and replicating the busiest
+    experts of a skewed batch evens the load out."""
+    from mimo26f_afd_b200 import synth, tp
+
+    ids, _ = synth.routing(0x26AFD, 4096, 1.0)
+    for world in (2, 4, 8):
+        home = tp.serving_rank(ids, world)
+        assert np.array_equal(home, ids // (256 // world))
+        hot = tp.busiest_experts(ids, 32)
+        assert len(set(hot.tolist())) == 32
+        counts = np.bincount(ids.reshape(-1), minlength=256)
+        assert counts[hot].min() >= np.delete(counts, hot).max()
+        serve = tp.serving_rank(ids, world, hot)
+        lo_hi = [tp.shard_tokens(4096, r, world) for r in range(world)]
+        for r, (lo, hi) in enumerate(lo_hi):
+            mine = serve == r
+            rep = np.isin(ids, hot)
+            own_tok = np.zeros(4096, bool); own_tok[lo:hi] = True
+            assert np.array_equal(mine, (rep & own_tok[:, None]) | (~rep & (ids // (256 // world) == r)))
+        load0 = np.bincount(home.reshape(-1), minlength=world)
+        load1 = np.bincount(serve.reshape(-1), minlength=world)
+        assert load1.sum() == ids.size and load1.max() / load1.mean() < load0.max() / load0.mean()
+        assert load1.max() / load1.mean() < 1.15
