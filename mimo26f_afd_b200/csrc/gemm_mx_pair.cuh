@@ -110,18 +110,7 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int half = tt.n_mma >> 1;                   // token rows this CTA holds
                 const int tok_row = tt.row_base + int(rank) * half;
                 const uint32_t tx = kPairM * 64 + uint32_t(half) * 128 + 3 * kScaleBlockBytes;
-#ifdef M26B_PREFETCH_NEXT
-                // the weight rows of this pair's next item, one chunk per chunk of this one, into L2
-                int next_row = -1;
-                if (it + n_pairs < n_items) {
-                    const ItemInfo nx = load_item(p, it + n_pairs, n_items);
-                    next_row = (nx.tt.expert * p.m_tiles + nx.wi.m_tile + int(rank)) * kPairM;
-                }
-#endif
                 for (int c = 0; c < p.k_chunks; ++c) {
-#ifdef M26B_PREFETCH_NEXT
-                    if (next_row >= 0) tma_prefetch_2d(&map_w, c * kChunkK, next_row);
-#endif
                     if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t bar = cluster_map(smem_u32(&s.full[stage]), 0);
                     if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * tx);   // the bytes of both CTAs' loads
