@@ -382,7 +382,7 @@ def run_tp(ctx, name, layer, scratch, k, y16=False, with_e2e=True, with_kernels=
     res = dict(workload=name, tokens=tokens, active_experts=inp["active"], parallelism=f"tp{world}" if world > 1 else "single",
                route_outputs="bf16" if y16 else "f32", value=tokens / (st["median"] * 1e-3), unit="tokens/s",
                ms_per_step=st["median"], ms_per_step_stats=st, rank_spread_ms=spread, clocks=clocks.summary())
-    il, routes = I // world, tokens * TOPK
+    il, routes = I // (world * args.rank_slice), tokens * TOPK
     if with_kernels and tokens <= PASS_ROWS:
         # the same step with an event between every two kernels: per-kernel durations for the roofline
         scratch.set_debug(2)
@@ -714,6 +714,9 @@ def main():
     ap.add_argument("--workload", default="decode16", choices=["decode16", "verify128", "prefill8k"],
                     help="the headline workload of the JSON line (the others are reported under their own keys)")
     ap.add_argument("--no-extra", action="store_true", help="headline workload only: no sub-results, no CPU baseline")
+    ap.add_argument("--rank-slice", type=int, default=1, choices=[1, 2, 4, 8],
+                    help="with --gpus 1: run ONE rank's share of a G-way tensor-parallel step (rank 0's slice of every expert, no "
+                         "exchange) on this GPU; for profiling a rank's kernels, not a benchmark result")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the ranks' planes are summed (NVLink peer-memory kernel, or NCCL all-gather + sum kernel)")
     args = ap.parse_args()
@@ -742,13 +745,23 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     k, k_big = args.steps, max(3, min(args.steps, 7))
     weights = synth.layer_torch(synth.MASTER_SEED, dev)
-    layer = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS], tp_rank=rank, tp_size=world)
+    if args.rank_slice > 1 and world > 1:
+        raise SystemExit("--rank-slice is for --gpus 1")
+    layer = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS], tp_rank=rank, tp_size=world * args.rank_slice)
     del weights
     torch.cuda.empty_cache()
     scratch = M.Scratch()
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
     ctx = Ctx(args, dev, stream, rank, world)
+    if args.rank_slice > 1:
+        # one rank's kernels on one GPU: timings only (the parity block needs the whole layer, sub-results mean nothing here)
+        r = run_tp(ctx, args.workload, layer, scratch, args.steps, with_e2e=False)
+        print(json.dumps(dict(note=f"one rank's share of a {args.rank_slice}-way tensor-parallel step on one GPU, no exchange: not a benchmark result",
+                              rank_slice=args.rank_slice, config=workload_config(args.workload), ms_per_step=r["ms_per_step"],
+                              ms_per_step_stats=r["ms_per_step_stats"], kernels_ms=r.get("kernels_ms"), roofline=r.get("roofline"),
+                              clocks=r["clocks"], identity=identity(args, dev))), flush=True)
+        return
 
     parity = dict(checked=True, before=parity_tp(ctx, layer, scratch))
     if not parity["before"]["ok"]:
