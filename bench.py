@@ -270,15 +270,20 @@ class Ctx:
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         return bool(t.item())
 
-    def timed_device(self, step, k):
+    def timed_device(self, step, k, align=None):
         """k samples of step() on the launching stream: barrier + synchronise + L2 flush before each (not timed), CUDA
-        events around it."""
+        events around it. `align` (several ranks): a device-side rendezvous of the ranks enqueued right before the first
+        event, so that every rank's sample starts within a microsecond of the others', as consecutive steps of a serving
+        loop do (each step ends in the exchange, which is such a rendezvous); without it the host barrier and the flush
+        leave the ranks several microseconds apart, and that skew would be counted as step time of the earliest rank."""
         import torch
 
         ms = []
         for _ in range(k):
             self.barrier()
             self.flush.fill_(1)
+            if align is not None:
+                align()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(self.stream)
             step()
@@ -375,8 +380,10 @@ def run_tp(ctx, name, layer, scratch, k, y16=False, with_e2e=True, with_kernels=
     for _ in range(args.warmup):
         step()
     check()
+    # the exchange kernel on an (unread) plane is the ranks' device-side rendezvous before each sample
+    align = (lambda: ex.sum(8, total, stream=stream.cuda_stream)) if ex is not None else None
     with ClockSampler(dev.index or 0) as clocks:
-        ms, spread = ctx.timed_device(step, k)
+        ms, spread = ctx.timed_device(step, k, align)
     check()
     st = stats(ms)
     res = dict(workload=name, tokens=tokens, active_experts=inp["active"], parallelism=f"tp{world}" if world > 1 else "single",
@@ -815,7 +822,8 @@ def main():
                     rank_spread_ms=main_r["rank_spread_ms"], higher_is_better=True, scaling="strong", vs_baseline=None,
                     dtype="e4m3 x e2m1 (mxf8f6f4), f32 accumulate", data="synthetic", config=workload_config(args.workload),
                     parallelism=main_r["parallelism"], exchange=(args.exchange if world > 1 else None),
-                    timing="value: per sample a barrier over the ranks, a device synchronise and an L2 flush (256 MB fill), then CUDA events "
+                    timing="value: per sample a barrier over the ranks, a device synchronise and an L2 flush (256 MB fill), with several "
+                           "ranks a device-side rendezvous (one exchange kernel on an unread plane), then CUDA events "
                            "on the launching stream around the step, max over ranks, value = tokens / median sample; e2e: wall clock "
                            "around each synchronous host call, calls back to back (inputs larger than L2: 1.4-3.4 GB of weights per step)",
                     active_experts=main_r["active_experts"], e2e=main_r.get("e2e"), gpu_launches=main_r["gpu_launches_per_step"] * k,
