@@ -358,10 +358,14 @@ def run_tp(ctx, name, layer, scratch, k, y16=False, with_e2e=True, with_kernels=
     xd, idd, wd = inp["xd"], inp["idd"], inp["wd"]
     out = torch.empty((tokens, H), dtype=torch.int16, device=dev)
     total = torch.empty((tokens, H), dtype=torch.float32, device=dev) if world > 1 else None
-    ex = tp.make_exchange(tokens) if world > 1 and args.exchange == "peer" else None
+    ex = tp.make_exchange(tokens) if world > 1 and args.exchange in ("peer", "pull") else None
     scratch.set_route_output(y16)
 
     def step():
+        if ex is not None and tokens <= PASS_ROWS and args.exchange == "peer":
+            # combine and exchange in one kernel up to 512 tokens; the library falls back to combine + pull exchange above
+            expert.ffn_tp_dev(layer, scratch, ex, xd, idd, wd, tokens, total, stream=stream.cuda_stream)
+            return
         dst = ex.plane() if ex is not None else out.data_ptr()
         for r0 in range(0, tokens, PASS_ROWS):
             n = min(PASS_ROWS, tokens - r0)
@@ -431,7 +435,11 @@ def run_tp(ctx, name, layer, scratch, k, y16=False, with_e2e=True, with_kernels=
                              tflops=FLOP_PER_TOKEN * tokens / step_s / 1e12, tflops_per_gpu=FLOP_PER_TOKEN * tokens / world / step_s / 1e12)
     passes = (tokens + PASS_ROWS - 1) // PASS_ROWS
     per_pass = 4 if tokens <= 128 else 5 if routes <= 4096 else 7
-    res["gpu_launches_per_step"] = passes * per_pass + (1 if world > 1 else 0)
+    fused_exchange = ex is not None and tokens <= 512 and args.exchange == "peer"
+    res["gpu_launches_per_step"] = passes * per_pass + (1 if world > 1 and not fused_exchange else 0)
+    if world > 1:
+        res["exchange"] = ("combine + push exchange in one kernel" if fused_exchange else
+                           "pull exchange kernel" if ex is not None else "nccl all-gather + rank-sum kernel")
 
     if with_e2e and tokens <= PASS_ROWS:
         # end to end through the host entry points: pinned host buffers, copies inside the timed region
@@ -623,6 +631,16 @@ def parity_tp(ctx, layer, scratch):
             same &= bool(torch.equal(peer_sum.view(torch.int32), nccl_sum.view(torch.int32)))
         out[f"peer_exchange_equals_nccl_sum_{tokens}"] = ctx.all_true(same)
         out["ok"] &= out[f"peer_exchange_equals_nccl_sum_{tokens}"]
+        same = True
+        for _ in range(3):                                      # the same with combine and exchange in one kernel
+            peer_sum.zero_()
+            expert.ffn_tp_dev(layer, scratch, ex, xd, idd, wd, tokens, peer_sum, stream=stream.cuda_stream)
+            scratch.status(stream.cuda_stream)
+            ex.status(stream.cuda_stream)
+            torch.cuda.synchronize()
+            same &= bool(torch.equal(peer_sum.view(torch.int32), nccl_sum.view(torch.int32)))
+        out[f"fused_combine_exchange_equals_nccl_sum_{tokens}"] = ctx.all_true(same)
+        out["ok"] &= out[f"fused_combine_exchange_equals_nccl_sum_{tokens}"]
         if tokens == 16 and ctx.rank == 0:
             tensors = synth.layer_np(synth.MASTER_SEED, np.unique(ids))
             planes = [oracle.ffn_layer(tensors, xq, xs, ids, w, tp_rank=r, tp_size=world)["bf16"] for r in range(world)]
@@ -724,8 +742,10 @@ def main():
     ap.add_argument("--rank-slice", type=int, default=1, choices=[1, 2, 4, 8],
                     help="with --gpus 1: run ONE rank's share of a G-way tensor-parallel step (rank 0's slice of every expert, no "
                          "exchange) on this GPU; for profiling a rank's kernels, not a benchmark result")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: how the ranks' planes are summed (NVLink peer-memory kernel, or NCCL all-gather + sum kernel)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "pull", "nccl"],
+                    help="N > 1: how the ranks' planes are summed: peer = NVLink peer memory, combine and exchange in one kernel up "
+                         "to 512 tokens (the default); pull = combine kernel, then the exchange kernel that reads the peers' planes; "
+                         "nccl = NCCL all-gather + sum kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

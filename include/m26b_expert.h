@@ -192,8 +192,9 @@ int m26b_produce_dev(const float* logits, const float* bias, uint32_t rows, int3
  *             scheme only protects a slot while every step's wait succeeds; a rank that keeps going after a lost
  *             step can overwrite a plane a slow peer is still reading). The same holds for the m26b_ep_* rendezvous.
  *   set_wait_ms: the bound of the wait (default 2000 ms).
- *   publish_as: marks the next step as published by `peer_rank` from the host; for single-process tests and for a
- *             coordinator that stands in for a rank it knows to be idle. */
+ *   publish_as: marks the next step as published by `peer_rank` from the host (its plane flag and its chunk flags of
+ *             m26b_ffn_tp_dev's fused form) and returns once the marks are in place (it synchronises `stream`); for
+ *             single-process tests and for a coordinator that stands in for a rank it knows to be idle. */
 int m26b_exchange_new(uint64_t plane_bytes, uint32_t rank, uint32_t world, m26b_exchange** out, uint8_t* handle_out,
                       char* err, size_t errlen);
 int m26b_exchange_connect(m26b_exchange* x, const uint8_t* handles, char* err, size_t errlen);
@@ -213,7 +214,8 @@ void m26b_exchange_free(m26b_exchange* x);
  * return a BF16 partial for the coordinator to sum (crates/mimo26-spark/src/serve.rs:206-246, then
  * crates/mimo26-wire/src/l4.rs:169-244). The request goes up from HOST memory exactly as in m26b_ffn, the rank's slice
  * runs with its BF16 plane written into the exchange window `x`, the planes are summed in rank order over NVLink
- * (m26b_exchange_sum_dev), and the FP32 sum [rows*4096] comes back to HOST memory on the ranks that pass sum_out (NULL
+ * (the fused kernel of m26b_ffn_tp_dev for requests of at most 512 tokens, else m26b_exchange_sum_dev), and the FP32 sum
+ * [rows*4096] comes back to HOST memory on the ranks that pass sum_out (NULL
  * elsewhere: one rank downloading is enough). Every rank of the group must make the call for every request.
  * rows x 8192 bytes must fit the exchange plane. Synchronous. ms (or NULL): [0] upload + enqueue, [1] GPU time
  * including the exchange, [2] host tail, [3] token tiles, the rest 0. Returns m26b_ffn's codes, or 5 when a peer's
@@ -221,6 +223,20 @@ void m26b_exchange_free(m26b_exchange* x);
 int m26b_ffn_tp(const m26b_layer* layer, m26b_scratch* scratch, m26b_exchange* x, const uint8_t* payload, size_t payload_pitch,
                 const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
                 float* sum_out, float* ms, char* err, size_t errlen);
+/* The device-pointer form, with the combine and the exchange in ONE kernel: m26b_ffn_dev's arguments (x, x_dtype,
+ * x_scales, codec, ids, weights as there), and instead of the rank's BF16 plane the call leaves the rank-ordered FP32 sum
+ * of all ranks' BF16 planes (+ residual, or NULL) in sum_out [rows*4096] on every rank: what the reference gets from the
+ * ranks' return frames and the coordinator's sum (crates/mimo26-wire/src/l4.rs:169-244, kernels/glue.cu:202-213), bit for
+ * bit. For steps of at most 512 tokens each CTA of the combine kernel stores its BF16 chunk into every peer's window
+ * (plain peer stores over NVLink, one flag per 1,024-element chunk) and, once its chunks are out, adds the chunks the
+ * peers pushed from local memory; the transfer overlaps the combine and no second kernel or read round trip follows.
+ * Larger steps (bandwidth-bound) run m26b_ffn_dev into m26b_exchange_plane() and m26b_exchange_sum_residual_dev behind
+ * it. One exchange step either way: every rank makes the call for every step, and the step counter is shared with
+ * m26b_exchange_sum_dev. Asynchronous on `stream`; m26b_scratch_status and m26b_exchange_status report as for the two
+ * calls it replaces (a peer's chunk that does not arrive within the bound: code 5 from m26b_exchange_status). */
+int m26b_ffn_tp_dev(const m26b_layer* layer, m26b_scratch* scratch, m26b_exchange* x, const void* x_act, int x_dtype,
+                    const uint8_t* x_scales, int codec, const int32_t* ids, const float* weights, uint32_t rows,
+                    const float* residual, float* sum_out, void* stream, char* err, size_t errlen);
 
 /* Expert parallelism inside one NVLink box, one process per GPU (the reference has no expert-
  * parallel mode: it shards every expert's intermediate dimension over its four ranks, crates/mimo26-repack/src/geom.rs:29-35).

@@ -17,6 +17,7 @@ from .expert import (  # noqa: F401
     ffn_dev,
     ffn_strided,
     ffn_tp,
+    ffn_tp_dev,
     plan_static,
     produce_dev,
     quantize_dev,

@@ -20,7 +20,7 @@ SYMBOLS = (
     "m26b_ep_set_wait_ms", "m26b_ep_publish_as", "m26b_ep_begin_dev", "m26b_ep_compute_dev", "m26b_ep_finish_dev",
     "m26b_ep_status", "m26b_ep_free", "m26b_produce_dev",
     "m26b_rank_sum_residual_dev", "m26b_exchange_sum_residual_dev", "m26b_scratch_set_route_output", "m26b_ep_set_route_output",
-    "m26b_ffn_tp", "m26b_ep_ffn", "m26b_layer_image", "m26b_layer_new_from_checkpoint_ep_replicated",
+    "m26b_ffn_tp", "m26b_ffn_tp_dev", "m26b_ep_ffn", "m26b_layer_image", "m26b_layer_new_from_checkpoint_ep_replicated",
     "m26b_frame_request_bytes", "m26b_frame_return_bytes", "m26b_frame_crc32c", "m26b_frame_crc32c_table", "m26b_frame_encode_request",
     "m26b_serve_frame", "m26b_frame_parse_return", "m26b_frame_check_request",
 )
@@ -57,6 +57,7 @@ def lib() -> C.CDLL:
     L.m26b_ffn_dev.argtypes = [vp, vp, vp, C.c_int, u8p, C.c_int, i32p, f32p, C.c_uint32, u16p, f32p, vp, *err]
     L.m26b_scratch_status.argtypes = [vp, vp, *err]
     L.m26b_scratch_set_debug.argtypes = [vp, C.c_uint32]
+    L.m26b_ffn_tp_dev.argtypes = [vp, vp, vp, vp, C.c_int, u8p, C.c_int, i32p, f32p, C.c_uint32, f32p, f32p, vp, *err]
     L.m26b_ffn_tp.argtypes = [vp, vp, vp, u8p, C.c_size_t, u8p, C.c_size_t, i32p, f32p, C.c_uint32, f32p, f32p, *err]
     L.m26b_ep_ffn.argtypes = [vp, vp, vp, u8p, C.c_size_t, u8p, C.c_size_t, i32p, f32p, C.c_uint32, u16p, *err]
     L.m26b_scratch_set_route_output.argtypes = [vp, C.c_int]

@@ -201,6 +201,14 @@ struct m26b_exchange {
     uint64_t plane_bytes = 0;
     uint32_t step = 0;                  // steps summed so far; the next step writes slot (step + 1) & 1
     long long wait_cycles = 0;
+    PushLayout push{};                  // chunk flags and receive planes of the fused combine + exchange (small steps)
+};
+
+// Where a pass's combine goes when it is fused with the plane exchange of a tensor-parallel group.
+struct PushSink {
+    m26b_exchange* X;
+    float* out;                         // FP32 rank-ordered sum (+ residual)
+    const float* residual;
 };
 
 struct m26b_ep {
@@ -462,7 +470,7 @@ struct EpPass {
 int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const uint8_t* xs, const int32_t* ids,
                  const float* w, uint32_t rows, uint16_t* bf16_out, float* partial_out, Status* status,
                  cudaStream_t st, bool events, char* err, size_t errlen, const RawInput* raw = nullptr,
-                 bool status_cleared = false, const EpPass* ep = nullptr) {
+                 bool status_cleared = false, const EpPass* ep = nullptr, const PushSink* push = nullptr) {
     cudaError_t e;
     const uint32_t routes = rows * kTopK;
     const LaunchClass lc = launch_class(rows);
@@ -574,7 +582,21 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     }
     if (events) M26B_CK(cudaEventRecord(S->ec, st), "m26b event c");
     if (kt) M26B_CK(cudaEventRecord(S->kev[5], st), "m26b event");
-    if (!ep) {   // an expert-parallel pass leaves its rows with the tokens' owners; they combine after the step's rendezvous
+    if (push) {
+        // combine, push into every rank's window, add the peers' chunks: one kernel, one step of the exchange
+        m26b_exchange* X = push->X;
+        X->step += 1;
+        const uint32_t chunks = rows * (kHidden / 1024);
+        const uint32_t blocks = chunks < uint32_t(S->sms) * 4u ? chunks : uint32_t(S->sms) * 4u;
+        if (y16)
+            M26B_CK(launch_dependent(reduce_exchange_kernel<true>, blocks, 256u, size_t(0), st, static_cast<const void*>(S->y.p), w, rows,
+                                     X->peers, X->push, X->rank, X->world, X->step, X->wait_cycles, push->out, push->residual,
+                                     &status->fault_reduce), "m26b reduce+exchange launch");
+        else
+            M26B_CK(launch_dependent(reduce_exchange_kernel<false>, blocks, 256u, size_t(0), st, static_cast<const void*>(S->y.p), w, rows,
+                                     X->peers, X->push, X->rank, X->world, X->step, X->wait_cycles, push->out, push->residual,
+                                     &status->fault_reduce), "m26b reduce+exchange launch");
+    } else if (!ep) {   // an expert-parallel pass leaves its rows with the tokens' owners; they combine after the step's rendezvous
         if (y16) {
             const uint64_t n8 = uint64_t(rows) * (kHidden / 8);
             const uint32_t blocks = uint32_t(n8 / 256 + 1 < 16384 ? n8 / 256 + 1 : 16384);
@@ -987,6 +1009,52 @@ int m26b_ffn_dev(const m26b_layer* L, m26b_scratch* S, const void* x, int x_dtyp
     return 0;
 }
 
+// m26b_ffn_dev for a rank of a tensor-parallel group: the pass's combine is fused with the plane exchange, so the call
+// leaves the rank-ordered FP32 sum of every rank's BF16 plane (+ residual) in sum_out. Steps too large for the fused form
+// run the combine into the rank's plane and the pull-form exchange kernel behind it; either way it is one exchange step.
+int m26b_ffn_tp_dev(const m26b_layer* L, m26b_scratch* S, m26b_exchange* X, const void* x, int x_dtype, const uint8_t* x_scales,
+                    int codec, const int32_t* ids, const float* weights, uint32_t rows, const float* residual, float* sum_out,
+                    void* stream, char* err, size_t errlen) {
+    if (!L || !S || !X || !rows || rows > kMaxPassRows || !x || !ids || !weights || !sum_out || x_dtype < 0 || x_dtype > 2 ||
+        (x_dtype == 2 && !x_scales) || codec < 0 || codec > 1 || uint64_t(rows) * kHidden * 2 > X->plane_bytes) {
+        set_msg(err, errlen, "m26b ffn_tp: bad rows/handles/pitch (the request must fit the exchange plane)");
+        return 1;
+    }
+    if (!device_ok(L->device, err, errlen) || !device_ok(S->device, err, errlen) || !device_ok(X->device, err, errlen)) return 1;
+    if (uint32_t(X->world) != L->tp_size || uint32_t(X->rank) != L->tp_rank) {
+        set_msg(err, errlen, "m26b ffn_tp: the exchange window and the layer belong to different ranks");
+        return 1;
+    }
+    for (int r = 0; r < X->world; ++r)
+        if (!X->peers.window[r]) { set_msg(err, errlen, "m26b ffn_tp: the exchange is not connected to every peer"); return 1; }
+    if (reinterpret_cast<uintptr_t>(x) & 15u) {
+        set_msg(err, errlen, "m26b ffn: the activation pointer must be 16-byte aligned");
+        return 1;
+    }
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : S->st;
+    int rc = ensure_pass(S, rows, L->i_local, x_dtype != 2, err, errlen);
+    if (rc) return rc;
+    Status* status = S->status.as<Status>();
+    const uint8_t* xq = static_cast<const uint8_t*>(x);
+    const uint8_t* xs = x_scales;
+    RawInput raw{x, x_dtype, codec, &status[1].fault_input};
+    if (x_dtype != 2) {
+        cudaError_t e;
+        M26B_CK(cudaMemsetAsync(status, 0, 2 * sizeof(Status), st), "m26b status clear");
+        xq = S->xq.as<uint8_t>(); xs = S->xs.as<uint8_t>();
+    }
+    S->kev_quant = false;
+    const bool fused = uint64_t(rows) * kHidden * 2 <= X->push.cap;
+    const PushSink sink{X, sum_out, residual};
+    rc = enqueue_pass(L, S, xq, xs, ids, weights, rows, fused ? nullptr : static_cast<uint16_t*>(m26b_exchange_plane(X)), nullptr,
+                      status, st, false, err, errlen, x_dtype != 2 ? &raw : nullptr, x_dtype != 2, nullptr, fused ? &sink : nullptr);
+    if (rc) return rc;
+    S->pending = true;
+    S->n_status = x_dtype != 2 ? 2 : 1;
+    if (!fused) return m26b_exchange_sum_residual_dev(X, uint64_t(rows) * kHidden, residual, sum_out, st, err, errlen);
+    return 0;
+}
+
 int m26b_scratch_status(m26b_scratch* S, void* stream, char* err, size_t errlen) {
     if (!S) { set_msg(err, errlen, "m26b status: null scratch"); return 1; }
     cudaError_t e;
@@ -1041,9 +1109,19 @@ int m26b_exchange_new(uint64_t plane_bytes, uint32_t rank, uint32_t world, m26b_
     cudaError_t e;
     m26b_exchange* X = new m26b_exchange();
     X->rank = int(rank); X->world = int(world); X->plane_bytes = plane_bytes;
+    // behind the two plane slots of the pull form: chunk flags and receive planes of the push form (steps of at most
+    // kPushRows tokens, where a kernel boundary and a round trip matter; larger steps are bandwidth-bound and pull)
+    const uint64_t push_cap = plane_bytes < uint64_t(kPushRows) * kHidden * 2 ? plane_bytes : uint64_t(kPushRows) * kHidden * 2;
+    X->push.cap = push_cap;
+    X->push.max_chunks = uint32_t((push_cap / 2 + 1023) / 1024);
+    X->push.cflag_off = sizeof(ExchangeWindow) + 2 * plane_bytes;
+    const uint64_t flag_bytes = ((uint64_t(2) * 8 * X->push.max_chunks * 4 + 255) / 256) * 256;
+    X->push.recv_off = X->push.cflag_off + flag_bytes;
+    const uint64_t total = X->push.recv_off + uint64_t(2) * world * push_cap;
     if ((e = cudaGetDevice(&X->device)) != cudaSuccess ||
-        (e = cudaMalloc(&X->window, sizeof(ExchangeWindow) + 2 * plane_bytes)) != cudaSuccess ||
-        (e = cudaMemset(X->window, 0, sizeof(ExchangeWindow))) != cudaSuccess) {
+        (e = cudaMalloc(&X->window, total)) != cudaSuccess ||
+        (e = cudaMemset(X->window, 0, sizeof(ExchangeWindow))) != cudaSuccess ||
+        (e = cudaMemset(static_cast<uint8_t*>(X->window) + X->push.cflag_off, 0, flag_bytes)) != cudaSuccess) {
         set_err(err, errlen, "m26b exchange window", e);
         m26b_exchange_free(X);
         return 2;
@@ -1110,9 +1188,16 @@ int m26b_exchange_set_wait_ms(m26b_exchange* X, uint32_t ms) {
 int m26b_exchange_publish_as(m26b_exchange* X, uint32_t peer_rank, void* stream, char* err, size_t errlen) {
     if (!X || int(peer_rank) >= X->world || int(peer_rank) == X->rank) { set_msg(err, errlen, "m26b exchange: bad peer"); return 1; }
     const uint32_t next = X->step + 1;
-    const cudaError_t e = cudaMemcpyAsync(&static_cast<ExchangeWindow*>(X->window)->flags[peer_rank], &next, 4,
-                                          cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+    cudaError_t e = cudaMemcpyAsync(&static_cast<ExchangeWindow*>(X->window)->flags[peer_rank], &next, 4,
+                                    cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) { set_err(err, errlen, "m26b exchange publish", e); return 2; }
+    // and the peer's chunk flags of the fused form, for the slot the next step uses
+    uint32_t* cf = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(X->window) + X->push.cflag_off) +
+                   (size_t(next & 1u) * 8 + peer_rank) * X->push.max_chunks;
+    fill_words_kernel<<<(X->push.max_chunks + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(cf, next, X->push.max_chunks);
+    if ((e = cudaGetLastError()) != cudaSuccess) { set_err(err, errlen, "m26b exchange publish", e); return 2; }
+    // the marks must be in place before any kernel that waits for them is launched (on whatever stream)
+    if ((e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream))) != cudaSuccess) { set_err(err, errlen, "m26b exchange publish", e); return 2; }
     return 0;
 }
 
@@ -1437,17 +1522,28 @@ int m26b_ffn_tp(const m26b_layer* L, m26b_scratch* S, m26b_exchange* X, const ui
     const float* w_d;
     rc = upload_request(S, payload, payload_pitch, scales, scales_pitch, ids, weights, rows, &xq_d, &xs_d, &ids_d, &w_d, err, errlen);
     if (rc) return rc;
+    for (int r = 0; r < X->world; ++r)
+        if (!X->peers.window[r]) { set_msg(err, errlen, "m26b ffn_tp: the exchange is not connected to every peer"); return 1; }
     uint16_t* const plane = static_cast<uint16_t*>(m26b_exchange_plane(X));
     M26B_CK(cudaEventRecord(S->e0, S->st), "m26b event 0");
-    for (uint32_t ps = 0; ps < passes; ++ps) {
+    const bool fused = passes == 1 && uint64_t(rows) * kHidden * 2 <= X->push.cap;
+    const PushSink sink{X, S->tp_sum.as<float>(), nullptr};
+    if (fused) {
+        rc = enqueue_pass(L, S, xq_d, xs_d, ids_d, w_d, rows, nullptr, nullptr, S->status.as<Status>(), S->st, false, err, errlen,
+                          nullptr, false, nullptr, &sink);
+        if (rc) return rc;
+    }
+    for (uint32_t ps = 0; ps < (fused ? 0u : passes); ++ps) {
         const uint32_t r0 = ps * kMaxPassRows, n = rows - r0 < kMaxPassRows ? rows - r0 : kMaxPassRows;
         rc = enqueue_pass(L, S, xq_d + size_t(r0) * kHidden, xs_d + size_t(r0) * (kHidden / kBlockK), ids_d + size_t(r0) * kTopK,
                           w_d + size_t(r0) * kTopK, n, plane + size_t(r0) * kHidden, nullptr, S->status.as<Status>() + ps, S->st,
                           false, err, errlen);
         if (rc) return rc;
     }
-    rc = m26b_exchange_sum_residual_dev(X, uint64_t(rows) * kHidden, nullptr, S->tp_sum.as<float>(), S->st, err, errlen);
-    if (rc) return rc;
+    if (!fused) {
+        rc = m26b_exchange_sum_residual_dev(X, uint64_t(rows) * kHidden, nullptr, S->tp_sum.as<float>(), S->st, err, errlen);
+        if (rc) return rc;
+    }
     M26B_CK(cudaEventRecord(S->e1, S->st), "m26b event 1");
     if (sum_out)
         M26B_CK(cudaMemcpyAsync(sum_out, S->tp_sum.p, size_t(rows) * kHidden * 4, cudaMemcpyDeviceToHost, S->st), "m26b sum download");

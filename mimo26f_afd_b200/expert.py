@@ -251,6 +251,17 @@ def ffn_dev(layer: Layer, scratch: Scratch, x, ids, weights, rows: int, bf16_out
     _check(rc, err)
 
 
+def ffn_tp_dev(layer: Layer, scratch: Scratch, exchange: "Exchange", x, ids, weights, rows: int, sum_out, *,
+               x_dtype: int = X_BF16, x_scales=None, codec: int = CODEC_WIRE, residual=None, stream=None) -> None:
+    """``ffn_dev`` for a rank of a tensor-parallel group, with the combine and the plane exchange in one kernel: leaves
+    the rank-ordered FP32 sum of every rank's BF16 plane (+ ``residual``) in ``sum_out`` [rows, 4096] on every rank.
+    One step of ``exchange``; every rank makes the call. ``Scratch.status`` / ``Exchange.status`` report faults."""
+    err = C.create_string_buffer(256)
+    rc = _native.lib().m26b_ffn_tp_dev(layer._h, scratch._h, exchange._h, _ptr(x), x_dtype, _ptr(x_scales), codec, _ptr(ids),
+                                       _ptr(weights), rows, _ptr(residual), _ptr(sum_out), _ptr(stream), err, 256)
+    _check(rc, err)
+
+
 def quantize_dev(x, x_dtype: int, n_elems: int, codec: int, payload, scales, fault, stream=None) -> None:
     err = C.create_string_buffer(256)
     _check(_native.lib().m26b_quantize_dev(_ptr(x), x_dtype, n_elems, codec, _ptr(payload), _ptr(scales), _ptr(fault),

@@ -922,19 +922,24 @@ def test_bf16_route_outputs_follow_the_reference_variant(layer, dev, oracle_mod,
 
 # ------------------------------------------------------------------------------------------ tensor-parallel host entry point
 def test_ffn_tp_host_entry_point_one_rank_and_two_windows(weights, dev, oracle_mod):
-    """m26b_ffn_tp through ctypes on one GPU. World 1: the sum of one plane equals the BF16 output widened. World 2 with
-    both windows in this process: rank 1's plane is written first and its publication marked from the host (so no
-    kernel waits for another kernel); rank 0's call then returns the rank-ordered sum of the two planes, equal bit for
-    bit to the sum kernel on the same planes and within the end-to-end bar of the oracle's wire result."""
+    """m26b_ffn_tp / m26b_ffn_tp_dev through ctypes on one GPU. World 1: the sum of one plane equals the BF16 output
+    widened (+ residual). World 2 with both windows in this process, no kernel ever waiting for another kernel: up to 512
+    tokens (combine and exchange fused) rank 0's chunk flags are marked from the host, rank 1's call pushes its plane and
+    flags into rank 0's window, and rank 0's call then finds them; above 512 tokens rank 1's plane is written first and
+    its publication marked from the host. Rank 0's sum equals the oracle's rank-ordered sum of the two planes bit for
+    bit, and the oracle's wire result within the end-to-end bar."""
     import torch
 
     import mimo26f_afd_b200 as M
     from mimo26f_afd_b200 import expert, synth
 
-    for tokens in (16, 200):
+    for tokens in (16, 200, 600):
+        fused = tokens <= 512
         x_bits = synth.activations_bf16(SEED + 70, tokens)
         ids, w = synth.routing(SEED + 70, tokens, 0.0)
         xq, xs = oracle_mod.quant_wire(synth.bf16_to_f32_np(x_bits))
+        xqd, xsd = to_dev(xq, dev), to_dev(xs, dev)
+        idd, wd = to_dev(ids, dev), to_dev(w, dev)
         # world 1
         L = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS])
         s = M.Scratch()
@@ -946,6 +951,13 @@ def test_ffn_tp_host_entry_point_one_rank_and_two_windows(weights, dev, oracle_m
         M.ffn(L, s, xq.reshape(-1), xs.reshape(-1), ids.reshape(-1), w.reshape(-1), tokens, bf.reshape(-1))
         assert np.array_equal(total.view(np.uint32), synth.bf16_to_f32_np(bf).view(np.uint32))
         M.ffn_tp(L, s, ex, xq, xs, ids, w, tokens, None)       # a rank that does not download
+        # the device form, from BF16 activations, with the residual folded in
+        res = torch.randn(tokens, H, device=dev)
+        got = torch.empty(tokens, H, device=dev)
+        expert.ffn_tp_dev(L, s, ex, to_dev(x_bits.view(np.int16), dev), idd, wd, tokens, got, residual=res)
+        s.status(); ex.status()
+        want = res.cpu().numpy() + synth.bf16_to_f32_np(bf)
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.astype(np.float32).view(np.uint32))
         ex.close(); L.close()
         # world 2, both windows here
         layers = [M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS], tp_rank=r, tp_size=2) for r in range(2)]
@@ -953,29 +965,48 @@ def test_ffn_tp_host_entry_point_one_rank_and_two_windows(weights, dev, oracle_m
         for e in exs:
             e.connect_local(exs)
         s1 = M.Scratch()
-        xqd, xsd = to_dev(xq, dev), to_dev(xs, dev)
-        idd, wd = to_dev(ids, dev), to_dev(w, dev)
+        plane1_d = torch.empty(tokens * H, dtype=torch.int16, device=dev)
+        expert.ffn_dev(layers[1], s1, xqd, idd, wd, tokens, plane1_d, x_dtype=expert.X_E4M3, x_scales=xsd)
+        s1.status()
+        plane1 = plane1_d.cpu().numpy().view(np.uint16).reshape(tokens, H)
+        bf0 = np.empty((tokens, H), np.uint16)
+        M.ffn(layers[0], s, xq.reshape(-1), xs.reshape(-1), ids.reshape(-1), w.reshape(-1), tokens, bf0.reshape(-1))
+        want = oracle_mod.rank_sum(np.stack([bf0, plane1]))
+        sum1 = torch.empty(tokens * H, dtype=torch.float32, device=dev)
         for step in range(3):                                   # both slots and a reuse
-            expert.ffn_dev(layers[1], s1, xqd, idd, wd, tokens, exs[1].plane(), x_dtype=expert.X_E4M3, x_scales=xsd)
-            s1.status()
-            plane1 = torch.as_tensor(_DevView(exs[1].plane(), tokens * H, "<i2"), device=dev).cpu().numpy().view(np.uint16).reshape(tokens, H)
-            exs[0].publish_as(1)
-            torch.cuda.synchronize()
-            M.ffn_tp(layers[0], s, exs[0], xq, xs, ids, w, tokens, total)
-            # rank 1 takes the same step (its sum is not read here)
-            exs[1].publish_as(0)
-            exs[1].sum(tokens * H, torch.empty(tokens * H, dtype=torch.float32, device=dev))
-            exs[1].status()
-            bf0 = np.empty((tokens, H), np.uint16)
-            M.ffn(layers[0], s, xq.reshape(-1), xs.reshape(-1), ids.reshape(-1), w.reshape(-1), tokens, bf0.reshape(-1))
-            want = oracle_mod.rank_sum(np.stack([bf0, plane1]))
+            if fused:
+                exs[1].publish_as(0)
+                expert.ffn_tp_dev(layers[1], s1, exs[1], xqd, idd, wd, tokens, sum1, x_dtype=expert.X_E4M3, x_scales=xsd)
+                s1.status(); exs[1].status()
+                torch.cuda.synchronize()
+                M.ffn_tp(layers[0], s, exs[0], xq, xs, ids, w, tokens, total)
+            else:
+                expert.ffn_dev(layers[1], s1, xqd, idd, wd, tokens, exs[1].plane(), x_dtype=expert.X_E4M3, x_scales=xsd)
+                s1.status()
+                exs[0].publish_as(1)
+                torch.cuda.synchronize()
+                M.ffn_tp(layers[0], s, exs[0], xq, xs, ids, w, tokens, total)
+                exs[1].publish_as(0)                            # rank 1 takes the same step (its sum is not read here)
+                exs[1].sum(tokens * H, sum1)
+                exs[1].status()
             assert np.array_equal(total.view(np.uint32), want.view(np.uint32)), (tokens, step)
-        ref = [oracle_mod.ffn_layer(synth.layer_np(SEED, np.unique(ids)), xq, xs, ids, w, tp_rank=r, tp_size=2) for r in range(2)]
-        wire = oracle_mod.rank_sum(np.stack([r["bf16"] for r in ref]))
-        assert rel_l2(total, wire) <= 1e-3
+        if fused:
+            # rank 1 once more, now that rank 0's chunks of the last step are in its window: the same sum on both ranks
+            # (the two slots alternate, so a step of rank 1 alone re-reads rank 0's chunks of two steps back: same data)
+            exs[1].publish_as(0)
+            expert.ffn_tp_dev(layers[1], s1, exs[1], xqd, idd, wd, tokens, sum1, x_dtype=expert.X_E4M3, x_scales=xsd)
+            s1.status(); exs[1].status()
+            assert np.array_equal(sum1.cpu().numpy().view(np.uint32).reshape(tokens, H), want.view(np.uint32))
+        if tokens <= 200:
+            ref = [oracle_mod.ffn_layer(synth.layer_np(SEED, np.unique(ids)), xq, xs, ids, w, tp_rank=r, tp_size=2) for r in range(2)]
+            wire = oracle_mod.rank_sum(np.stack([r["bf16"] for r in ref]))
+            assert rel_l2(total, wire) <= 1e-3
         # a layer of another rank, or a request larger than the plane, is refused before anything runs
         with pytest.raises(M.ExpertError) as e:
             M.ffn_tp(layers[1], s, exs[0], xq, xs, ids, w, tokens, total)
+        assert e.value.code == 1
+        with pytest.raises(M.ExpertError) as e:
+            expert.ffn_tp_dev(layers[1], s, exs[0], xqd, idd, wd, tokens, sum1, x_dtype=expert.X_E4M3, x_scales=xsd)
         assert e.value.code == 1
         for e_ in exs:
             e_.close()

@@ -1,8 +1,9 @@
 """One rank of the multi-GPU tensor-parallel check (launched by test_tp_multi_gpu.py through torch.distributed.run).
 
-Every rank builds its slice of the synthetic layer, runs the same batch, and the ranks' BF16 planes are summed twice:
-through the NVLink peer-memory exchange kernel and through an NCCL all-gather followed by the rank-sum kernel. The two
-must agree bit for bit, on every rank, and match the CPU oracle of the whole layer within the end-to-end tolerance."""
+Every rank builds its slice of the synthetic layer, runs the same batch, and the ranks' BF16 planes are summed three ways:
+by the NVLink peer-memory exchange kernel (pull), by the combine kernel that pushes its chunks into the peers' windows and
+adds what the peers pushed (one kernel), and by an NCCL all-gather followed by the rank-sum kernel. The three must agree
+bit for bit, on every rank, and match the CPU oracle of the whole layer within the end-to-end tolerance."""
 import os
 import sys
 
@@ -49,6 +50,21 @@ def main():
             tp.tp_combine(plane, nccl_sum, stream=stream.cuda_stream)
             torch.cuda.synchronize()
             assert torch.equal(peer_sum.view(torch.int32), nccl_sum.view(torch.int32)), (tokens, step, rank)
+        res = torch.randn((tokens, H), device=dev)
+        for step in range(3):                                   # combine and exchange in one kernel, residual folded in
+            peer_sum.zero_()
+            expert.ffn_tp_dev(layer, scratch, ex, xd, idd, wd, tokens, peer_sum, residual=res if step == 2 else None,
+                              stream=stream.cuda_stream)
+            scratch.status(stream.cuda_stream)
+            ex.status(stream.cuda_stream)
+            torch.cuda.synchronize()
+            want = nccl_sum + res if step == 2 else nccl_sum
+            assert torch.equal(peer_sum.view(torch.int32), want.view(torch.int32)), ("fused", tokens, step, rank)
+        expert.ffn_dev(layer, scratch, xd, idd, wd, tokens, ex.plane(), stream=stream.cuda_stream)   # and the pull form again
+        ex.sum(tokens * H, peer_sum, stream=stream.cuda_stream)
+        ex.status(stream.cuda_stream)
+        torch.cuda.synchronize()
+        assert torch.equal(peer_sum.view(torch.int32), nccl_sum.view(torch.int32)), ("pull after fused", tokens, rank)
         if tokens == 16:
             x = synth.bf16_to_f32_np(x_bits)
             xq, xs = oracle.quant_wire(x)
