@@ -838,38 +838,47 @@ __global__ void __launch_bounds__(256) exchange_sum_kernel(ExchangePeers peers, 
 
 // ---------------------------------------------------------------- combine + exchange in one kernel (push form)
 // For decode-sized steps of a tensor-parallel rank the two kernels above (combine into the rank's own plane; exchange
-// kernel that publishes, waits and reads the peers' planes over NVLink) become one: every CTA computes the ordered top-8
-// combine of its chunk of the plane (1,024 elements), stores the BF16 chunk into EVERY rank's window (its own and, with
-// plain peer stores, the peers'), raises the chunk's flag in the peers' windows, and - once all its chunks are pushed -
-// waits for the peers' flags of the same chunks and adds the G chunks in rank order from LOCAL memory. The NVLink
-// transfer is posted stores that overlap the combine of the following chunks, and the read round trip and one kernel
-// boundary of the pull form disappear. Pushes never wait for anything, so no rank can block another before it has
-// delivered; the waits are bounded like the pull form's (error word, status code 5).
+// kernel that publishes, waits and reads the peers' planes over NVLink) become one. Every thread computes the ordered top-8
+// combine of four columns, and stores the four BF16 codes TOGETHER WITH THE STEP NUMBER into every rank's window (its own
+// and, with plain peer stores, the peers'): one 16-byte store {codes 0-1, step, codes 2-3, step}. NVLink delivers each
+// 8-byte half whole, so a half whose flag word equals the step carries that step's data: no fence, no separate flag and no
+// acknowledged round trip stand between a rank's store and a peer's use of it. Once its chunks are out, the CTA polls the
+// same 16 bytes of every source's plane in its OWN window until both flags show the step (bounded; error word, status
+// code 5) and adds the G planes in rank order from local memory. Pushes never wait for anything, so no rank can block
+// another before it has delivered.
 //
-// Window area of the push form (behind the pull form's two plane slots): chunk flags [2 slots][8 sources][max_chunks] and
-// receive planes [2 slots][G sources][cap bytes]. A slot is rewritten two steps later, after this rank has seen every
-// peer's flags of the step in between, which a peer only raises after its own step before that has finished reading.
-constexpr uint32_t kPushRows = 512;        // largest step (tokens) the fused form serves: 4 MB per receive plane
+// Window area of the push form (behind the pull form's two plane slots): receive planes [2 slots][G sources][cap bytes],
+// 4 bytes per plane element. A slot is rewritten two steps later, which a peer can only reach after this rank has pushed
+// the step in between, which it does after it has finished reading. Flags are step numbers, so nothing is ever cleared.
+constexpr uint32_t kPushRows = 512;        // largest step (tokens) the fused form serves: 8 MB per receive plane
 struct PushLayout {
-    uint64_t cflag_off, recv_off, cap;      // byte offsets inside a window; bytes per receive plane
-    uint32_t max_chunks;
+    uint64_t recv_off, cap;                // byte offset inside a window; bytes per receive plane
 };
-__device__ __forceinline__ uint32_t* push_flag(uint8_t* window, const PushLayout& lay, uint32_t slot, uint32_t src, uint32_t chunk) {
-    return reinterpret_cast<uint32_t*>(window + lay.cflag_off) + (size_t(slot) * 8 + src) * lay.max_chunks + chunk;
+__device__ __forceinline__ uint4* push_plane(uint8_t* window, const PushLayout& lay, uint32_t slot, uint32_t world, uint32_t src) {
+    return reinterpret_cast<uint4*>(window + lay.recv_off + (size_t(slot) * world + src) * lay.cap);
 }
-__device__ __forceinline__ uint8_t* push_plane(uint8_t* window, const PushLayout& lay, uint32_t slot, uint32_t world, uint32_t src) {
-    return window + lay.recv_off + (size_t(slot) * world + src) * lay.cap;
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-__global__ void fill_words_kernel(uint32_t* p, uint32_t v, uint32_t n) {
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Host-side stand-in for a peer (single-process tests, an idle rank): marks every element of `plane` as delivered for
+// `step`, leaving the data words as they are.
+__global__ void push_mark_kernel(uint4* plane, uint32_t step, uint32_t n) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) p[i] = v;
+    if (i < n) {
+        uint32_t* f = reinterpret_cast<uint32_t*>(plane + i);
+        f[1] = step; f[3] = step;
+    }
 }
 template <bool Y16>
 __global__ void __launch_bounds__(256) reduce_exchange_kernel(const void* __restrict__ y_in, const float* __restrict__ w, uint32_t rows,
                                                               ExchangePeers peers, PushLayout lay, int rank, int world, uint32_t step,
                                                               long long wait_cycles, float* __restrict__ out,
                                                               const float* residual, uint32_t* __restrict__ fault) {
-    __shared__ uint32_t late;
     const float kMax = 3.402823466e+38f;
     const uint32_t slot = step & 1u, tid = threadIdx.x;
     const uint64_t n4 = uint64_t(rows) * (kHidden / 4);                 // groups of four columns, one per thread and chunk
@@ -877,89 +886,80 @@ __global__ void __launch_bounds__(256) reduce_exchange_kernel(const void* __rest
     ExchangeWindow* mine = reinterpret_cast<ExchangeWindow*>(peers.window[rank]);
     bool failed = false;
     grid_dep_wait();             // y comes from the FC2 kernel
-    // ---- phase 1: combine, push, flag
+    // ---- phase 1: combine and push
     for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x) {
         const uint64_t i = uint64_t(c) * 256 + tid;
-        if (i < n4) {
-            const uint64_t row = i / (kHidden / 4), c4 = i % (kHidden / 4);
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            bool ok = true;
-            float z[kTopK][4];
+        if (i >= n4) break;
+        const uint64_t row = i / (kHidden / 4), c4 = i % (kHidden / 4);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        bool ok = true;
+        float z[kTopK][4];
 #pragma unroll
-            for (int j = 0; j < kTopK; ++j) {
-                if constexpr (Y16) {
-                    const uint2 q = reinterpret_cast<const uint2*>(y_in)[(row * kTopK + j) * (kHidden / 4) + c4];
-                    z[j][0] = __uint_as_float(q.x << 16); z[j][1] = __uint_as_float(q.x & 0xffff0000u);
-                    z[j][2] = __uint_as_float(q.y << 16); z[j][3] = __uint_as_float(q.y & 0xffff0000u);
-                } else {
-                    const float4 q = reinterpret_cast<const float4*>(y_in)[(row * kTopK + j) * (kHidden / 4) + c4];
-                    z[j][0] = q.x; z[j][1] = q.y; z[j][2] = q.z; z[j][3] = q.w;
-                }
+        for (int j = 0; j < kTopK; ++j) {
+            if constexpr (Y16) {
+                const uint2 q = reinterpret_cast<const uint2*>(y_in)[(row * kTopK + j) * (kHidden / 4) + c4];
+                z[j][0] = __uint_as_float(q.x << 16); z[j][1] = __uint_as_float(q.x & 0xffff0000u);
+                z[j][2] = __uint_as_float(q.y << 16); z[j][3] = __uint_as_float(q.y & 0xffff0000u);
+            } else {
+                const float4 q = reinterpret_cast<const float4*>(y_in)[(row * kTopK + j) * (kHidden / 4) + c4];
+                z[j][0] = q.x; z[j][1] = q.y; z[j][2] = q.z; z[j][3] = q.w;
             }
-#pragma unroll
-            for (int j = 0; j < kTopK; ++j) {
-                const float wt = w[row * kTopK + j];
-                ok = ok && wt >= 0.0f && wt <= kMax;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    ok = ok && z[j][k] >= -kMax && z[j][k] <= kMax;
-                    v[k] = __fadd_rn(v[k], __fmul_rn(wt, z[j][k]));
-                    ok = ok && v[k] >= -kMax && v[k] <= kMax;
-                }
-            }
-            uint32_t code[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { code[k] = bf16_rne_bits(v[k]); ok = ok && (code[k] & 0x7f80u) != 0x7f80u; }
-            if (!ok) { failed = true; code[0] = code[1] = code[2] = code[3] = 0; }
-            const uint2 packed = make_uint2(code[0] | (code[1] << 16), code[2] | (code[3] << 16));
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-                if (r < world) reinterpret_cast<uint2*>(push_plane(peers.window[r], lay, slot, uint32_t(world), uint32_t(rank)))[i] = packed;
         }
-        // the chunk's stores happen before the barrier, the barrier before the flag's release (system scope, cumulative):
-        // a peer that acquires the flag sees the chunk. One releasing thread per peer, not a fence in every thread:
-        // 16K system-scope fences per launch cost more than the transfer they order.
-        __syncthreads();
-        if (tid < uint32_t(world) && int(tid) != rank) st_release_sys(push_flag(peers.window[tid], lay, slot, uint32_t(rank), c), step);
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) {
+            const float wt = w[row * kTopK + j];
+            ok = ok && wt >= 0.0f && wt <= kMax;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                ok = ok && z[j][k] >= -kMax && z[j][k] <= kMax;
+                v[k] = __fadd_rn(v[k], __fmul_rn(wt, z[j][k]));
+                ok = ok && v[k] >= -kMax && v[k] <= kMax;
+            }
+        }
+        uint32_t code[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { code[k] = bf16_rne_bits(v[k]); ok = ok && (code[k] & 0x7f80u) != 0x7f80u; }
+        if (!ok) { failed = true; code[0] = code[1] = code[2] = code[3] = 0; }
+        const uint4 word = make_uint4(code[0] | (code[1] << 16), step, code[2] | (code[3] << 16), step);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < world) st_volatile_v4(push_plane(peers.window[r], lay, slot, uint32_t(world), uint32_t(rank)) + i, word);
     }
-    // ---- phase 2: wait for the peers' chunks, add in rank order from local memory
-    for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x) {
-        if (tid == 0) late = 0;
-        __syncthreads();
-        if (tid < uint32_t(world) && int(tid) != rank) {
-            const uint32_t* f = push_flag(peers.window[rank], lay, slot, tid, c);
-            const long long t0 = clock64();
-            while (int32_t(ld_acquire_sys(f) - step) < 0) {
-                if (clock64() - t0 > wait_cycles) { atomicOr(&late, 1u << tid); break; }
-            }
-        }
-        __syncthreads();
-        if (late) {
-            if (tid == 0) atomicOr(&mine->error, late);
-            break;                   // uniform: `late` is shared
-        }
+    // ---- phase 2: every source's words of this rank's window, as they arrive; add in rank order
+    uint32_t late = 0;
+    for (uint32_t c = blockIdx.x; c < chunks && !late; c += gridDim.x) {
         const uint64_t i = uint64_t(c) * 256 + tid;
-        if (i < n4) {
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint2 q[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-                if (r < world) q[r] = __ldcv(reinterpret_cast<const uint2*>(push_plane(peers.window[rank], lay, slot, uint32_t(world), uint32_t(r))) + i);
+        if (i >= n4) break;
+        uint4 q[8];
+        uint32_t pending = (1u << world) - 1u;
+        const long long t0 = clock64();
+        while (pending) {
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
-                if (r >= world) break;
-                s4[0] = __fadd_rn(s4[0], __uint_as_float(q[r].x << 16));
-                s4[1] = __fadd_rn(s4[1], __uint_as_float(q[r].x & 0xffff0000u));
-                s4[2] = __fadd_rn(s4[2], __uint_as_float(q[r].y << 16));
-                s4[3] = __fadd_rn(s4[3], __uint_as_float(q[r].y & 0xffff0000u));
+                if (r < world && (pending >> r & 1u)) {
+                    q[r] = ld_volatile_v4(push_plane(peers.window[rank], lay, slot, uint32_t(world), uint32_t(r)) + i);
+                    if (q[r].y == step && q[r].w == step) pending &= ~(1u << r);
+                }
             }
-            if (residual) {
-                const float4 a = reinterpret_cast<const float4*>(residual)[i];
-                s4[0] = __fadd_rn(a.x, s4[0]); s4[1] = __fadd_rn(a.y, s4[1]); s4[2] = __fadd_rn(a.z, s4[2]); s4[3] = __fadd_rn(a.w, s4[3]);
-            }
-            reinterpret_cast<float4*>(out)[i] = make_float4(s4[0], s4[1], s4[2], s4[3]);
+            if (pending && clock64() - t0 > wait_cycles) { late = pending; break; }
         }
+        if (late) break;
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= world) break;
+            s4[0] = __fadd_rn(s4[0], __uint_as_float(q[r].x << 16));
+            s4[1] = __fadd_rn(s4[1], __uint_as_float(q[r].x & 0xffff0000u));
+            s4[2] = __fadd_rn(s4[2], __uint_as_float(q[r].z << 16));
+            s4[3] = __fadd_rn(s4[3], __uint_as_float(q[r].z & 0xffff0000u));
+        }
+        if (residual) {
+            const float4 a = reinterpret_cast<const float4*>(residual)[i];
+            s4[0] = __fadd_rn(a.x, s4[0]); s4[1] = __fadd_rn(a.y, s4[1]); s4[2] = __fadd_rn(a.z, s4[2]); s4[3] = __fadd_rn(a.w, s4[3]);
+        }
+        reinterpret_cast<float4*>(out)[i] = make_float4(s4[0], s4[1], s4[2], s4[3]);
     }
+    if (late) atomicOr(&mine->error, late);
     if (__syncthreads_or(failed) && tid == 0) atomicOr(fault, uint32_t(kFaultReduce));
 }
 

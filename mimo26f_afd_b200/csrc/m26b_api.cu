@@ -201,7 +201,7 @@ struct m26b_exchange {
     uint64_t plane_bytes = 0;
     uint32_t step = 0;                  // steps summed so far; the next step writes slot (step + 1) & 1
     long long wait_cycles = 0;
-    PushLayout push{};                  // chunk flags and receive planes of the fused combine + exchange (small steps)
+    PushLayout push{};                  // receive planes of the fused combine + exchange (small steps)
 };
 
 // Where a pass's combine goes when it is fused with the plane exchange of a tensor-parallel group.
@@ -1044,7 +1044,7 @@ int m26b_ffn_tp_dev(const m26b_layer* L, m26b_scratch* S, m26b_exchange* X, cons
         xq = S->xq.as<uint8_t>(); xs = S->xs.as<uint8_t>();
     }
     S->kev_quant = false;
-    const bool fused = uint64_t(rows) * kHidden * 2 <= X->push.cap;
+    const bool fused = uint64_t(rows) * kHidden * 4 <= X->push.cap;
     const PushSink sink{X, sum_out, residual};
     rc = enqueue_pass(L, S, xq, xs, ids, weights, rows, fused ? nullptr : static_cast<uint16_t*>(m26b_exchange_plane(X)), nullptr,
                       status, st, false, err, errlen, x_dtype != 2 ? &raw : nullptr, x_dtype != 2, nullptr, fused ? &sink : nullptr);
@@ -1109,19 +1109,17 @@ int m26b_exchange_new(uint64_t plane_bytes, uint32_t rank, uint32_t world, m26b_
     cudaError_t e;
     m26b_exchange* X = new m26b_exchange();
     X->rank = int(rank); X->world = int(world); X->plane_bytes = plane_bytes;
-    // behind the two plane slots of the pull form: chunk flags and receive planes of the push form (steps of at most
-    // kPushRows tokens, where a kernel boundary and a round trip matter; larger steps are bandwidth-bound and pull)
-    const uint64_t push_cap = plane_bytes < uint64_t(kPushRows) * kHidden * 2 ? plane_bytes : uint64_t(kPushRows) * kHidden * 2;
+    // behind the two plane slots of the pull form: the receive planes of the push form (steps of at most kPushRows tokens,
+    // where a kernel boundary and a round trip matter; larger steps are bandwidth-bound and pull). 4 bytes per element:
+    // every 8-byte half carries two BF16 codes and the step number. Zero-filled once: step numbers start at 1.
+    const uint64_t push_cap = (plane_bytes < uint64_t(kPushRows) * kHidden * 2 ? plane_bytes : uint64_t(kPushRows) * kHidden * 2) * 2;
     X->push.cap = push_cap;
-    X->push.max_chunks = uint32_t((push_cap / 2 + 1023) / 1024);
-    X->push.cflag_off = sizeof(ExchangeWindow) + 2 * plane_bytes;
-    const uint64_t flag_bytes = ((uint64_t(2) * 8 * X->push.max_chunks * 4 + 255) / 256) * 256;
-    X->push.recv_off = X->push.cflag_off + flag_bytes;
+    X->push.recv_off = sizeof(ExchangeWindow) + 2 * plane_bytes;
     const uint64_t total = X->push.recv_off + uint64_t(2) * world * push_cap;
     if ((e = cudaGetDevice(&X->device)) != cudaSuccess ||
         (e = cudaMalloc(&X->window, total)) != cudaSuccess ||
         (e = cudaMemset(X->window, 0, sizeof(ExchangeWindow))) != cudaSuccess ||
-        (e = cudaMemset(static_cast<uint8_t*>(X->window) + X->push.cflag_off, 0, flag_bytes)) != cudaSuccess) {
+        (e = cudaMemset(static_cast<uint8_t*>(X->window) + X->push.recv_off, 0, uint64_t(2) * world * push_cap)) != cudaSuccess) {
         set_err(err, errlen, "m26b exchange window", e);
         m26b_exchange_free(X);
         return 2;
@@ -1191,10 +1189,11 @@ int m26b_exchange_publish_as(m26b_exchange* X, uint32_t peer_rank, void* stream,
     cudaError_t e = cudaMemcpyAsync(&static_cast<ExchangeWindow*>(X->window)->flags[peer_rank], &next, 4,
                                     cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) { set_err(err, errlen, "m26b exchange publish", e); return 2; }
-    // and the peer's chunk flags of the fused form, for the slot the next step uses
-    uint32_t* cf = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(X->window) + X->push.cflag_off) +
-                   (size_t(next & 1u) * 8 + peer_rank) * X->push.max_chunks;
-    fill_words_kernel<<<(X->push.max_chunks + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(cf, next, X->push.max_chunks);
+    // and the peer's receive plane of the fused form, for the slot the next step uses: flags only, data as they are
+    uint4* pl = reinterpret_cast<uint4*>(static_cast<uint8_t*>(X->window) + X->push.recv_off +
+                                         (size_t(next & 1u) * X->world + peer_rank) * X->push.cap);
+    const uint32_t words = uint32_t(X->push.cap / 16);
+    push_mark_kernel<<<(words + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(pl, next, words);
     if ((e = cudaGetLastError()) != cudaSuccess) { set_err(err, errlen, "m26b exchange publish", e); return 2; }
     // the marks must be in place before any kernel that waits for them is launched (on whatever stream)
     if ((e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream))) != cudaSuccess) { set_err(err, errlen, "m26b exchange publish", e); return 2; }
@@ -1526,7 +1525,7 @@ int m26b_ffn_tp(const m26b_layer* L, m26b_scratch* S, m26b_exchange* X, const ui
         if (!X->peers.window[r]) { set_msg(err, errlen, "m26b ffn_tp: the exchange is not connected to every peer"); return 1; }
     uint16_t* const plane = static_cast<uint16_t*>(m26b_exchange_plane(X));
     M26B_CK(cudaEventRecord(S->e0, S->st), "m26b event 0");
-    const bool fused = passes == 1 && uint64_t(rows) * kHidden * 2 <= X->push.cap;
+    const bool fused = passes == 1 && uint64_t(rows) * kHidden * 4 <= X->push.cap;
     const PushSink sink{X, S->tp_sum.as<float>(), nullptr};
     if (fused) {
         rc = enqueue_pass(L, S, xq_d, xs_d, ids_d, w_d, rows, nullptr, nullptr, S->status.as<Status>(), S->st, false, err, errlen,
