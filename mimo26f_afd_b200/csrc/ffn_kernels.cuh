@@ -1010,6 +1010,21 @@ __global__ void __launch_bounds__(256) prep_s13_kernel(ProjSrc gate, ProjSrc up,
     }
     if (odd) atomicOr(abnormal, 1u);
 }
+// s13h[e][j][h][c][512]: the scale block of half item h of tile pair j = rows 0..63 the gate rows 64 h .., rows 64..127 the
+// up rows 64 h .. of the same features: per 16-byte lane row, 8 bytes of the gate block and 8 of the up block of s13.
+__global__ void __launch_bounds__(256) prep_s13_half_kernel(const uint8_t* __restrict__ s13, int i_local, uint8_t* __restrict__ dst, int n_experts) {
+    const uint64_t chunks = kHidden / kChunkK, tiles = uint64_t(i_local) / kTileM;
+    const uint64_t total = uint64_t(n_experts) * tiles * 2 * chunks * kScaleBlockBytes;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint32_t o = uint32_t(i % kScaleBlockBytes);
+        const uint64_t c = (i / kScaleBlockBytes) % chunks, h = (i / kScaleBlockBytes / chunks) % 2;
+        const uint64_t ej = i / kScaleBlockBytes / chunks / 2;                  // e * tiles + j
+        const uint32_t lane = o >> 4, grp = (o >> 2) & 3u, kb = o & 3u;
+        const uint64_t b = grp >> 1;                                           // 0: gate block, 1: up block
+        const uint32_t src_grp = uint32_t(h) * 2u + (grp & 1u);
+        dst[i] = s13[((ej * chunks + c) * 2 + b) * kScaleBlockBytes + lane * 16 + src_grp * 4 + kb];
+    }
+}
 // w2[e][h][i_local/2]: this rank's K slice of every down_proj row.
 __global__ void __launch_bounds__(256) prep_w2_kernel(ProjSrc down, int i_local, uint8_t* __restrict__ dst, int n_experts) {
     const uint64_t vec_per_row = uint64_t(i_local) / 2 / 16;

@@ -121,16 +121,33 @@ struct TokenMaps {
     CUtensorMap box[4];
 };
 
-template <int B_ROWS, int STAGES>
+// A_TILES = 2: an item is a 256-row weight tile pair (two MMA tiles side by side in tensor memory). A_TILES = 1 (FC1 only):
+// an item is HALF a tile pair - 64 gate rows and the 64 up rows of the same features in ONE 128-row MMA tile - so a
+// decode step has twice as many, half as long items to spread over the SMs (a tensor-parallel rank of eight has 204 full
+// items for 148 SMs: two rounds where 1.4 would do). Gate and up of a feature then sit in different tensor-memory lanes
+// (quadrants 0-1 gate, 2-3 up): the up warps hand their values to the gate warps through `xup`.
+template <int B_ROWS, int STAGES, int A_TILES = 2>
 struct GemmSmem {
-    alignas(1024) uint8_t a[STAGES][kPairM * 128];
+    alignas(1024) uint8_t a[STAGES][A_TILES * kTileM * 128];
     alignas(1024) uint8_t b[STAGES][B_ROWS * 128];
-    alignas(16) uint8_t sfa[STAGES][2 * kScaleBlockBytes];
+    alignas(16) uint8_t sfa[STAGES][A_TILES * kScaleBlockBytes];
     alignas(16) uint8_t sfb[STAGES][kScaleBlockBytes];
     uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
+    alignas(16) uint32_t xup[A_TILES == 1 ? 8 : 1][A_TILES == 1 ? B_ROWS / 4 : 1][32];   // [warp pair][value][lane]
 };
+
+// Barrier `id` (1..15) over `threads` threads that also ORs a predicate over them: every participant gets the same answer.
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t threads, bool pred) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %3, 0;\n\tbar.red.or.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(r) : "r"(id), "r"(threads), "r"(uint32_t(pred)) : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
+}
 
 // E-ACT-CR32 activation: e = exp(-|g|) (never a positive exponential), s = g / (1 + e) or g e / (1 + e),
 // h = s u. The exponential and the reciprocal of 1 + e (which lies in [1, 2]) use the hardware
@@ -147,14 +164,19 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return __fmul_rn(__fmul_rn(num, r), u);
 }
 
-static_assert(sizeof(GemmSmem<32, 6>) + 1024 <= 232448 && sizeof(GemmSmem<kMaxN, 4>) + 1024 <= 232448 && sizeof(GemmSmem<64, 5>) + 1024 <= 232448,
+static_assert(sizeof(GemmSmem<32, 6>) + 1024 <= 232448 && sizeof(GemmSmem<kMaxN, 4>) + 1024 <= 232448 && sizeof(GemmSmem<64, 5>) + 1024 <= 232448 &&
+              sizeof(GemmSmem<32, 10, 1>) + 1024 <= 232448,
               "a CTA has at most 227 KB of shared memory");
 
 // DUMP: also store the FP32 intermediate (stage dumps of the parity tests). Y16: FC2 rows as BF16.
-template <int MODE, int B_ROWS, int STAGES, bool DUMP = false, bool Y16 = false>
+// A_TILES = 1 (FC1, token tiles of at most 64): half items; map_w then has 64-row boxes, p.sfa names the half-item scale
+// image [E][m_tiles][2 halves][k_chunks][512] and WorkItem::m_tile counts halves.
+template <int MODE, int B_ROWS, int STAGES, bool DUMP = false, bool Y16 = false, int A_TILES = 2>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_x, const GemmArgs p) {
-    using Smem = GemmSmem<B_ROWS, STAGES>;
+    using Smem = GemmSmem<B_ROWS, STAGES, A_TILES>;
+    constexpr bool kHalf = A_TILES == 1;
+    static_assert(!kHalf || (MODE == kModeFc1 && B_ROWS <= 64), "half items: FC1 with token tiles of at most 64");
     // Token tiles of at most 64 columns leave room for two accumulator sets in each tile's 128 tensor-memory columns
     // (set b at column offset b * B_ROWS): the MMAs of item i + 1 start while the epilogue still pulls item i. With items
     // as short as a rank's K slice under tensor parallelism (2-8 chunks) the hand-over would otherwise be half the time.
@@ -221,18 +243,21 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const WorkItem wi = cur.wi;
                 const TokenTile tt = cur.tt;
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
-                const uint32_t tx = kPairM * 64 + tt.n_mma * 128 + 3 * kScaleBlockBytes;
+                const uint32_t tx = A_TILES * kTileM * 64 + tt.n_mma * 128 + (A_TILES + 1) * kScaleBlockBytes;
                 for (int mm = 0; mm < p.m_span && ok; ++mm) {
-                    const int slot = tt.expert * p.m_tiles + wi.m_tile + mm;
-                    const int w_row = slot * kPairM;
-                    const uint8_t* sfa_g = p.sfa + size_t(slot) * p.k_chunks * 2 * kScaleBlockBytes;
+                    // half items: m_tile counts halves; half h of tile pair j = gate rows 64 h .. and up rows 128 + 64 h ..
+                    const int m_pair = kHalf ? (wi.m_tile >> 1) : wi.m_tile + mm, half = kHalf ? (wi.m_tile & 1) : 0;
+                    const int slot = tt.expert * p.m_tiles + m_pair;
+                    const int w_row = slot * kPairM + half * (kTileM / 2);
+                    const uint8_t* sfa_g = p.sfa + (size_t(slot) * 2 + half * (kHalf ? 1 : 0)) * p.k_chunks * kScaleBlockBytes;
                     for (int c = 0; c < p.k_chunks; ++c) {
                         const bool weights_in_flight = kEarlyWeights && it == blockIdx.x && mm == 0 && c < early;
                         if (!weights_in_flight) {
                             if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                             mbar_expect_tx(&s.full[stage], tx);
                             tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
-                            bulk_load(s.sfa[stage], sfa_g + size_t(c) * 2 * kScaleBlockBytes, 2 * kScaleBlockBytes, &s.full[stage]);
+                            if constexpr (kHalf) tma_load_2d(s.a[stage] + (kTileM / 2) * 128, &map_w, c * kChunkK, w_row + kTileM, &s.full[stage]);
+                            bulk_load(s.sfa[stage], sfa_g + size_t(c) * A_TILES * kScaleBlockBytes, A_TILES * kScaleBlockBytes, &s.full[stage]);
                         }
                         int r = 0;
 #pragma unroll
@@ -279,7 +304,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     sf_slot ^= 1u;
                     const uint64_t sfa_d = sfa_desc0 + stage * kSfaStage;
                     tc_cp_scales(t_sf, sfa_d);
-                    tc_cp_scales(t_sf + 4, sfa_d + (kScaleBlockBytes >> 4));
+                    if constexpr (!kHalf) tc_cp_scales(t_sf + 4, sfa_d + (kScaleBlockBytes >> 4));
                     tc_cp_scales(t_sf + 8, sfb_desc0 + stage * kSfbStage);
                     const uint64_t ad = a_desc0 + stage * kAStage, bd = b_desc0 + stage * kBStage;
 #pragma unroll
@@ -289,7 +314,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const uint32_t idesc = idesc0 | (kb << 4) | (kb << 29);
                         const uint32_t accum = (c | int(kb)) ? 1u : 0u;
                         tc_mma_mx(d0, ad + 2 * kb, bd + 2 * kb, idesc, t_sf, t_sf + 8, accum);
-                        tc_mma_mx(d1, ad + ((kTileM * 128) >> 4) + 2 * kb, bd + 2 * kb, idesc, t_sf + 4, t_sf + 8, accum);
+                        if constexpr (!kHalf) tc_mma_mx(d1, ad + ((kTileM * 128) >> 4) + 2 * kb, bd + 2 * kb, idesc, t_sf + 4, t_sf + 8, accum);
                     }
                     tc_commit(&s.empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -321,9 +346,76 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           // the item's weight tile pairs one after the other: same token tile, same output rows
           for (int mm = 0; mm < p.m_span && ok; ++mm, ++local, ++wi.m_tile) {
             const uint32_t aset = local % kAccSets, ause = local / kAccSets;
-            if (!mbar_wait(&s.acc_full[aset], ause & 1u, abort_flag)) { ok = false; break; }
-            tc_fence_after();
+            const bool got = mbar_wait(&s.acc_full[aset], ause & 1u, abort_flag);
             const uint32_t t_acc = tb + ((q * 32u) << 16) + aset * B_ROWS;
+            if constexpr (kHalf) {
+                // lanes of quadrants 0, 1: gate of features 64 half + 32 q + lane; quadrants 2, 3: up of the same features.
+                // Warp (q, wq) and warp (q + 2, wq) form a pair on named barrier 1 + pair: the up warp parks its values in
+                // shared memory, the gate warp picks them up. The first barrier also carries "my wait ran out", so both
+                // warps of a pair leave together and neither can be left waiting at a barrier.
+                const uint32_t pair = (q & 1u) * 4u + wq;
+                uint32_t gt[2][8];
+                if (got) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        const int c0 = (int(wq) + 4 * g) * 8;
+                        if (c0 < tt.n_mma) tmem_ld8(t_acc + uint32_t(c0), gt[g]);
+                    }
+                    tmem_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s.acc_empty[aset]);
+                    if (q >= 2u) {
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {
+                            if ((int(wq) + 4 * g) * 8 >= tt.n_mma) break;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) s.xup[pair][g * 8 + j][lane] = gt[g][j];
+                        }
+                    }
+                }
+                if (named_bar_or(1u + pair, 64u, !got)) { ok = false; break; }
+                if (q >= 2u) { named_bar_sync(1u + pair, 64u); continue; }
+                uint32_t up[2][8];
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    if ((int(wq) + 4 * g) * 8 >= tt.n_mma) break;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) up[g][j] = s.xup[pair][g * 8 + j][lane];
+                }
+                named_bar_sync(1u + pair, 64u);          // the up warp may overwrite its slots for the next item
+                const int m_pair = wi.m_tile >> 1, half = wi.m_tile & 1;
+                const int feat0 = m_pair * kTileM + half * (kTileM / 2) + int(q) * 32;
+                uint8_t* sf_tile = p.mid_sf + (size_t(wi.tile) * (p.i_local / kChunkK) + m_pair) * kScaleBlockBytes;
+                uint8_t* mq = p.mid_q + size_t(tt.row_base) * p.i_local + feat0 + lane;
+                float* mf = DUMP ? p.mid_f32 + size_t(tt.row_base) * p.i_local + feat0 + lane : nullptr;
+                uint32_t fault = 0;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int c0 = (int(wq) + 4 * g) * 8;
+                    if (c0 >= tt.n_mma) break;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int t = c0 + j;
+                        if (t >= tt.n_valid) continue;   // warp-uniform
+                        const float h = silu_mul(__uint_as_float(gt[g][j]), __uint_as_float(up[g][j]));
+                        if constexpr (DUMP) mf[size_t(t) * p.i_local] = h;
+                        const uint32_t bits = __float_as_uint(h);
+                        const uint32_t amax = __reduce_max_sync(0xffffffffu, bits & 0x7fffffffu);
+                        if (amax >= 0x7f800000u) { fault |= kFaultQuantNonfinite; continue; }
+                        const int k = quant_v1_scale_exp(amax);
+                        const uint32_t code = quant_v1_payload(bits, k);
+                        if (k > 119 && __any_sync(0xffffffffu, !quant_v1_finite(code, k))) { fault |= kFaultQuantOverflow; continue; }
+                        mq[size_t(t) * p.i_local] = uint8_t(code);
+                        if (lane == 0) sf_tile[scale_block_offset(t, half * 2 + int(q))] = uint8_t(k + 127);
+                    }
+                }
+                if (fault && lane == 0) atomicOr(p.fault, fault);
+                continue;
+            }
+            if (!got) { ok = false; break; }
+            tc_fence_after();
             if constexpr (MODE == kModeFc2) {
                 // warp (q, wq): weight tile (wq & 1) of the pair, token groups (wq >> 1), +2, +4 ... of 8 tokens;
                 // hidden row = 256 m + 128 tile + 32 q + lane

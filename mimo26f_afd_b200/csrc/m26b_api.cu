@@ -86,13 +86,13 @@ cudaError_t launch_dependent(void (*kernel)(P...), unsigned grid, unsigned block
     return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
 }
 
-template <int MODE, int B_ROWS, int STAGES, bool DUMP, bool Y16>
+template <int MODE, int B_ROWS, int STAGES, bool DUMP, bool Y16, int A_TILES = 2>
 cudaError_t launch_gemm(const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
-    const int smem = int(sizeof(GemmSmem<B_ROWS, STAGES>)) + 1024;
-    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16>,
+    const int smem = int(sizeof(GemmSmem<B_ROWS, STAGES, A_TILES>)) + 1024;
+    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16, A_TILES>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return launch_dependent(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16>, unsigned(ctas), kGemmThreads, size_t(smem), st, mw, mx, a);
+    return launch_dependent(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16, A_TILES>, unsigned(ctas), kGemmThreads, size_t(smem), st, mw, mx, a);
 }
 // Scale blocks as a 2-D tensor of 128 x u32 rows (one 512-byte block per row), no swizzle.
 bool make_sf_map(CUtensorMap* m, const void* base, uint64_t blocks, uint32_t box_rows) {
@@ -171,6 +171,12 @@ cudaError_t launch_gemm_class(uint32_t rows, bool variant, const CUtensorMap& mw
     return launch_gemm_variant<MODE, kMaxN, 4>(variant, mw, mx, a, ctas, st);
 }
 
+// FC1 with half items (64 gate + 64 up rows per item): `mw` has 64-row boxes, a.sfa names the half-item scale image.
+// Only the smallest launch class (at most 32 tokens) ever has few enough items for them to pay.
+cudaError_t launch_fc1_half(bool dump, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
+    return dump ? launch_gemm<kModeFc1, 32, 10, true, false, 1>(mw, mx, a, ctas, st) : launch_gemm<kModeFc1, 32, 10, false, false, 1>(mw, mx, a, ctas, st);
+}
+
 // Device status block of one pass: PlanMeta then four fault words.
 struct Status {
     PlanMeta meta;
@@ -183,6 +189,7 @@ static_assert(sizeof(Status) == 64, "status block is 64 bytes");
 
 struct m26b_layer {
     uint8_t *w13 = nullptr, *s13 = nullptr, *w2 = nullptr, *s2 = nullptr;
+    uint8_t* s13h = nullptr;                    // the scale blocks of s13 regrouped for half items: [slot][tile][half][chunk][512]
     int16_t* slots = nullptr;                   // device, [256]: slot of each expert in the weight image (layout.cuh)
     int i_local = 0;
     uint32_t tp_rank = 0, tp_size = 1;
@@ -191,6 +198,7 @@ struct m26b_layer {
     bool all_normal = false;
     int device = 0;
     CUtensorMap map_w13, map_w2, map_s13, map_s2;
+    CUtensorMap map_w13h;                       // w13 with 64-row boxes (half items)
 };
 
 struct m26b_exchange {
@@ -299,6 +307,7 @@ int prepare_layer(const ExpertSet& home, const ExpertSet* rep, const int32_t* re
         return rc;
     };
     if ((e = cudaMalloc(&L->w13, w13_bytes)) != cudaSuccess || (e = cudaMalloc(&L->s13, s13_bytes)) != cudaSuccess ||
+        (e = cudaMalloc(&L->s13h, s13_bytes)) != cudaSuccess ||
         (e = cudaMalloc(&L->w2, w2_bytes)) != cudaSuccess || (e = cudaMalloc(&L->s2, s2_bytes)) != cudaSuccess ||
         (e = cudaMalloc(&L->slots, sizeof table)) != cudaSuccess || (e = cudaMalloc(&flag, 4)) != cudaSuccess)
         return fail("m26b layer alloc", e, 2);
@@ -314,6 +323,7 @@ int prepare_layer(const ExpertSet& home, const ExpertSet* rep, const int32_t* re
         prep_w2_kernel<<<2048, 256>>>(src.down, i_local, L->w2 + first * w2_e, src.n);
         prep_s2_kernel<<<2048, 256>>>(src.down, i_local, L->s2 + first * s2_e, flag, src.n);
     }
+    prep_s13_half_kernel<<<2048, 256>>>(L->s13, i_local, L->s13h, n_slots);
     uint32_t h = 1;
     if ((e = cudaGetLastError()) != cudaSuccess || (e = cudaMemcpy(&h, flag, 4, cudaMemcpyDeviceToHost)) != cudaSuccess ||
         (e = cudaDeviceSynchronize()) != cudaSuccess)
@@ -321,6 +331,7 @@ int prepare_layer(const ExpertSet& home, const ExpertSet* rep, const int32_t* re
     cudaFree(flag); flag = nullptr;
     L->all_normal = h == 0;
     if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(n_slots) * 2 * i_local, kHidden / 2, kPairM) ||
+        !make_map(&L->map_w13h, true, L->w13, kHidden, uint64_t(n_slots) * 2 * i_local, kHidden / 2, kTileM / 2) ||
         !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(n_slots) * kHidden, uint64_t(i_local) / 2, kPairM)) {
         set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight operands");
         m26b_layer_free(L);
@@ -380,7 +391,7 @@ int ensure_pass(m26b_scratch* S, uint32_t rows, int i_local, bool own_input, cha
     M26B_CK(S->gweights.ensure(routes * 4), "m26b gweights alloc");
     M26B_CK(S->experts.ensure(kExperts * sizeof(ExpertPlan)), "m26b experts alloc");
     M26B_CK(S->tiles.ensure(tiles_max * sizeof(TokenTile)), "m26b tiles alloc");
-    M26B_CK(S->items1.ensure(tiles_max * (i_local / kTileM) * sizeof(WorkItem)), "m26b fc1 items alloc");
+    M26B_CK(S->items1.ensure(tiles_max * (i_local / kTileM) * 2 * sizeof(WorkItem)), "m26b fc1 items alloc");   // x 2: half items
     M26B_CK(S->items2.ensure(tiles_max * (kHidden / kPairM) * sizeof(WorkItem)), "m26b fc2 items alloc");
     M26B_CK(S->sfb1.ensure(tiles_max * (kHidden / kChunkK) * kScaleBlockBytes), "m26b sfb alloc");
     M26B_CK(S->mid_sf.ensure(tiles_max * (i_local / kChunkK) * kScaleBlockBytes), "m26b mid scale alloc");
@@ -456,6 +467,16 @@ void launch_small_prologue(uint32_t sms, cudaStream_t st, const SmallIo& io, con
     }
 }
 
+// Half items for FC1 of a decode-sized pass? The host knows the token count, not the plan: it estimates the token tiles as
+// one per routed expert (at most 256, at most one per route). Half items pay when full items would not fill two rounds of
+// the SMs (16 tokens on a rank of eight: 204 items for 148 SMs, FC1 38.9 -> 35.0 us; 4 tokens: 20.5 -> 18.5 us); with more
+// items they lose, because a half item moves half the bytes per copy instruction and per pipeline hand-over (16 tokens on
+// one GPU, 1,632 items: 162 -> 191 us; rank of four, 408 items: 57.4 -> 61.4 us).
+bool fc1_half_items(uint32_t rows, int mt1, int sms) {
+    const uint32_t routes = rows * kTopK, tiles = routes < uint32_t(kExperts) ? routes : uint32_t(kExperts);
+    return tiles * uint32_t(mt1) < 2u * uint32_t(sms);
+}
+
 // A pass of an expert-parallel step: where the pass's token rows live and where its FC2 rows go.
 struct EpPass {
     TokenSources src;
@@ -487,6 +508,10 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     const int k2 = L->i_local / kChunkK;
     const int span2 = pair ? 1 : (k2 >= 8 ? 1 : k2 >= 4 ? 2 : 4);
     const int m_step1 = pair ? 2 : 1, m_step2 = pair ? 2 : span2;
+    // FC1 of a decode-sized pass: half items (twice as many, half as long) when full items would leave the SMs a ragged
+    // last round
+    const bool half1 = !pair && rows <= 32 && fc1_half_items(rows, mt1, S->sms);
+    const int mt1_plan = half1 ? 2 * mt1 : mt1;
     const bool kt = (S->debug & 2u) != 0;
     if (kt) M26B_CK(cudaEventRecord(S->kev[1], st), "m26b event");
     const PlanScope scope{L->slots, ep ? ep->own_lo : 0u, ep ? ep->own_hi : rows, ep ? 1 : 0};
@@ -502,16 +527,16 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         const uint32_t grid = uint32_t(S->sms);
         const int sel = raw ? raw->codec * 2 + raw->dtype : 4;
         switch (sel) {
-            case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
-            case 1: launch_small_prologue<0, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
-            case 2: launch_small_prologue<1, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
-            case 3: launch_small_prologue<1, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
-            default: launch_small_prologue<0, 2>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1, mt2, span2, po); break;
+            case 0: launch_small_prologue<0, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1_plan, mt2, span2, po); break;
+            case 1: launch_small_prologue<0, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1_plan, mt2, span2, po); break;
+            case 2: launch_small_prologue<1, 0>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1_plan, mt2, span2, po); break;
+            case 3: launch_small_prologue<1, 1>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1_plan, mt2, span2, po); break;
+            default: launch_small_prologue<0, 2>(grid, st, io, ids, w, rows, L->slots, lc.max_n, mt1_plan, mt2, span2, po); break;
         }
         M26B_CK(cudaGetLastError(), "m26b prologue launch");
     } else {
         if (routes <= 4096) {
-            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, scope, lc.max_n, mt1, mt2, m_step1, m_step2, po);
+            plan_kernel<<<1, 1024, 0, st>>>(ids, w, rows, scope, lc.max_n, mt1_plan, mt2, m_step1, m_step2, po);
         } else {
             // each CTA takes a whole number of 1024-route slabs, so every warp segment is a multiple of 32
             const uint32_t slabs = (routes + 1023u) / 1024u;
@@ -519,7 +544,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
             const uint32_t cta_routes = ((slabs + n_cta - 1u) / n_cta) * 1024u;
             uint32_t* cta_cnt = S->plan_cnt.as<uint32_t>();
             plan_count_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, scope, cta_routes, cta_cnt, &status->meta);
-            plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1, mt2, m_step1, m_step2, L->slots, po);
+            plan_scan_kernel<<<1, 1024, 0, st>>>(n_cta, cta_cnt, lc.max_n, mt1_plan, mt2, m_step1, m_step2, L->slots, po);
             plan_place_kernel<<<n_cta, 1024, 0, st>>>(ids, w, rows, cta_routes, cta_cnt, po, scope);
         }
         M26B_CK(cudaGetLastError(), "m26b plan launch");
@@ -564,6 +589,9 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
         PairMaps pm = S->pair_x;
         pm.sfa = L->map_s13;
         M26B_CK(launch_fc1_pair(dump, L->map_w13, pm, a, S->pair_ctas, st), "m26b fc1 launch");
+    } else if (half1) {
+        a.sfa = L->s13h;
+        M26B_CK(launch_fc1_half(dump, L->map_w13h, S->map_x, a, S->sms, st), "m26b fc1 launch");
     } else {
         M26B_CK(launch_gemm_class<kModeFc1>(rows, dump, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
     }
@@ -789,7 +817,7 @@ int m26b_layer_i_local(const m26b_layer* L) { return L ? L->i_local : 0; }
 
 void m26b_layer_free(m26b_layer* L) {
     if (!L) return;
-    cudaFree(L->w13); cudaFree(L->s13); cudaFree(L->w2); cudaFree(L->s2); cudaFree(L->slots);
+    cudaFree(L->w13); cudaFree(L->s13); cudaFree(L->s13h); cudaFree(L->w2); cudaFree(L->s2); cudaFree(L->slots);
     delete L;
 }
 

@@ -514,7 +514,22 @@ def test_ffn_verify_round_128_tokens_zipf(layer, scratch, dev, oracle_mod):
 
 @pytest.mark.parametrize("tokens", [1, 2, 33, 113])
 def test_ffn_ragged_token_counts(layer, scratch, dev, oracle_mod, tokens):
+    """1 and 2 tokens also run FC1 with half items (64 gate + 64 up rows per item): fewer than two rounds of full items."""
     check_ffn(layer, scratch, dev, oracle_mod, tokens, 0.7, codec=0, seed=SEED + tokens)
+
+
+@pytest.mark.parametrize("tp_rank,tp_size,tokens", [(3, 8, 16), (1, 4, 9), (7, 8, 18)])
+def test_ffn_tensor_parallel_rank_stages_with_half_items(weights, scratch, dev, oracle_mod, tp_rank, tp_size, tokens):
+    """A rank of a tensor-parallel group on the decode batch, every stage against the oracle's slice: these sizes run FC1
+    with half items (the up accumulators cross from their warps to the gate warps through shared memory)."""
+    import mimo26f_afd_b200 as M
+    from mimo26f_afd_b200 import synth
+
+    L = M.Layer.from_checkpoint(*[weights[n] for n in synth.TENSORS], tp_rank=tp_rank, tp_size=tp_size)
+    try:
+        check_ffn(L, scratch, dev, oracle_mod, tokens, 0.0, codec=0, tp_rank=tp_rank, tp_size=tp_size, seed=SEED + 31 * tokens)
+    finally:
+        L.close()
 
 
 @pytest.mark.parametrize("tokens,cut,zipf", [(129, 1, 1.5), (130, 111, 0.5), (145, 61, 1.5), (513, 325, 0.0), (1025, 350, 1.5), (2469, 1206, 0.0)])
