@@ -126,12 +126,15 @@ struct TokenMaps {
 // decode step has twice as many, half as long items to spread over the SMs (a tensor-parallel rank of eight has 204 full
 // items for 148 SMs: two rounds where 1.4 would do). Gate and up of a feature then sit in different tensor-memory lanes
 // (quadrants 0-1 gate, 2-3 up): the up warps hand their values to the gate warps through `xup`.
+// A stage of half items holds TWO K chunks, so that a stage (and with it every copy instruction and barrier hand-over)
+// moves as many bytes as a stage of full items: [chunk][rows][128 bytes] for both operands, [chunk][512] for the scales.
 template <int B_ROWS, int STAGES, int A_TILES = 2>
 struct GemmSmem {
-    alignas(1024) uint8_t a[STAGES][A_TILES * kTileM * 128];
-    alignas(1024) uint8_t b[STAGES][B_ROWS * 128];
-    alignas(16) uint8_t sfa[STAGES][A_TILES * kScaleBlockBytes];
-    alignas(16) uint8_t sfb[STAGES][kScaleBlockBytes];
+    static constexpr int kSub = A_TILES == 1 ? 2 : 1;      // K chunks per stage
+    alignas(1024) uint8_t a[STAGES][kSub * A_TILES * kTileM * 128];
+    alignas(1024) uint8_t b[STAGES][kSub * B_ROWS * 128];
+    alignas(16) uint8_t sfa[STAGES][kSub * A_TILES * kScaleBlockBytes];
+    alignas(16) uint8_t sfb[STAGES][kSub * kScaleBlockBytes];
     uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -165,17 +168,19 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 }
 
 static_assert(sizeof(GemmSmem<32, 6>) + 1024 <= 232448 && sizeof(GemmSmem<kMaxN, 4>) + 1024 <= 232448 && sizeof(GemmSmem<64, 5>) + 1024 <= 232448 &&
-              sizeof(GemmSmem<32, 10, 1>) + 1024 <= 232448,
+              sizeof(GemmSmem<32, 5, 1>) + 1024 <= 232448,
               "a CTA has at most 227 KB of shared memory");
 
 // DUMP: also store the FP32 intermediate (stage dumps of the parity tests). Y16: FC2 rows as BF16.
-// A_TILES = 1 (FC1, token tiles of at most 64): half items; map_w then has 64-row boxes, p.sfa names the half-item scale
-// image [E][m_tiles][2 halves][k_chunks][512] and WorkItem::m_tile counts halves.
+// A_TILES = 1 (FC1, token tiles of at most 64): half items; map_w is then the 3-D view of w13 [tile pair x gate/up][128 rows][K]
+// with boxes of 2 x 64 rows, p.sfa names the half-item scale image [E][m_tiles][2 halves][k_chunks][512] and
+// WorkItem::m_tile counts halves.
 template <int MODE, int B_ROWS, int STAGES, bool DUMP = false, bool Y16 = false, int A_TILES = 2>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_x, const GemmArgs p) {
     using Smem = GemmSmem<B_ROWS, STAGES, A_TILES>;
     constexpr bool kHalf = A_TILES == 1;
+    constexpr int kSub = Smem::kSub;
     static_assert(!kHalf || (MODE == kModeFc1 && B_ROWS <= 64), "half items: FC1 with token tiles of at most 64");
     // Token tiles of at most 64 columns leave room for two accumulator sets in each tile's 128 tensor-memory columns
     // (set b at column offset b * B_ROWS): the MMAs of item i + 1 start while the epilogue still pulls item i. With items
@@ -243,32 +248,40 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const WorkItem wi = cur.wi;
                 const TokenTile tt = cur.tt;
                 const uint8_t* sfb_g = p.sfb + size_t(wi.tile) * p.k_chunks * kScaleBlockBytes;
-                const uint32_t tx = A_TILES * kTileM * 64 + tt.n_mma * 128 + (A_TILES + 1) * kScaleBlockBytes;
+                const uint32_t tx = kSub * (A_TILES * kTileM * 64 + tt.n_mma * 128 + (A_TILES + 1) * kScaleBlockBytes);
                 for (int mm = 0; mm < p.m_span && ok; ++mm) {
                     // half items: m_tile counts halves; half h of tile pair j = gate rows 64 h .. and up rows 128 + 64 h ..
                     const int m_pair = kHalf ? (wi.m_tile >> 1) : wi.m_tile + mm, half = kHalf ? (wi.m_tile & 1) : 0;
                     const int slot = tt.expert * p.m_tiles + m_pair;
-                    const int w_row = slot * kPairM + half * (kTileM / 2);
-                    const uint8_t* sfa_g = p.sfa + (size_t(slot) * 2 + half * (kHalf ? 1 : 0)) * p.k_chunks * kScaleBlockBytes;
-                    for (int c = 0; c < p.k_chunks; ++c) {
+                    const int w_row = slot * kPairM;
+                    const uint8_t* sfa_g = p.sfa + (size_t(slot) * 2 + half) * p.k_chunks * kScaleBlockBytes;
+                    for (int c = 0; c < p.k_chunks; c += kSub) {
                         const bool weights_in_flight = kEarlyWeights && it == blockIdx.x && mm == 0 && c < early;
                         if (!weights_in_flight) {
                             if (!mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                             mbar_expect_tx(&s.full[stage], tx);
-                            tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
-                            if constexpr (kHalf) tma_load_2d(s.a[stage] + (kTileM / 2) * 128, &map_w, c * kChunkK, w_row + kTileM, &s.full[stage]);
-                            bulk_load(s.sfa[stage], sfa_g + size_t(c) * A_TILES * kScaleBlockBytes, A_TILES * kScaleBlockBytes, &s.full[stage]);
-                        }
-                        int r = 0;
+                            if constexpr (kHalf) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int rows = 128 >> i;
-                            if (tt.n_mma - r >= rows) {   // n_mma <= 128: each size is needed at most once
-                                tma_load_2d(s.b[stage] + r * 128, &maps_x.box[i], c * kChunkK, tt.row_base + r, &s.full[stage]);
-                                r += rows;
+                                for (int u = 0; u < kSub; ++u)      // one box: 64 gate rows, then the 64 up rows of the same features
+                                    tma_load_3d(s.a[stage] + u * kTileM * 128, &map_w, (c + u) * kChunkK, half * (kTileM / 2), slot * 2, &s.full[stage]);
+                            } else {
+                                tma_load_2d(s.a[stage], &map_w, c * kChunkK, w_row, &s.full[stage]);
+                            }
+                            bulk_load(s.sfa[stage], sfa_g + size_t(c) * A_TILES * kScaleBlockBytes, kSub * A_TILES * kScaleBlockBytes, &s.full[stage]);
+                        }
+#pragma unroll
+                        for (int u = 0; u < kSub; ++u) {
+                            int r = 0;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int rows = 128 >> i;
+                                if (tt.n_mma - r >= rows) {   // n_mma <= 128: each size is needed at most once
+                                    tma_load_2d(s.b[stage] + (u * B_ROWS + r) * 128, &maps_x.box[i], (c + u) * kChunkK, tt.row_base + r, &s.full[stage]);
+                                    r += rows;
+                                }
                             }
                         }
-                        bulk_load(s.sfb[stage], sfb_g + size_t(c) * kScaleBlockBytes, kScaleBlockBytes, &s.full[stage]);
+                        bulk_load(s.sfb[stage], sfb_g + size_t(c) * kScaleBlockBytes, kSub * kScaleBlockBytes, &s.full[stage]);
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
                 }
@@ -296,25 +309,29 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (!mbar_wait(&s.acc_empty[aset], (ause & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d0 = tb + aset * B_ROWS, d1 = d0 + kAcc1;
-                for (int c = 0; c < p.k_chunks; ++c) {
+                for (int c = 0; c < p.k_chunks; c += kSub) {
                     if (!mbar_wait(&s.full[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    // consecutive chunks alternate between two scale slots in tensor memory
-                    const uint32_t t_sf = tb + kSfSlot0 + sf_slot * kSfSlotStride;
-                    sf_slot ^= 1u;
-                    const uint64_t sfa_d = sfa_desc0 + stage * kSfaStage;
-                    tc_cp_scales(t_sf, sfa_d);
-                    if constexpr (!kHalf) tc_cp_scales(t_sf + 4, sfa_d + (kScaleBlockBytes >> 4));
-                    tc_cp_scales(t_sf + 8, sfb_desc0 + stage * kSfbStage);
-                    const uint64_t ad = a_desc0 + stage * kAStage, bd = b_desc0 + stage * kBStage;
 #pragma unroll
-                    for (uint32_t kb = 0; kb < 4; ++kb) {
-                        // K32 slice kb: 32 bytes further into the swizzle atom (descriptor addresses count 16 bytes);
-                        // scale-factor byte kb of each tensor-memory column (instruction-descriptor bits 4-5 and 29-30)
-                        const uint32_t idesc = idesc0 | (kb << 4) | (kb << 29);
-                        const uint32_t accum = (c | int(kb)) ? 1u : 0u;
-                        tc_mma_mx(d0, ad + 2 * kb, bd + 2 * kb, idesc, t_sf, t_sf + 8, accum);
-                        if constexpr (!kHalf) tc_mma_mx(d1, ad + ((kTileM * 128) >> 4) + 2 * kb, bd + 2 * kb, idesc, t_sf + 4, t_sf + 8, accum);
+                    for (int u = 0; u < kSub; ++u) {
+                        // consecutive chunks alternate between two scale slots in tensor memory
+                        const uint32_t t_sf = tb + kSfSlot0 + sf_slot * kSfSlotStride;
+                        sf_slot ^= 1u;
+                        const uint64_t sfa_d = sfa_desc0 + stage * kSfaStage + u * ((A_TILES * kScaleBlockBytes) >> 4);
+                        tc_cp_scales(t_sf, sfa_d);
+                        if constexpr (!kHalf) tc_cp_scales(t_sf + 4, sfa_d + (kScaleBlockBytes >> 4));
+                        tc_cp_scales(t_sf + 8, sfb_desc0 + stage * kSfbStage + u * (kScaleBlockBytes >> 4));
+                        const uint64_t ad = a_desc0 + stage * kAStage + u * ((A_TILES * kTileM * 128) >> 4);
+                        const uint64_t bd = b_desc0 + stage * kBStage + u * ((B_ROWS * 128) >> 4);
+#pragma unroll
+                        for (uint32_t kb = 0; kb < 4; ++kb) {
+                            // K32 slice kb: 32 bytes further into the swizzle atom (descriptor addresses count 16 bytes);
+                            // scale-factor byte kb of each tensor-memory column (instruction-descriptor bits 4-5 and 29-30)
+                            const uint32_t idesc = idesc0 | (kb << 4) | (kb << 29);
+                            const uint32_t accum = (c | u | int(kb)) ? 1u : 0u;
+                            tc_mma_mx(d0, ad + 2 * kb, bd + 2 * kb, idesc, t_sf, t_sf + 8, accum);
+                            if constexpr (!kHalf) tc_mma_mx(d1, ad + ((kTileM * 128) >> 4) + 2 * kb, bd + 2 * kb, idesc, t_sf + 4, t_sf + 8, accum);
+                        }
                     }
                     tc_commit(&s.empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }

@@ -73,6 +73,19 @@ bool make_map(CUtensorMap* m, bool fp4, void* base, uint64_t cols, uint64_t rows
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The 4-bit FC1 weight image [rows][4096] seen as [blocks of 128 rows][128][4096] (blocks alternate gate / up) with boxes of
+// 128 elements x 64 rows x 2 blocks: one copy brings the 64 gate rows and the 64 up rows of a half item's features.
+bool make_map_half(CUtensorMap* m, void* base, uint64_t rows) {
+    EncodeTiledFn f = encode_fn();
+    if (!f) return false;
+    cuuint64_t dims[3] = {uint64_t(kHidden), uint64_t(kTileM), rows / kTileM};
+    cuuint64_t strides[2] = {uint64_t(kHidden) / 2, uint64_t(kTileM) * (kHidden / 2)};
+    cuuint32_t box[3] = {128, kTileM / 2, 2};
+    cuuint32_t es[3] = {1, 1, 1};
+    return f(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Launch with the programmatic-serialization attribute: the kernel may be placed while the kernel before it in the
 // stream drains, and orders itself with grid_dep_wait().
 template <typename... P, typename... A>
@@ -172,9 +185,9 @@ cudaError_t launch_gemm_class(uint32_t rows, bool variant, const CUtensorMap& mw
 }
 
 // FC1 with half items (64 gate + 64 up rows per item): `mw` has 64-row boxes, a.sfa names the half-item scale image.
-// Only the smallest launch class (at most 32 tokens) ever has few enough items for them to pay.
+// Only the smallest launch class (at most 32 tokens) ever has few enough items for them to pay. Five stages of two K chunks.
 cudaError_t launch_fc1_half(bool dump, const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
-    return dump ? launch_gemm<kModeFc1, 32, 10, true, false, 1>(mw, mx, a, ctas, st) : launch_gemm<kModeFc1, 32, 10, false, false, 1>(mw, mx, a, ctas, st);
+    return dump ? launch_gemm<kModeFc1, 32, 5, true, false, 1>(mw, mx, a, ctas, st) : launch_gemm<kModeFc1, 32, 5, false, false, 1>(mw, mx, a, ctas, st);
 }
 
 // Device status block of one pass: PlanMeta then four fault words.
@@ -331,7 +344,7 @@ int prepare_layer(const ExpertSet& home, const ExpertSet* rep, const int32_t* re
     cudaFree(flag); flag = nullptr;
     L->all_normal = h == 0;
     if (!make_map(&L->map_w13, true, L->w13, kHidden, uint64_t(n_slots) * 2 * i_local, kHidden / 2, kPairM) ||
-        !make_map(&L->map_w13h, true, L->w13, kHidden, uint64_t(n_slots) * 2 * i_local, kHidden / 2, kTileM / 2) ||
+        !make_map_half(&L->map_w13h, L->w13, uint64_t(n_slots) * 2 * i_local) ||
         !make_map(&L->map_w2, true, L->w2, uint64_t(i_local), uint64_t(n_slots) * kHidden, uint64_t(i_local) / 2, kPairM)) {
         set_msg(err, errlen, "m26b layer: cuTensorMapEncodeTiled failed for the weight operands");
         m26b_layer_free(L);
@@ -468,13 +481,14 @@ void launch_small_prologue(uint32_t sms, cudaStream_t st, const SmallIo& io, con
 }
 
 // Half items for FC1 of a decode-sized pass? The host knows the token count, not the plan: it estimates the token tiles as
-// one per routed expert (at most 256, at most one per route). Half items pay when full items would not fill two rounds of
-// the SMs (16 tokens on a rank of eight: 204 items for 148 SMs, FC1 38.9 -> 35.0 us; 4 tokens: 20.5 -> 18.5 us); with more
-// items they lose, because a half item moves half the bytes per copy instruction and per pipeline hand-over (16 tokens on
-// one GPU, 1,632 items: 162 -> 191 us; rank of four, 408 items: 57.4 -> 61.4 us).
+// one per routed expert (at most 256, at most one per route). Half items pay when full items would not fill four rounds
+// of the SMs. Measured on one GPU, FC1 between events / whole step of a rank, full -> half items: 16 tokens on a rank of
+// eight (204 full items for 148 SMs) 38.9 -> 35.9 / 66.6 -> 62.5 us, 4 tokens there 21.5 -> 17.4 / 42.0 -> 35.8 us, 32 tokens
+// there 52.3 -> 50.2 / 89.1 -> 87.0 us, 4 tokens on one GPU 66.6 -> 64.5 / 105.5 -> 103.4 us; with more items the better
+// spread no longer pays for the extra item hand-overs (16 tokens on one GPU, 1,632 full items: 158.8 -> 160.8 / 248.8 -> 250.9 us).
 bool fc1_half_items(uint32_t rows, int mt1, int sms) {
     const uint32_t routes = rows * kTopK, tiles = routes < uint32_t(kExperts) ? routes : uint32_t(kExperts);
-    return tiles * uint32_t(mt1) < 2u * uint32_t(sms);
+    return tiles * uint32_t(mt1) < 4u * uint32_t(sms);
 }
 
 // A pass of an expert-parallel step: where the pass's token rows live and where its FC2 rows go.
