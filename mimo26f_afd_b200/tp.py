@@ -4,9 +4,11 @@ The reference shards the expert intermediate dimension over four machines (TP4: 
 [512 r, 512 (r+1)) and the matching down columns, ``crates/mimo26-repack/src/geom.rs:29-35``) and sums the four
 BF16 partial planes on the coordinator in FP32, in rank order (``crates/mimo26-coordinator/kernels/glue.cu:202-213``,
 ``crates/mimo26-wire/src/l4.rs:169-244``). Here the ranks are G in {1, 2, 4, 8} GPUs: inputs are replicated and each
-rank produces a full-width BF16 partial. By default the planes stay where each rank's combine wrote them, in a window
-every peer has mapped, and one kernel per rank adds them in rank order while reading the peers' planes over NVLink
-(``make_exchange`` / ``Exchange.sum``); ``tp_combine`` is the alternative that gathers the planes with one NCCL
+rank produces a full-width BF16 partial. For decode-sized steps ``expert.ffn_tp_dev`` runs the combine and the exchange as
+one kernel (every rank stores its BF16 codes, tagged with the step number, into windows the peers have mapped, and adds
+what the peers stored). Otherwise the planes stay where each rank's combine wrote them, in such a window, and one kernel
+per rank adds them in rank order while reading the peers' planes over NVLink (``make_exchange`` / ``Exchange.sum``);
+``tp_combine`` is the alternative that gathers the planes with one NCCL
 all-gather and sums them with the library's kernel (also what runs on CPU tensors over gloo in the tests). Both keep
 the reference's bit-exact rank-ordered sum (an NCCL ring reduce would round per hop, in ring order). ``make_expert_parallel``
 connects the windows of the expert-parallel step (experts and tokens split over the ranks).
