@@ -182,7 +182,9 @@ int m26b_produce_dev(const float* logits, const float* bias, uint32_t rows, int3
  * the slot m26b_exchange_plane() names, and m26b_exchange_sum_dev() enqueues ONE kernel that publishes the plane,
  * waits (bounded) for every peer's, reads the peers' planes over NVLink and writes the rank-ordered FP32 sum.
  *   new:      allocate the window (plane_bytes a multiple of 256); handle_out receives 64 bytes for the peers
- *             (an IPC handle of the window), or pass NULL when every rank lives in this process.
+ *             (an IPC handle of the window), or pass NULL when every rank lives in this process. The window holds the
+ *             two plane slots and, for m26b_ffn_tp_dev's fused form, two receive planes per rank of
+ *             2 x min(plane_bytes, 4 MiB) bytes each (at most 128 MiB at eight ranks).
  *   connect:  `handles` = world x 64 bytes in rank order, gathered by the caller (e.g. an all-gather on the host).
  *   connect_local: the same for windows of one process (`all` = world handles in rank order).
  *   plane:    device address the NEXT step's BF16 plane must be written to (alternates between the two slots).
