@@ -90,7 +90,9 @@ void m26b_scratch_free(m26b_scratch* scratch);
  * ms (or NULL) receives 8 floats: [0] host time to upload and enqueue, [1] GPU
  * time of the FFN, [2] host tail (download, checks), [3] token tiles (the
  * reference reports 16-row groups here), [4] plan+permute+FC1 (the
- * intermediate quantiser is fused into FC1), [5] 0, [6] FC2, [7] combine. */
+ * intermediate quantiser is fused into FC1), [5] 0, [6] FC2, [7] combine.
+ * [4]..[7] are measured only with debug flag 4 (m26b_scratch_set_debug) and read 0 otherwise: the events between
+ * the kernels they need cost the overlap of dependent launches, about 10 us of a 16-token step. */
 int m26b_ffn(const m26b_layer* layer, m26b_scratch* scratch, const uint8_t* payload, size_t payload_pitch,
              const uint8_t* scales, size_t scales_pitch, const int32_t* ids, const float* weights, uint32_t rows,
              uint16_t* bf16_out, float* ms, char* err, size_t errlen);
@@ -114,7 +116,8 @@ int m26b_scratch_status(m26b_scratch* scratch, void* stream, char* err, size_t e
 
 /* Stage dumps for parity tests (the reference's primitive cell dumps stages the
  * same way: crates/mimo26-expert/tests/b1_core/primitive.cu:173-196).
- * flags bit 0: keep an FP32 copy of silu(gate)*up before quantisation; bit 1: record per-kernel events. */
+ * flags bit 0: keep an FP32 copy of silu(gate)*up before quantisation; bit 1: record per-kernel events;
+ * bit 2 (value 4): m26b_ffn splits its GPU time into stages (ms[4..7]). */
 int m26b_scratch_set_debug(m26b_scratch* scratch, uint32_t flags);
 enum {
     M26B_PEEK_META = 0,            /* 8 x u32: fault, tiles, fc1 items, fc2 items, active experts, max count */

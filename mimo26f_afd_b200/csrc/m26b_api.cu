@@ -2,6 +2,7 @@
 // Declarations and the reference interfaces they replace: include/m26b_expert.h.
 #include <cuda_runtime.h>
 #include <cuda.h>
+#include <atomic>
 #include <chrono>
 #include <cstdint>
 #include <cstdio>
@@ -102,9 +103,17 @@ cudaError_t launch_dependent(void (*kernel)(P...), unsigned grid, unsigned block
 template <int MODE, int B_ROWS, int STAGES, bool DUMP, bool Y16, int A_TILES = 2>
 cudaError_t launch_gemm(const CUtensorMap& mw, const TokenMaps& mx, const GemmArgs& a, int ctas, cudaStream_t st) {
     const int smem = int(sizeof(GemmSmem<B_ROWS, STAGES, A_TILES>)) + 1024;
-    const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16, A_TILES>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
+    // the shared-memory opt-in is per kernel and per device: set once (one flag bit per device of this process)
+    static std::atomic<uint64_t> opted{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(opted.load(std::memory_order_relaxed) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16, A_TILES>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        opted.fetch_or(bit, std::memory_order_relaxed);
+    }
     return launch_dependent(gemm_mx_kernel<MODE, B_ROWS, STAGES, DUMP, Y16, A_TILES>, unsigned(ctas), kGemmThreads, size_t(smem), st, mw, mx, a);
 }
 // Scale blocks as a 2-D tensor of 128 x u32 rows (one 512-byte block per row), no swizzle.
@@ -609,7 +618,8 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     } else {
         M26B_CK(launch_gemm_class<kModeFc1>(rows, dump, L->map_w13, S->map_x, a, S->sms, st), "m26b fc1 launch");
     }
-    if (events) M26B_CK(cudaEventRecord(S->ea, st), "m26b event a");
+    const bool stage_events = events && (S->debug & 4u) != 0;    // events between the kernels cost their overlap
+    if (stage_events) M26B_CK(cudaEventRecord(S->ea, st), "m26b event a");
     if (kt) M26B_CK(cudaEventRecord(S->kev[4], st), "m26b event");
     // FC2: weights w2 (K = i_local), tokens mid_q
     a.items = S->items2.as<WorkItem>(); a.n_items = &status->meta.n_items_fc2;
@@ -622,7 +632,7 @@ int enqueue_pass(const m26b_layer* L, m26b_scratch* S, const uint8_t* xq, const 
     } else {
         M26B_CK(launch_gemm_class<kModeFc2>(rows, y16, L->map_w2, S->map_mid, a, S->sms, st), "m26b fc2 launch");
     }
-    if (events) M26B_CK(cudaEventRecord(S->ec, st), "m26b event c");
+    if (stage_events) M26B_CK(cudaEventRecord(S->ec, st), "m26b event c");
     if (kt) M26B_CK(cudaEventRecord(S->kev[5], st), "m26b event");
     if (push) {
         // combine, push into every rank's window, add the peers' chunks: one kernel, one step of the exchange
@@ -925,8 +935,10 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     rc = upload_request(S, payload, payload_pitch, scales, scales_pitch, ids, weights, rows, &xq_d, &xs_d, &ids_d, &w_d, err, errlen);
     if (rc) return rc;
     uint16_t* const out_d = S->gather.as<uint16_t>();
-    // stage timings cost four events between the kernels (and the overlap of dependent launches): only when asked for
+    // GPU time of the pass from two events around it; the stage split (two more events between the kernels, which cost
+    // the overlap of dependent launches: ~10 us of a decode step) only with debug flag 4
     const bool timed = ms != nullptr && passes == 1;
+    const bool staged = timed && (S->debug & 4u) != 0;
     for (uint32_t ps = 0; ps < passes; ++ps) {
         const uint32_t r0 = ps * kMaxPassRows, n = rows - r0 < kMaxPassRows ? rows - r0 : kMaxPassRows;
         rc = enqueue_pass(L, S, xq_d + size_t(r0) * kHidden, xs_d + size_t(r0) * (kHidden / kBlockK),
@@ -945,8 +957,8 @@ int m26b_ffn(const m26b_layer* L, m26b_scratch* S, const uint8_t* payload, size_
     const auto t2 = std::chrono::steady_clock::now();
     if (ms) {
         float gpu_ms = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-        if (timed) {
-            cudaEventElapsedTime(&gpu_ms, S->e0, S->e1);
+        if (timed) cudaEventElapsedTime(&gpu_ms, S->e0, S->e1);
+        if (staged) {
             cudaEventElapsedTime(&p1, S->e0, S->ea);
             cudaEventElapsedTime(&p2, S->ea, S->ec);
             cudaEventElapsedTime(&p3, S->ec, S->e1);

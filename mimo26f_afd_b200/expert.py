@@ -186,7 +186,7 @@ class FfnStats:
     gpu_ms: float
     tail_ms: float
     groups: int
-    phase_ms: tuple  # FC1 (with plan, permute and the fused quantiser), 0, FC2, combine
+    phase_ms: tuple  # FC1 (with plan, permute and the fused quantiser), 0, FC2, combine; zeros unless Scratch.set_debug(4)
 
 
 def _ffn_raw(layer, scratch, payload_ptr, payload_pitch, scales_ptr, scales_pitch, ids, weights, rows, bf16_out):
