@@ -334,7 +334,7 @@ def test_plane_exchange_two_windows_one_process(dev, oracle_mod):
         e_.close()
 
 
-@pytest.mark.parametrize("tokens,zipf,n_rep", [(9, 0.0, 0), (96, 1.2, 0), (300, 0.0, 0), (96, 1.2, 6), (700, 1.0, 12)])
+@pytest.mark.parametrize("tokens,zipf,n_rep", [(3, 0.0, 0), (9, 0.0, 0), (96, 1.2, 0), (300, 0.0, 0), (96, 1.2, 6), (700, 1.0, 12)])
 def test_expert_parallel_two_ranks_one_process_equals_single_gpu(layer, scratch, dev, tokens, zipf, n_rep):
     """Expert parallelism with both ranks in this process (each rank's rendezvous is marked reached from the host, so no
     kernel waits for another kernel): experts split 128 / 128, tokens split in two blocks, rows gathered from and

@@ -73,9 +73,9 @@ def test_step_bench_replays_a_workload_file_on_the_gpu(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     rep = json.loads(r.stdout.strip().splitlines()[-1])
     steps = SH.parse(doc, "C16-w8")["steps"]
-    assert rep["workload"] == "C16-w8" and rep["tokens"] == 16 and rep["steps"] == 3 and rep["samples_per_step"] == 5
+    assert rep["workload"] == "C16-w8" and rep["tokens"] == SH.WORKLOAD_TOKENS["C16-w8"] and rep["steps"] == 3 and rep["samples_per_step"] == 5
     assert rep["source"] == str(path)
     assert abs(rep["experts_per_step_mean"] - np.mean([s["experts"] for s in steps])) < 1e-9
-    # a 16-token step streams its distinct experts' weights: between a tenth of and the whole HBM bandwidth of the part
+    # a verify-round step streams its distinct experts' weights: between a tenth of and the whole HBM bandwidth of the part
     assert 500.0 < rep["distinct_weight_gbs_min"] <= rep["distinct_weight_gbs_median"] < 8000.0
     assert 0.0 < rep["us_per_step_median"] <= rep["us_per_step_max"] < 2000.0
