@@ -1020,6 +1020,22 @@ def test_ffn_tp_host_entry_point_one_rank_and_two_windows(weights, dev, oracle_m
             expert.ffn_tp_dev(layers[1], s1, exs[1], xqd, idd, wd, tokens, sum1, x_dtype=expert.X_E4M3, x_scales=xsd)
             s1.status(); exs[1].status()
             assert np.array_equal(sum1.cpu().numpy().view(np.uint32).reshape(tokens, H), want.view(np.uint32))
+        if fused and tokens == 16:
+            # a peer that never delivers: rank 0's bounded wait runs out, the call's status names the late rank (code 5),
+            # nothing hangs or faults and the handles stay usable
+            exs[0].set_wait_ms(20)
+            expert.ffn_tp_dev(layers[0], s, exs[0], xqd, idd, wd, tokens, sum1, x_dtype=expert.X_E4M3, x_scales=xsd)
+            s.status(); exs[0].status()                         # rank 1 has already pushed this step (its extra one above)
+            assert np.array_equal(sum1.cpu().numpy().view(np.uint32).reshape(tokens, H), want.view(np.uint32))
+            expert.ffn_tp_dev(layers[0], s, exs[0], xqd, idd, wd, tokens, sum1, x_dtype=expert.X_E4M3, x_scales=xsd)
+            s.status()
+            with pytest.raises(M.ExpertError) as e:
+                exs[0].status()
+            assert e.value.code == 5 and "0x2" in str(e.value)
+            exs[0].status()                                     # the error word was cleared
+            bf_again = np.empty((tokens, H), np.uint16)
+            M.ffn(layers[0], s, xq.reshape(-1), xs.reshape(-1), ids.reshape(-1), w.reshape(-1), tokens, bf_again.reshape(-1))
+            assert np.array_equal(bf_again, bf0)
         if tokens <= 200:
             ref = [oracle_mod.ffn_layer(synth.layer_np(SEED, np.unique(ids)), xq, xs, ids, w, tp_rank=r, tp_size=2) for r in range(2)]
             wire = oracle_mod.rank_sum(np.stack([r["bf16"] for r in ref]))
