@@ -69,7 +69,9 @@ int m26b_layer_all_normal(const m26b_layer* layer);
  * which: 0 = gate/up payload [E][I/128][256 rows][2048 B] (rows 0..127 gate, 128..255 up of the same 128 features),
  * 1 = gate/up scale blocks [E][I/128][32 chunks][2][512 B], 2 = down payload [E][4096][I/2 B],
  * 3 = down scale blocks [E][16][I/128][2][512 B]; a 512-byte scale block holds rows r = 0..127 x K32 blocks kb = 0..3 of
- * one 128-wide K chunk at byte (r % 32) * 16 + (r / 32) * 4 + kb. E = the experts the layer holds, I = its local
+ * one 128-wide K chunk at byte (r % 32) * 16 + (r / 32) * 4 + kb; 4 = the gate/up scale blocks regrouped for half items
+ * [E][I/128][2 halves][32 chunks][512 B]: rows 0..63 of a block are the gate rows 64 h .. 64 h + 63 of the tile, rows
+ * 64..127 the up rows of the same features. E = the experts the layer holds, I = its local
  * intermediate width. Returns NULL for a bad argument; *bytes (may be NULL) receives the image size. */
 const void* m26b_layer_image(const m26b_layer* layer, int which, uint64_t* bytes);
 /* Local intermediate width of the layer (2048 / tp_size). */

@@ -828,10 +828,11 @@ int m26b_layer_new_from_checkpoint_ep_replicated(const uint8_t* gate_w, const ui
 }
 
 const void* m26b_layer_image(const m26b_layer* L, int which, uint64_t* bytes) {
-    if (!L || which < 0 || which > 3) return nullptr;
+    if (!L || which < 0 || which > 4) return nullptr;
     const uint64_t n = uint64_t(L->n_local + L->n_rep), il = uint64_t(L->i_local);
-    const uint64_t size[4] = {n * 2 * il * (kHidden / 2), n * 2 * il * (kHidden / kBlockK), n * kHidden * (il / 2), n * kHidden * (il / kBlockK)};
-    const uint8_t* base[4] = {L->w13, L->s13, L->w2, L->s2};
+    const uint64_t size[5] = {n * 2 * il * (kHidden / 2), n * 2 * il * (kHidden / kBlockK), n * kHidden * (il / 2), n * kHidden * (il / kBlockK),
+                              n * 2 * il * (kHidden / kBlockK)};
+    const uint8_t* base[5] = {L->w13, L->s13, L->w2, L->s2, L->s13h};
     if (bytes) *bytes = size[which];
     return base[which];
 }

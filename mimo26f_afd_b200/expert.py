@@ -99,10 +99,11 @@ class Layer:
             C.byref(out), err, 256), err)
         return cls(out.value)
 
-    IMAGES = {"w13": 0, "s13": 1, "w2": 2, "s2": 3}
+    IMAGES = {"w13": 0, "s13": 1, "w2": 2, "s2": 3, "s13h": 4}
 
     def image(self, which: str):
-        """(device address, bytes) of a prepared operand image: ``w13`` / ``s13`` / ``w2`` / ``s2`` (read-only)."""
+        """(device address, bytes) of a prepared operand image: ``w13`` / ``s13`` / ``w2`` / ``s2`` / ``s13h`` (the gate/up
+        scale blocks regrouped for half items) (read-only)."""
         n = C.c_uint64()
         p = _native.lib().m26b_layer_image(self._h, self.IMAGES[which], C.byref(n))
         if not p:

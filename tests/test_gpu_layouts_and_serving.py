@@ -139,7 +139,7 @@ def test_repack_of_a_tensor_parallel_rank_from_the_canonical_image():
     image = 2 * (gp + gs) + dp + ds
     n = image * 256
     ar = lambda m: torch.arange(m, dtype=torch.int64, device=dev)
-    got = {w: None for w in ("w13", "s13", "w2", "s2")}
+    got = {w: None for w in ("w13", "s13", "w2", "s2", "s13h")}
     for k in range(5):                                      # 7-bit codes: 35 bits cover the image, byte 255 never occurs
         src = _coded(n, k, 7, dev)
         layer = M.Layer.new_tp(src, n, 5, g)
@@ -155,6 +155,14 @@ def test_repack_of_a_tensor_parallel_rank_from_the_canonical_image():
     rr, kb = (o >> 4) + 32 * ((o >> 2) & 3), o & 3
     want = e * image + gp + blk * (gp + gs) + (j * 128 + rr) * (H // 32) + c * 4 + kb
     assert torch.equal(got["s13"], want.reshape(-1))
+    # the regrouped scale image of half items: block (tile j, half h, chunk c) = 64 gate rows, then the 64 up rows of the
+    # same features; a permutation of s13
+    e, j, h, c, o = torch.meshgrid(ar(256), ar(il // 128), ar(2), ar(H // 128), ar(512), indexing="ij")
+    grp, kb = (o >> 2) & 3, o & 3
+    rr = 64 * h + 32 * (grp & 1) + (o >> 4)
+    want = e * image + gp + (grp >> 1) * (gp + gs) + (j * 128 + rr) * (H // 32) + c * 4 + kb
+    assert torch.equal(got["s13h"], want.reshape(-1))
+    assert torch.equal(torch.sort(got["s13h"]).values, torch.sort(got["s13"]).values)
     e, h, b = torch.meshgrid(ar(256), ar(H), ar(il // 2), indexing="ij")
     assert torch.equal(got["w2"], (e * image + 2 * (gp + gs) + h * (il // 2) + b).reshape(-1))
     e, t, c, blk, o = torch.meshgrid(ar(256), ar(H // 256), ar(il // 128), ar(2), ar(512), indexing="ij")
