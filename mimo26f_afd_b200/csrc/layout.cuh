@@ -9,6 +9,8 @@
 //                                               the same 128 intermediate features
 //   s13  [E][I_local/128][H/128][2][512 bytes]  scale blocks (see scale_block_offset):
 //                                               block 0 the gate rows, block 1 the up rows
+//   s13h [E][I_local/128][2][H/128][512 bytes]  the bytes of s13 regrouped for FC1's half items: block (tile, half h,
+//                                               chunk) = gate rows 64 h .. 64 h + 63, then the up rows of the same features
 //   w2   [E][H rows][I_local/2 bytes]           down_proj rows, this rank's K slice
 //   s2   [E][H/256][I_local/128][2][512 bytes]  block b covers rows 256 t + 128 b + r
 // A GEMM work item pairs two 128-row weight tiles (gate/up of the same
