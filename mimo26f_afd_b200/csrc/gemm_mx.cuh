@@ -371,11 +371,12 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 // shared memory, the gate warp picks them up. The first barrier also carries "my wait ran out", so both
                 // warps of a pair leave together and neither can be left waiting at a barrier.
                 const uint32_t pair = (q & 1u) * 4u + wq;
-                uint32_t gt[2][8];
+                constexpr int kHalfGroups = B_ROWS / 32;       // groups of 8 token columns a warp takes (token tiles of at most B_ROWS)
+                uint32_t gt[kHalfGroups][8];
                 if (got) {
                     tc_fence_after();
 #pragma unroll
-                    for (int g = 0; g < 2; ++g) {
+                    for (int g = 0; g < kHalfGroups; ++g) {
                         const int c0 = (int(wq) + 4 * g) * 8;
                         if (c0 < tt.n_mma) tmem_ld8(t_acc + uint32_t(c0), gt[g]);
                     }
@@ -385,7 +386,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (lane == 0) mbar_arrive(&s.acc_empty[aset]);
                     if (q >= 2u) {
 #pragma unroll
-                        for (int g = 0; g < 2; ++g) {
+                        for (int g = 0; g < kHalfGroups; ++g) {
                             if ((int(wq) + 4 * g) * 8 >= tt.n_mma) break;
 #pragma unroll
                             for (int j = 0; j < 8; ++j) s.xup[pair][g * 8 + j][lane] = gt[g][j];
@@ -394,9 +395,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (named_bar_or(1u + pair, 64u, !got)) { ok = false; break; }
                 if (q >= 2u) { named_bar_sync(1u + pair, 64u); continue; }
-                uint32_t up[2][8];
+                uint32_t up[kHalfGroups][8];
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
+                for (int g = 0; g < kHalfGroups; ++g) {
                     if ((int(wq) + 4 * g) * 8 >= tt.n_mma) break;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) up[g][j] = s.xup[pair][g * 8 + j][lane];
@@ -409,7 +410,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float* mf = DUMP ? p.mid_f32 + size_t(tt.row_base) * p.i_local + feat0 + lane : nullptr;
                 uint32_t fault = 0;
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
+                for (int g = 0; g < kHalfGroups; ++g) {
                     const int c0 = (int(wq) + 4 * g) * 8;
                     if (c0 >= tt.n_mma) break;
 #pragma unroll
